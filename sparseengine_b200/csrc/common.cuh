@@ -1,0 +1,69 @@
+// Shared device helpers for the sparseengine_b200 kernels (sm_100a).
+//
+// Conventions of every exported launcher (extern "C", prefix se_):
+//   * pointers are raw device pointers, sizes are explicit integer arguments;
+//   * `dtype` selects the activation type: 0 = float32, 1 = bfloat16;
+//   * the last argument is the CUDA stream; the return value is a cudaError_t as int
+//     (0 = success), or a negative SE_ERR_* code for an argument the kernel refuses.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define SE_ERR_UNSUPPORTED (-2)   // a size this kernel does not take
+#define SE_ERR_ARGUMENT (-3)      // an inconsistent argument
+
+#define SE_DTYPE_F32 0
+#define SE_DTYPE_BF16 1
+
+#define SE_LAUNCH_CHECK() return (int)cudaGetLastError()
+
+#define SE_DISPATCH_DTYPE(dtype, T, ...)                         \
+    if ((dtype) == SE_DTYPE_F32) { using T = float; __VA_ARGS__; } \
+    else if ((dtype) == SE_DTYPE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else return SE_ERR_ARGUMENT;
+
+namespace se {
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round a 32-bit value to the activation type and return it as 32-bit again.
+template <typename T> __device__ __forceinline__ float round_act(float v) { return to_float<T>(from_float<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the whole block; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace se

@@ -1,0 +1,97 @@
+// Embedding gather, RMSNorm (with and without the fused residual add), row gather and
+// the block-table update kernel.
+//
+// RMSNorm follows src/sparseengine/kernels/triton/rmsnorm.py:17-66 of the reference:
+// with a residual the 32-bit sum x+res is what gets normalised, and the residual is
+// overwritten with the sum rounded to the activation type.
+#include "common.cuh"
+
+namespace se {
+
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    T* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* src = table + (size_t)(ok ? id : 0) * hidden;
+    T* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? src[i] : from_float<T>(0.f);
+}
+
+// One block per row. x_sum (dynamic shared memory, `hidden` floats) keeps the 32-bit row.
+template <typename T>
+__global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restrict__ w,
+                               T* y, T* residual_out, int hidden, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = to_float(x[base + i]);
+        if (residual != nullptr) {
+            v += to_float(residual[base + i]);
+            residual_out[base + i] = from_float<T>(v);
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        y[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ idx,
+                                   T* __restrict__ dst, int width) {
+    const size_t s = (size_t)idx[blockIdx.x] * width, d = (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[d + i] = src[s + i];
+}
+
+// updates: n triples (row, index, page); table[row * stride + index] = page.
+__global__ void table_update_kernel(int* table, int stride, const int* __restrict__ updates, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[(size_t)updates[3 * i] * stride + updates[3 * i + 1]] = updates[3 * i + 2];
+}
+
+}  // namespace se
+
+extern "C" int se_embed_gather(const void* table, const int* ids, void* out, int tokens, int hidden,
+                               int vocab, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::embed_gather_kernel<T><<<tokens, 256, 0, stream>>>((const T*)table, ids, (T*)out, hidden, vocab));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+                          int rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    const int threads = hidden >= 2048 ? 512 : 256;
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        se::rmsnorm_kernel<T><<<rows, threads, smem, stream>>>((const T*)x, (const T*)residual, (const T*)w,
+                                                                (T*)y, (T*)residual_out, hidden, eps);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_gather_rows(const void* src, const int* idx, void* dst, int rows, int width, int dtype,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::gather_rows_kernel<T><<<rows, 256, 0, stream>>>((const T*)src, idx, (T*)dst, width));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_table_update(int* table, int stride, const int* updates, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    se::table_update_kernel<<<se::ceil_div(n, 256), 256, 0, stream>>>(table, stride, updates, n);
+    SE_LAUNCH_CHECK();
+}

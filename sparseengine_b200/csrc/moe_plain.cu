@@ -1,0 +1,224 @@
+// Routed experts, plain path: routing build (count, rank, scatter, tile list), grouped
+// GEMMs on CUDA cores with 32-bit accumulation (float32 or bfloat16 operands), and the
+// top-k combine in router slot order.
+//
+// Reference pipeline: src/sparseengine/kernels/triton/moe.py:336-463 (assignment),
+// :466-574,634-739 (routed GEMM, gate/up + SwiGLU), :1098-1210 (sum over k in slot
+// order), :1374-1440 (bf16 pipeline); SiLU src/sparseengine/kernels/triton/silu_and_mul.py:41-60.
+// Rounding points: gate and up are rounded to the activation type, silu(gate) is
+// computed in 32-bit and rounded, the product with up is rounded; the down projection
+// times the routing weight (32-bit) is rounded; the sum over slots is 32-bit, rounded once.
+#include "common.cuh"
+
+namespace se {
+
+// ---- routing build -------------------------------------------------------------------
+// ids: [assignments] expert of flat assignment a = token * top_k + slot.
+// Block e walks all assignments in order and ranks those of expert e (stable).
+__global__ void moe_count_rank_kernel(const int* __restrict__ ids, int assignments, int* __restrict__ counts,
+                                      int* __restrict__ rank) {
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    __shared__ int warp_count[32];
+    __shared__ int running;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    for (int base = 0; base < assignments; base += blockDim.x) {
+        const int a = base + threadIdx.x;
+        const bool mine = a < assignments && ids[a] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[warp] = __popc(ballot);
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; ++w) before += warp_count[w];
+        if (mine) rank[a] = before + __popc(ballot & ((1u << lane) - 1u));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwarps; ++w) tot += warp_count[w];
+            running += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = running;
+}
+
+// One block: exclusive scan of counts -> offsets[experts+1], tile list for rows-per-tile
+// `tile_rows`: tile_expert[i], tile_row0[i] (first sorted row), num_tiles[0].
+// All blocks: scatter sorted[offset[e] + rank[a]] = a, inv_pos[a] = that position.
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
+                                   const int* __restrict__ counts, int assignments, int experts, int tile_rows,
+                                   int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ inv_pos,
+                                   int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                   int* __restrict__ num_tiles) {
+    extern __shared__ int off[];   // experts + 1 offsets, then experts counts
+    int* cnt = off + experts + 1;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = counts[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            off[e] = run;
+            const int c = cnt[e];
+            if (blockIdx.x == 0) {
+                for (int r = 0; r < c; r += tile_rows) {
+                    tile_expert[tiles] = e;
+                    tile_row0[tiles] = run + r;
+                    ++tiles;
+                }
+            }
+            run += c;
+        }
+        off[experts] = run;
+        if (blockIdx.x == 0) num_tiles[0] = tiles;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0)
+        for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = off[e];
+    for (int a = blockIdx.x * blockDim.x + threadIdx.x; a < assignments; a += gridDim.x * blockDim.x) {
+        const int p = off[ids[a]] + rank[a];
+        sorted[p] = a;
+        inv_pos[a] = p;
+    }
+}
+
+// ---- grouped GEMM on CUDA cores ------------------------------------------------------
+constexpr int kBM = 32, kBN = 64, kBK = 16;   // 256 threads, each 2 x 4 outputs
+
+// MODE 0: gate/up + SwiGLU.  A row of sorted position p = x[sorted[p] / top_k];
+//         W = w13[e] ([2*n_out, k_dim]: gate rows then up rows); out[p, n] (n_out = I).
+// MODE 1: down.  A row = act[p]; W = w2[e] ([n_out, k_dim]); out[p, n] = acc * weight[sorted[p]].
+template <typename T, int MODE>
+__global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __restrict__ w,
+                                          const int* __restrict__ sorted, const int* __restrict__ offsets,
+                                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                                          const int* __restrict__ num_tiles, const float* __restrict__ route_w,
+                                          T* __restrict__ out, int n_out, int k_dim, int top_k) {
+    if ((int)blockIdx.x >= num_tiles[0]) return;
+    const int e = tile_expert[blockIdx.x];
+    const int row0 = tile_row0[blockIdx.x];
+    const int row_end = offsets[e + 1];
+    const int n0 = blockIdx.y * kBN;
+    constexpr int NW = MODE == 0 ? 2 : 1;
+    __shared__ float as[kBK][kBM + 1];
+    __shared__ float ws[NW][kBK][kBN + 1];
+    __shared__ int src_row[kBM];
+    const int tid = threadIdx.x;
+    if (tid < kBM) {
+        const int p = row0 + tid;
+        src_row[tid] = p < row_end ? (MODE == 0 ? sorted[p] / top_k : p) : -1;
+    }
+    __syncthreads();
+    const size_t w_rows = (size_t)(MODE == 0 ? 2 * n_out : n_out);
+    const T* we = w + (size_t)e * w_rows * k_dim;
+    const int tm = (tid / 16) * 2, tn = (tid % 16) * 4;
+    float acc[NW][2][4] = {};
+    for (int k0 = 0; k0 < k_dim; k0 += kBK) {
+        for (int i = tid; i < kBM * kBK; i += 256) {
+            const int r = i / kBK, c = i % kBK;
+            const int sr = src_row[r];
+            as[c][r] = (sr >= 0 && k0 + c < k_dim) ? to_float(a[(size_t)sr * k_dim + k0 + c]) : 0.f;
+        }
+        for (int i = tid; i < kBN * kBK; i += 256) {
+            const int r = i / kBK, c = i % kBK;
+            const bool ok = n0 + r < n_out && k0 + c < k_dim;
+#pragma unroll
+            for (int h = 0; h < NW; ++h)
+                ws[h][c][r] = ok ? to_float(we[((size_t)h * n_out + n0 + r) * k_dim + k0 + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < kBK; ++c) {
+            float av[2], wv[NW][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) av[i] = as[c][tm + i];
+#pragma unroll
+            for (int h = 0; h < NW; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[h][j] = ws[h][c][tn + j];
+#pragma unroll
+            for (int h = 0; h < NW; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[h][i][j] = fmaf(av[i], wv[h][j], acc[h][i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int p = row0 + tm + i;
+        if (p >= row_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tn + j;
+            if (n >= n_out) continue;
+            float v;
+            if (MODE == 0) {
+                const float g = round_act<T>(acc[0][i][j]);
+                const float u = round_act<T>(acc[NW - 1][i][j]);
+                v = round_act<T>(g / (1.f + expf(-g))) * u;
+            } else {
+                v = acc[0][i][j] * route_w[sorted[p]];
+            }
+            out[(size_t)p * n_out + n] = from_float<T>(v);
+        }
+    }
+}
+
+// out[t, :] = cast(sum over slots (32-bit, slot order) of y[inv_pos[t * top_k + slot], :]).
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, T* __restrict__ out,
+                                   int hidden, int top_k) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
+        out[(size_t)t * hidden + i] = from_float<T>(s);
+    }
+}
+
+}  // namespace se
+
+extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, int tile_rows, int* counts, int* rank,
+                                  int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
+                                  int* num_tiles, cudaStream_t stream) {
+    if (assignments <= 0) return 0;
+    if (tile_rows <= 0 || experts <= 0) return SE_ERR_ARGUMENT;
+    se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
+    const int blocks = min(se::ceil_div(assignments, 256), 64);
+    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 1) * sizeof(int), stream>>>(
+        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_moe_plain_tile_rows() { return se::kBM; }
+
+// mode 0: gate/up + SwiGLU (a = x [tokens, k_dim], w = w13 [E, 2*n_out, k_dim]);
+// mode 1: down * routing weight (a = act [assignments, k_dim], w = w2 [E, n_out, k_dim]).
+extern "C" int se_moe_grouped_gemm_plain(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
+                                         const int* tile_expert, const int* tile_row0, const int* num_tiles,
+                                         const float* route_w, void* out, int max_tiles, int n_out, int k_dim,
+                                         int top_k, int dtype, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid(max_tiles, se::ceil_div(n_out, se::kBN));
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (mode == 0)
+            se::grouped_gemm_plain_kernel<T, 0><<<grid, 256, 0, stream>>>(
+                (const T*)a, (const T*)w, sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (T*)out, n_out,
+                k_dim, top_k);
+        else
+            se::grouped_gemm_plain_kernel<T, 1><<<grid, 256, 0, stream>>>(
+                (const T*)a, (const T*)w, sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (T*)out, n_out,
+                k_dim, top_k);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_moe_combine(const void* y, const int* inv_pos, void* out, int tokens, int hidden, int top_k,
+                              int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::moe_combine_kernel<T><<<tokens, 256, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
+    SE_LAUNCH_CHECK();
+}

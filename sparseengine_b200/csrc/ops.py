@@ -1,0 +1,194 @@
+"""Python bindings of the exported kernel launchers (ctypes, raw device pointers).
+
+Every launcher is ``extern "C" int se_<name>(..., cudaStream_t)``.  A binding checks
+device, dtype and contiguity of each tensor, passes ``data_ptr()`` and the current
+CUDA stream, and raises on a non-zero return.  There is no other implementation behind
+these functions: without the compiled library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_SIG = {"p": _P, "i": _I, "f": _F, "l": ctypes.c_longlong}
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {-2: "a size this kernel does not support", -3: "an inconsistent argument"}
+
+_fns: dict = {}
+
+
+def library():
+    return _build.load()
+
+
+def _fn(name: str, sig: str):
+    f = _fns.get(name)
+    if f is None:
+        f = getattr(library(), name)
+        f.restype = _I
+        f.argtypes = [_SIG[c] for c in sig]
+        _fns[name] = f
+    return f
+
+
+def _ptr(t: Optional[torch.Tensor], dtype=None, name: str = "tensor") -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise ValueError(f"{what}: {_ERRORS[code]}")
+    raise RuntimeError(f"{what}: CUDA error {code}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"activation dtype must be float32 or bfloat16, got {dtype}") from None
+
+
+# ---- elementwise -------------------------------------------------------------------------
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    tokens, hidden = out.shape
+    _check(_fn("se_embed_gather", "pppiiiip")(
+        _ptr(table, out.dtype, "table"), _ptr(ids, torch.int32, "ids"), _ptr(out), tokens, hidden,
+        table.shape[0], dtype_code(out.dtype), _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(x, w, eps: float, out, residual=None, residual_out=None):
+    """out = rmsnorm(x [+ residual]) * w; with a residual, residual_out = x + residual."""
+    rows, hidden = x.shape
+    if (residual is None) != (residual_out is None):
+        raise ValueError("residual and residual_out go together")
+    if w.shape != (hidden,):
+        raise ValueError(f"norm weight shape {tuple(w.shape)} does not match width {hidden}")
+    _check(_fn("se_rmsnorm", "pppppiifip")(
+        _ptr(x, None, "x"), _ptr(residual, x.dtype, "residual"), _ptr(w, x.dtype, "w"), _ptr(out, x.dtype, "out"),
+        _ptr(residual_out, x.dtype, "residual_out"), rows, hidden, float(eps), dtype_code(x.dtype), _stream()),
+        "rmsnorm")
+    return out
+
+
+def gather_rows(src, idx, out):
+    rows, width = out.shape
+    _check(_fn("se_gather_rows", "pppiiip")(
+        _ptr(src, out.dtype, "src"), _ptr(idx, torch.int32, "idx"), _ptr(out), rows, width,
+        dtype_code(out.dtype), _stream()), "gather_rows")
+    return out
+
+
+def table_update(table, updates, n: int):
+    _check(_fn("se_table_update", "pipip")(
+        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(updates, torch.int32, "updates"), n, _stream()),
+        "table_update")
+
+
+# ---- attention ---------------------------------------------------------------------------
+
+def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads,
+            num_kv_heads, head_dim, rotary_dim, eps, rope_scale, page_size, write_cache=True):
+    tokens = qkv.shape[0]
+    dt = qkv.dtype
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv width does not match the head counts")
+    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iiip")(
+        _ptr(qkv, None, "qkv"), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
+        _ptr(inv_freq, torch.float32, "inv_freq"), _ptr(positions, torch.int32, "positions"),
+        _ptr(token_seq, torch.int32, "token_seq"), _ptr(seq_rows, torch.int32, "seq_rows"),
+        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(cache, dt, "cache"), _ptr(q_out, dt, "q_out"),
+        tokens, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), float(rope_scale),
+        page_size, int(write_cache), dtype_code(dt), _stream()), "qk_prep")
+    return q_out
+
+
+def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads,
+                          head_dim, page_size, scale, window=None):
+    tokens = q.shape[0]
+    dt = q.dtype
+    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiii" "f" "iip")(
+        _ptr(q, None, "q"), _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
+        _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
+        _ptr(positions, torch.int32, "positions"), _ptr(out, dt, "out"), tokens, num_heads, num_kv_heads,
+        head_dim, page_size, float(scale), int(window or 0), dtype_code(dt), _stream()), "paged_attention_plain")
+    return out
+
+
+# ---- feed-forward ------------------------------------------------------------------------
+
+SCORE_FN = {"sigmoid": 0, "softmax": 1}
+
+
+def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
+           logits_out=None):
+    tokens, hidden = x.shape
+    experts = gate.shape[0]
+    if gate.shape != (experts, hidden):
+        raise ValueError("router weight shape does not match the activations")
+    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ip")(
+        _ptr(x, None, "x"), _ptr(gate, torch.float32, "gate"), _ptr(bias, torch.float32, "bias"),
+        _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"),
+        _ptr(logits_out, torch.float32, "logits_out"), tokens, hidden, experts, top_k, SCORE_FN[score_fn],
+        int(renormalize), float(routed_scale), dtype_code(x.dtype), _stream()), "router")
+    return ids, weights
+
+
+def moe_plain_tile_rows() -> int:
+    f = library().se_moe_plain_tile_rows
+    f.restype = _I
+    return int(f())
+
+
+def moe_route_build(ids, experts: int, tile_rows: int, ws: dict):
+    """ws: int32 tensors counts[E], rank[A], offsets[E+1], sorted[A], inv_pos[A],
+    tile_expert[max_tiles], tile_row0[max_tiles], num_tiles[1]."""
+    assignments = ids.numel()
+    _check(_fn("se_moe_route_build", "piii" "pppppppp" "p")(
+        _ptr(ids, torch.int32, "ids"), assignments, experts, tile_rows,
+        *[_ptr(ws[k], torch.int32, k) for k in ("counts", "rank", "offsets", "sorted", "inv_pos", "tile_expert",
+                                                 "tile_row0", "num_tiles")], _stream()), "moe_route_build")
+
+
+def moe_max_tiles(assignments: int, experts: int, tile_rows: int) -> int:
+    return -(-assignments // tile_rows) + min(experts, assignments)
+
+
+def moe_grouped_gemm_plain(mode: int, a, w, ws: dict, route_w, out, *, max_tiles, n_out, k_dim, top_k):
+    dt = a.dtype
+    _check(_fn("se_moe_grouped_gemm_plain", "i" "ppppppppp" "iiii" "ip")(
+        mode, _ptr(a, None, "a"), _ptr(w, dt, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
+        _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
+        _ptr(route_w, torch.float32, "route_w"), _ptr(out, dt, "out"), max_tiles, n_out, k_dim, top_k,
+        dtype_code(dt), _stream()), "moe_grouped_gemm_plain")
+    return out
+
+
+def moe_combine(y, inv_pos, out, top_k: int):
+    tokens, hidden = out.shape
+    _check(_fn("se_moe_combine", "pppiiiip")(
+        _ptr(y, out.dtype, "y"), _ptr(inv_pos, torch.int32, "inv_pos"), _ptr(out), tokens, hidden, top_k,
+        dtype_code(out.dtype), _stream()), "moe_combine")
+    return out

@@ -1,0 +1,172 @@
+"""The step function: one batch of (request, its next tokens) → logits at the wanted
+places.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere.  Only
+the tokens given are run; everything earlier comes from the cache.  Sampling is not
+done here.  The reference's runner takes either prompt chunks or decode tokens per step
+and samples inside (src/sparseengine/engine/model_runner.py:2572-2660; inputs built in
+src/sparseengine/engine/cache_manager/standard.py:2065-2206); this one takes any mix and
+returns logits.
+
+Per step: reserve pages (all or nothing) → pack the step's metadata into one pinned
+int32 buffer → one host-to-device copy → apply block-table updates → model forward →
+commit the tokens to the cache manager.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..csrc import ops
+from ..parts.base import StepContext
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens in this step and the places (indices into ``tokens``)
+    whose logits are wanted."""
+    seq_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class _Staging:
+    """A small ring of pinned host buffers, each guarded by an event so that a buffer is
+    not rewritten while its copy may still be in flight."""
+
+    def __init__(self, depth: int = 4):
+        self.depth = depth
+        self.bufs = [None] * depth
+        self.events = [None] * depth
+        self.i = 0
+
+    def get(self, n: int):
+        i = self.i
+        self.i = (i + 1) % self.depth
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < n:
+            self.bufs[i] = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
+        return i, self.bufs[i]
+
+    def mark(self, i: int):
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, device="cuda:0"):
+        self.model = model
+        self.cache = cache
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        self.slots = [cache.slot_for(e) for e in model.layout.entries]
+        self._staging = _Staging()
+        self.steps = 0
+        self.tokens = 0
+
+    # ---- life cycle of a request -------------------------------------------------------
+    def admit(self, seq_id) -> None:
+        self.cache.admit(seq_id)
+
+    def release(self, seq_id) -> None:
+        self.cache.release(seq_id)
+
+    # ---- the step ------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns logits ``[wanted, vocab]`` (activation dtype) in the
+        order of the entries and of each entry's ``want``, or ``None`` if nothing is wanted.
+
+        Raises :class:`OutOfPages` (and changes nothing) if the pages do not suffice."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        vocab = self.model.spec.vocab_size
+        seen = set()
+        for e in entries:
+            if e.seq_id in seen:
+                raise ValueError(f"request {e.seq_id!r} appears twice in one step")
+            seen.add(e.seq_id)
+            if not self.cache.has(e.seq_id):
+                raise ValueError(f"request {e.seq_id!r} was not admitted")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise ValueError(f"request {e.seq_id!r}: token id outside [0, {vocab})")
+            if any(not 0 <= w < len(e.tokens) for w in e.want):
+                raise ValueError(f"request {e.seq_id!r}: wanted place outside its tokens")
+        done = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.seq_id, len(e.tokens))
+                done.append(e.seq_id)
+        except (OutOfPages, ValueError):
+            for s in done:
+                self.cache.cancel(s)
+            raise
+
+        step, want_rows, updates = self._pack(entries)
+        with torch.cuda.device(self.device):
+            for g, (upd, n) in zip(self.cache.groups, updates):
+                if n:
+                    ops.table_update(g.table, upd, n)
+            logits = self.model.forward(step, self.slots, want_rows)
+        for e in entries:
+            self.cache.commit(e.seq_id, len(e.tokens))
+        self.steps += 1
+        self.tokens += step.num_tokens
+        return logits
+
+    def _pack(self, entries):
+        n = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        t = sum(q_lens)
+        q_starts = [self.cache.length(e.seq_id) for e in entries]
+        rows = [self.cache.row(e.seq_id) for e in entries]
+        kv_lens = [s + q for s, q in zip(q_starts, q_lens)]
+        want = []
+        base = 0
+        for e, q in zip(entries, q_lens):
+            want.extend(base + w for w in e.want)
+            base += q
+        upd = [self.cache.drain_updates(g) for g in range(len(self.cache.groups))]
+
+        # layout of the packed buffer (all int32)
+        sizes = [t, t, t, n, n + 1, n, len(want)] + [3 * len(u) for u in upd]
+        offs = np.concatenate(([0], np.cumsum([-(-s // 4) * 4 for s in sizes]))).astype(np.int64)
+        total = int(offs[-1])
+        slot, host = self._staging.get(total)
+        h = host.numpy()
+        tok = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        h[offs[0]:offs[0] + t] = tok
+        h[offs[1]:offs[1] + t] = np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(q_starts, q_lens)])
+        h[offs[2]:offs[2] + t] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+        h[offs[3]:offs[3] + n] = rows
+        h[offs[4]:offs[4] + n + 1] = np.concatenate(([0], np.cumsum(q_lens))).astype(np.int32)
+        h[offs[5]:offs[5] + n] = kv_lens
+        if want:
+            h[offs[6]:offs[6] + len(want)] = want
+        for i, u in enumerate(upd):
+            if u:
+                h[offs[7 + i]:offs[7 + i] + 3 * len(u)] = np.asarray(u, dtype=np.int32).reshape(-1)
+        with torch.cuda.device(self.device):
+            dev = torch.empty(total, dtype=torch.int32, device=self.device)
+            dev.copy_(host[:total], non_blocking=True)
+            self._staging.mark(slot)
+
+        def view(i, length):
+            return dev[int(offs[i]):int(offs[i]) + length]
+
+        step = StepContext(
+            num_tokens=t, num_seqs=n, token_ids=view(0, t), positions=view(1, t), token_seq=view(2, t),
+            seq_rows=view(3, n), cu_q=view(4, n + 1), kv_len=view(5, n), q_lens=q_lens, q_starts=q_starts,
+            kv_lens=kv_lens, rows=rows, dtype=self.model.dtype)
+        want_rows = view(6, len(want)) if want else None
+        updates = [(view(7 + i, 3 * len(u)), len(u)) for i, u in enumerate(upd)]
+        return step, want_rows, updates

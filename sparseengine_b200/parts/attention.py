@@ -1,0 +1,65 @@
+"""Grouped-query attention over the paged cache.
+
+qkv projection → (optional) whole-projection QK RMSNorm → position encoding → K/V into
+their page → attention over the request's pages → output projection.  Order of effects
+as in the reference (src/sparseengine/models/minimax_m2.py:334-359): this step's keys are
+written before attention reads the cache.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import ParamSpec
+from ..csrc import ops
+from .base import KVRequest, Mixer, make_position, register_mixer
+from .linear import linear
+
+
+class PagedAttention(Mixer):
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if s.head_dim % 16 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to 256)")
+        if s.qk_norm not in (None, "whole_projection"):
+            raise ValueError(f"qk_norm {s.qk_norm!r} is not supported")
+        self.position = make_position(s.position, dtype) if s.position is not None else None
+        self.q_norm = self.k_norm = None
+
+    def parameters(self):
+        s = self.spec
+        q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        out = {"qkv": ParamSpec((q + 2 * kv, s.hidden_size)), "o": ParamSpec((s.hidden_size, q))}
+        if s.qk_norm is not None:
+            out["q_norm"] = ParamSpec((q,), "act", "norm")
+            out["k_norm"] = ParamSpec((kv,), "act", "norm")
+        return out
+
+    def kv_request(self):
+        return KVRequest(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def forward(self, x, step, slot):
+        s = self.spec
+        tokens = x.shape[0]
+        qkv = linear(x, self.qkv)
+        q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
+        inv_freq, rot, rope_scale = (self.position.kernel_args(x.device) if self.position is not None
+                                     else (None, 0, 1.0))
+        ops.qk_prep(qkv, self.q_norm, self.k_norm, inv_freq, step.positions, step.token_seq, step.seq_rows,
+                    slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
+                    head_dim=s.head_dim, rotary_dim=rot, eps=s.qk_norm_eps, rope_scale=rope_scale,
+                    page_size=slot.page_size, write_cache=slot.write_cache)
+        attn = torch.empty_like(q)
+        self.attend(q, attn, step, slot)
+        return linear(attn, self.o)
+
+    def attend(self, q, out, step, slot):
+        s = self.spec
+        ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
+                                  num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+                                  page_size=slot.page_size, scale=s.scale, window=s.window)
+
+
+register_mixer("attention", PagedAttention)

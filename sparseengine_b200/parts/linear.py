@@ -1,0 +1,26 @@
+"""Dense projections ``y = x · Wᵀ`` (no bias), 32-bit accumulation.
+
+The reference runs these through a library GEMM (``F.linear``:
+src/sparseengine/layers/linear.py:174-191, src/sparseengine/layers/embed_head.py:80), and so
+does this module (cuBLAS through ``torch.matmul``).  In float32 the reduced-precision
+matrix modes are switched off for the whole process, so a float32 product is a true
+32-bit product.
+"""
+from __future__ import annotations
+
+import torch
+
+torch.backends.cuda.matmul.allow_tf32 = False
+torch.backends.cudnn.allow_tf32 = False
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [rows, in], w [out, in] → [rows, out]; CUDA tensors of one dtype only."""
+    if not (x.is_cuda and w.is_cuda):
+        raise ValueError("linear needs CUDA tensors (there is no CPU path)")
+    if x.dtype != w.dtype:
+        raise TypeError(f"linear: activation {x.dtype} and weight {w.dtype} differ")
+    if out is None:
+        return torch.matmul(x, w.t())
+    return torch.matmul(x, w.t(), out=out)

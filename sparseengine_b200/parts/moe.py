@@ -1,0 +1,107 @@
+"""Feed-forward parts: routed SwiGLU experts and the dense SwiGLU MLP.
+
+Router (32-bit) → routing build (rows sorted by expert) → grouped gate/up GEMM with the
+SwiGLU epilogue → grouped down GEMM times the routing weight → sum over the top-k slots
+in slot order.  Reference: src/sparseengine/models/minimax_m2.py:140-269,
+src/sparseengine/layers/packed_moe.py:138-155 (w13 = gate rows then up rows).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import ParamSpec
+from ..csrc import ops
+from .base import FeedForward, register_feed_forward
+
+
+class _RoutedSwiGLU(FeedForward):
+    """Shared machinery: given ids [T, k] int32 and weights [T, k] float32, run experts."""
+
+    num_experts: int
+    top_k: int
+    hidden: int
+    inter: int
+
+    def run_experts(self, x, ids, weights):
+        tokens = x.shape[0]
+        a = tokens * self.top_k
+        dev = x.device
+        tile_rows = ops.moe_plain_tile_rows()
+        max_tiles = ops.moe_max_tiles(a, self.num_experts, tile_rows)
+        i32 = dict(dtype=torch.int32, device=dev)
+        ws = {"counts": torch.empty(self.num_experts, **i32), "rank": torch.empty(a, **i32),
+              "offsets": torch.empty(self.num_experts + 1, **i32), "sorted": torch.empty(a, **i32),
+              "inv_pos": torch.empty(a, **i32), "tile_expert": torch.empty(max_tiles, **i32),
+              "tile_row0": torch.empty(max_tiles, **i32), "num_tiles": torch.empty(1, **i32)}
+        ops.moe_route_build(ids, self.num_experts, tile_rows, ws)
+        act = torch.empty(a, self.inter, dtype=x.dtype, device=dev)
+        ops.moe_grouped_gemm_plain(0, x, self.w13, ws, None, act, max_tiles=max_tiles, n_out=self.inter,
+                                   k_dim=self.hidden, top_k=self.top_k)
+        y = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
+        ops.moe_grouped_gemm_plain(1, act, self.w2, ws, weights, y, max_tiles=max_tiles, n_out=self.hidden,
+                                   k_dim=self.inter, top_k=self.top_k)
+        out = torch.empty(tokens, self.hidden, dtype=x.dtype, device=dev)
+        ops.moe_combine(y, ws["inv_pos"], out, self.top_k)
+        return out
+
+
+class SparseMoE(_RoutedSwiGLU):
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        if spec.activation != "silu":
+            raise ValueError(f"activation {spec.activation!r} is not supported (only 'silu')")
+        if spec.score_fn not in ops.SCORE_FN:
+            raise ValueError(f"score function {spec.score_fn!r} is not supported")
+        if not 0 < spec.top_k <= spec.num_experts:
+            raise ValueError("top_k must be in [1, num_experts]")
+        self.num_experts, self.top_k = spec.num_experts, spec.top_k
+        self.hidden, self.inter = spec.hidden_size, spec.intermediate_size
+        self.selection_bias = None
+
+    def parameters(self):
+        s = self.spec
+        out = {"gate": ParamSpec((s.num_experts, s.hidden_size), "float32"),
+               "w13": ParamSpec((s.num_experts, 2 * s.intermediate_size, s.hidden_size)),
+               "w2": ParamSpec((s.num_experts, s.hidden_size, s.intermediate_size))}
+        if s.selection_bias:
+            out["selection_bias"] = ParamSpec((s.num_experts,), "float32", "bias")
+        return out
+
+    def route(self, x):
+        tokens = x.shape[0]
+        ids = torch.empty(tokens, self.top_k, dtype=torch.int32, device=x.device)
+        weights = torch.empty(tokens, self.top_k, dtype=torch.float32, device=x.device)
+        s = self.spec
+        ops.router(x, self.gate, self.selection_bias, ids, weights, top_k=self.top_k, score_fn=s.score_fn,
+                   renormalize=s.renormalize, routed_scale=s.routed_scale)
+        return ids, weights
+
+    def forward(self, x, step):
+        ids, weights = self.route(x)
+        return self.run_experts(x, ids, weights)
+
+
+class DenseMLP(_RoutedSwiGLU):
+    """SwiGLU MLP = one expert every token selects with weight 1."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        if spec.activation != "silu":
+            raise ValueError(f"activation {spec.activation!r} is not supported (only 'silu')")
+        self.num_experts, self.top_k = 1, 1
+        self.hidden, self.inter = spec.hidden_size, spec.intermediate_size
+
+    def parameters(self):
+        s = self.spec
+        return {"w13": ParamSpec((1, 2 * s.intermediate_size, s.hidden_size)),
+                "w2": ParamSpec((1, s.hidden_size, s.intermediate_size))}
+
+    def forward(self, x, step):
+        tokens = x.shape[0]
+        ids = torch.zeros(tokens, 1, dtype=torch.int32, device=x.device)
+        weights = torch.ones(tokens, 1, dtype=torch.float32, device=x.device)
+        return self.run_experts(x, ids, weights)
+
+
+register_feed_forward("moe", SparseMoE)
+register_feed_forward("dense_mlp", DenseMLP)

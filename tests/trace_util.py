@@ -1,0 +1,216 @@
+"""Helpers shared by the replay tests: tiny model folders, traces in the four ways of
+cutting, and the comparison with the plain implementation."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import torch
+
+import plain_m2
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# name -> (config.json dict, seed, std, norm_std, bias_std, page size)
+TINY = {
+    "A": (plain_m2.TINY_A, 0, 0.02, 0.05, 0.0, 4),
+    "B": (plain_m2.TINY_B, 1, 0.03, 0.0, 0.1, 8),
+    "C": (plain_m2.TINY_C, 2, 0.05, 0.1, 0.05, 16),
+}
+
+
+def make_model_folder(folder: str, name: str, dtype: str = "float32") -> dict:
+    """Write config.json + model.safetensors with the plain implementation's own random
+    weights (so the engine's loader is tested against foreign tensors)."""
+    from safetensors.torch import save_file
+    cfg, seed, std, norm_std, bias_std, _ = TINY[name]
+    tensors = plain_m2.random_tensors(cfg, seed, std, norm_std, bias_std)
+    if dtype == "bfloat16":
+        tensors = {k: (v if k.endswith(("gate.weight", "e_score_correction_bias")) else v.to(torch.bfloat16))
+                   for k, v in tensors.items()}
+    os.makedirs(folder, exist_ok=True)
+    c = dict(cfg)
+    c["torch_dtype"] = dtype
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(c, f)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    return tensors
+
+
+def random_prompt(vocab: int, length: int, seed: int) -> list:
+    g = torch.Generator().manual_seed(1000 + seed)
+    return torch.randint(0, vocab, (length,), generator=g).tolist()
+
+
+# ---- traces: lists of steps {"step", "entries", "end"} ---------------------------------
+
+def trace_whole(seqs: dict) -> list:
+    steps = []
+    for i, (sid, toks) in enumerate(seqs.items()):
+        steps.append({"step": i, "entries": [{"id": sid, "tokens": toks, "want": list(range(len(toks)))}],
+                      "end": [sid]})
+    return steps
+
+
+def trace_tail_decode(seqs: dict, tail: int = 32) -> list:
+    steps = []
+    n = 0
+    for sid, toks in seqs.items():
+        head = max(1, len(toks) - tail)
+        cuts = [(0, head)] + [(i, i + 1) for i in range(head, len(toks))]
+        for a, b in cuts:
+            steps.append({"step": n, "entries": [{"id": sid, "tokens": toks[a:b], "want": list(range(b - a))}],
+                          "end": [sid] if b == len(toks) else []})
+            n += 1
+    return steps
+
+
+def trace_chunks(seqs: dict, sizes=(7, 2, 5, 3, 2, 11, 4, 2, 9)) -> list:
+    steps = []
+    n = 0
+    for sid, toks in seqs.items():
+        a, k = 0, 0
+        while a < len(toks):
+            b = min(len(toks), a + sizes[k % len(sizes)])
+            if len(toks) - b == 1:      # never leave a single last token: portions go down to two
+                b = len(toks)
+            steps.append({"step": n, "entries": [{"id": sid, "tokens": toks[a:b], "want": list(range(b - a))}],
+                          "end": [sid] if b == len(toks) else []})
+            n += 1
+            a, k = b, k + 1
+    return steps
+
+
+def trace_mixed(seqs: dict, live: int = 4, chunk: int = 6, decode_tail: int = 5, seed: int = 0) -> list:
+    """Up to ``live`` requests at a time: each is fed in chunks of ``chunk`` tokens until
+    ``decode_tail`` tokens are left, which then go one per step; portions of some requests
+    sit beside single tokens of others; a request is sometimes left out of a step; ended
+    requests make room (and free pages) for waiting ones."""
+    rng = np.random.RandomState(seed)
+    waiting = list(seqs.items())
+    active: dict = {}
+    steps = []
+    n = 0
+    while waiting or active:
+        while waiting and len(active) < live:
+            sid, toks = waiting.pop(0)
+            active[sid] = [toks, 0]
+        entries, end = [], []
+        ids = list(active)
+        for sid in ids:
+            toks, a = active[sid]
+            if len(ids) > 1 and rng.rand() < 0.2:
+                continue                      # left out of this step, goes on later
+            left = len(toks) - a
+            if left > decode_tail:
+                b = a + min(chunk, left - decode_tail)
+                if b - a == 1 and left - decode_tail == 1:
+                    b = a + 1
+            else:
+                b = a + 1
+            entries.append({"id": sid, "tokens": toks[a:b], "want": list(range(b - a))})
+            active[sid][1] = b
+            if b == len(toks):
+                end.append(sid)
+        for sid in end:
+            del active[sid]
+        if entries:
+            steps.append({"step": n, "entries": entries, "end": end})
+            n += 1
+    return steps
+
+
+def max_live_tokens(steps, round_to: int = 64) -> int:
+    """The --max-tokens a trace needs: the most tokens live requests hold at any time,
+    each request's count rounded up to ``round_to``."""
+    held: dict = {}
+    worst = 0
+    for s in steps:
+        for e in s["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        worst = max(worst, sum(-(-v // round_to) * round_to for v in held.values()))
+        for sid in s["end"]:
+            held.pop(sid, None)
+    return worst
+
+
+# ---- running a trace -------------------------------------------------------------------
+
+def run_trace_cli(model_dir: str, dtype: str, steps: list, out_dir: str, max_tokens: int, extra=()) -> dict:
+    """Run bin/trace_run as a subprocess; returns {(id, position): logits row}."""
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens), *extra]
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    try:
+        for s in steps:
+            proc.stdin.write(json.dumps(s) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline().strip()
+            assert line == f"done {s['step']}", f"expected 'done {s['step']}', got {line!r}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    return collect(steps, out_dir)
+
+
+def collect(steps: list, out_dir: str, vocab: int | None = None) -> dict:
+    out = {}
+    pos: dict = {}
+    for s in steps:
+        wanted = [(e["id"], pos.get(e["id"], 0) + w) for e in s["entries"] for w in e["want"]]
+        for e in s["entries"]:
+            pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+        for sid in s["end"]:
+            pos.pop(sid, None)
+        if not wanted:
+            continue
+        arr = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4")
+        arr = arr.reshape(len(wanted), -1)
+        for key, row in zip(wanted, arr):
+            out[key] = row
+    return out
+
+
+def run_trace_runner(runner, steps: list) -> dict:
+    """Run a trace in-process on a ModelRunner; returns {(id, position): logits row}."""
+    from sparseengine_b200.engine.runner import StepEntry
+    out = {}
+    pos: dict = {}
+    for s in steps:
+        entries = []
+        for e in s["entries"]:
+            if not runner.cache.has(e["id"]):
+                runner.admit(e["id"])
+            entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
+        logits = runner.step(entries)
+        wanted = [(e["id"], pos.get(e["id"], 0) + w) for e in s["entries"] for w in e["want"]]
+        for e in s["entries"]:
+            pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+        if wanted:
+            arr = logits.float().cpu().numpy()
+            for key, row in zip(wanted, arr):
+                out[key] = row
+        for sid in s["end"]:
+            runner.release(sid)
+            pos.pop(sid, None)
+    return out
+
+
+def compare(got: dict, ref: dict, atol: float, rtol: float, what: str = ""):
+    """ref: {id: [T, V] array}.  Reports the first wrong token."""
+    worst = 0.0
+    for (sid, p), row in sorted(got.items(), key=lambda kv: (str(kv[0][0]), kv[0][1])):
+        want = ref[sid][p]
+        err = np.abs(row - want)
+        lim = atol + rtol * np.abs(want)
+        if not (err <= lim).all():
+            j = int(np.argmax(err - lim))
+            raise AssertionError(f"{what}: request {sid!r} position {p}: logit {j} is {row[j]!r}, "
+                                 f"plain gives {want[j]!r} (|diff| {err[j]:.3e} > {lim[j]:.3e})")
+        worst = max(worst, float(err.max()))
+    return worst
