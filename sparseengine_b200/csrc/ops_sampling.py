@@ -1,0 +1,31 @@
+"""Bindings of the sampling kernels (csrc/sampling.cu)."""
+from __future__ import annotations
+
+import torch
+
+from .ops import _check, _fn, _ptr, _stream, dtype_code
+
+
+def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None):
+    rows, vocab = logits.shape
+    _check(_fn("se_sample", "ppppppp" "iii" "p")(
+        _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
+        _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),
+        _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"), rows, vocab,
+        dtype_code(logits.dtype), _stream()), "sample")
+    return out
+
+
+def apply_penalties(logits, pairs, n, repetition, presence):
+    rows, vocab = logits.shape
+    _check(_fn("se_apply_penalties", "ppiippp")(
+        _ptr(logits, torch.float32, "logits"), _ptr(pairs, torch.int32, "pairs"), n, vocab,
+        _ptr(repetition, torch.float32, "repetition"), _ptr(presence, torch.float32, "presence"), _stream()),
+        "apply_penalties")
+
+
+def to_float(src, dst):
+    _check(_fn("se_to_float", "pplip")(
+        _ptr(src, None, "src"), _ptr(dst, torch.float32, "dst"), src.numel(), dtype_code(src.dtype), _stream()),
+        "to_float")
+    return dst

@@ -1,0 +1,212 @@
+// Sampling over the vocabulary, one block per row: greedy argmax, temperature, top-k,
+// top-p, and the presence / repetition penalties.
+//
+// Reference semantics (src/sparseengine/layers/sampler.py:66-135): rows with temperature
+// <= 1e-10 take argmax of the unscaled logits; others take p = softmax(logits / T) in
+// 32-bit, keep the top-k (0 = all), then keep the smallest prefix of the sorted
+// probabilities whose mass before each kept entry does not exceed top-p (the first is
+// always kept), and draw by the exponential race argmax(p_i / e_i), e_i ~ Exp(1) clamped
+// at 1e-10.  Here the two cuts are found without sorting, by bisection on the value of
+// the threshold (entries that tie with the k-th value are all kept), and the noise
+// comes from a counter-based generator (Philox 4x32-10) keyed by the row's own seed, so
+// a request's draw does not depend on what else is in the batch.
+// Penalties (src/sparseengine/layers/sampler.py:10-64): repetition divides positive logits
+// and multiplies negative ones; presence subtracts.
+#include "common.cuh"
+
+namespace se {
+
+constexpr int kSampleThreads = 1024;
+
+__device__ __forceinline__ uint32_t ordered_key(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                              uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+struct ArgMax {
+    float v;
+    int i;
+};
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    // larger value wins; NaN counts as larger than anything; ties go to the lower index
+    const bool a_nan = a.v != a.v, b_nan = b.v != b.v;
+    if (a.i < 0) return b;
+    if (b.i < 0) return a;
+    if (a_nan || b_nan) {
+        if (a_nan && b_nan) return a.i < b.i ? a : b;
+        return a_nan ? a : b;
+    }
+    if (a.v > b.v) return a;
+    if (b.v > a.v) return b;
+    return a.i < b.i ? a : b;
+}
+
+__device__ ArgMax block_argmax(ArgMax x, ArgMax* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax y;
+        y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+        x = better(x, y);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        ArgMax t = lane < nwarps ? scratch[lane] : ArgMax{0.f, -1};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax y;
+            y.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            y.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, y);
+        }
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+template <typename T>
+__global__ void sample_kernel(const T* __restrict__ logits, const float* __restrict__ temperature,
+                              const int* __restrict__ top_k, const float* __restrict__ top_p,
+                              const unsigned long long* __restrict__ seeds, int* __restrict__ out,
+                              float* __restrict__ logprob, int vocab) {
+    __shared__ ArgMax am[33];
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const T* x = logits + (size_t)row * vocab;
+    const float temp = temperature ? temperature[row] : 0.f;
+    const bool greedy = temp <= 1e-10f;
+
+    // pass 1: argmax of the raw logits (also the maximum for the softmax)
+    ArgMax best{0.f, -1};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = better(best, ArgMax{to_float(x[i]), i});
+    best = block_argmax(best, am);
+    const float inv_t = greedy ? 1.f : 1.f / temp;
+    const float mx = best.v * inv_t;
+
+    int k = top_k ? top_k[row] : 0;
+    float p_cut = top_p ? top_p[row] : 1.f;
+    uint32_t thr = 0;   // keep entries with ordered_key(scaled) >= thr
+    if (!greedy && k > 0 && k < vocab) {
+        uint32_t prefix = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t cand = prefix | (1u << bit);
+            float cnt = 0.f;
+            for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+                cnt += ordered_key(to_float(x[i]) * inv_t) >= cand ? 1.f : 0.f;
+            cnt = block_sum(cnt, red);
+            if (cnt >= (float)k) prefix = cand;
+        }
+        thr = prefix;
+    }
+    float z = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float s = to_float(x[i]) * inv_t;
+        if (ordered_key(s) >= thr) z += expf(s - mx);
+    }
+    z = block_sum(z, red);
+    if (logprob != nullptr && greedy && threadIdx.x == 0) {
+        // log-probability of the chosen token under the unscaled distribution
+        logprob[row] = -logf(z);
+    }
+    if (greedy) {
+        if (threadIdx.x == 0) out[row] = best.i;
+        return;
+    }
+    if (p_cut < 1.f) {
+        uint32_t prefix = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t cand = prefix | (1u << bit);
+            float mass = 0.f;
+            for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+                const float s = to_float(x[i]) * inv_t;
+                const uint32_t key = ordered_key(s);
+                if (key >= cand && key >= thr) mass += expf(s - mx);
+            }
+            mass = block_sum(mass, red);
+            if (mass / z > p_cut) prefix = cand;
+        }
+        thr = max(thr, prefix);
+    }
+    const unsigned long long seed = seeds[row];
+    ArgMax pick{0.f, -1};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float s = to_float(x[i]) * inv_t;
+        if (ordered_key(s) < thr) continue;
+        uint32_t r[4];
+        philox4x32_10((uint32_t)(i >> 2), 0u, 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), r);
+        const float u = ((float)r[i & 3] + 0.5f) * 2.3283064365386963e-10f;   // (0, 1)
+        const float e = fmaxf(-logf(u), 1e-10f);
+        pick = better(pick, ArgMax{expf(s - mx) / e, i});
+    }
+    pick = block_argmax(pick, am);
+    if (threadIdx.x == 0) {
+        out[row] = pick.i;
+        if (logprob != nullptr) logprob[row] = to_float(x[pick.i]) * inv_t - mx - logf(z);
+    }
+}
+
+// pairs: n entries (row, token, flags); flags bit 0 = in prompt or completion (repetition),
+// bit 1 = in completion (presence).  logits is float32 [rows, vocab], changed in place.
+__global__ void penalties_kernel(float* logits, const int* __restrict__ pairs, int n, int vocab,
+                                 const float* __restrict__ repetition, const float* __restrict__ presence) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int row = pairs[3 * i], tok = pairs[3 * i + 1], flags = pairs[3 * i + 2];
+    if (tok < 0 || tok >= vocab) return;
+    float v = logits[(size_t)row * vocab + tok];
+    const float r = repetition[row], p = presence[row];
+    if ((flags & 1) && r != 1.f) v = v > 0.f ? v / r : v * r;
+    if ((flags & 2) && p != 0.f) v -= p;
+    logits[(size_t)row * vocab + tok] = v;
+}
+
+template <typename T>
+__global__ void to_float_kernel(const T* __restrict__ src, float* __restrict__ dst, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = to_float(src[i]);
+}
+
+}  // namespace se
+
+// temperature/top_k/top_p/seeds may be null (then every row is greedy).
+extern "C" int se_sample(const void* logits, const float* temperature, const int* top_k, const float* top_p,
+                         const unsigned long long* seeds, int* out, float* logprob, int rows, int vocab, int dtype,
+                         cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (temperature != nullptr && seeds == nullptr) return SE_ERR_ARGUMENT;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::sample_kernel<T><<<rows, se::kSampleThreads, 0, stream>>>((const T*)logits, temperature, top_k, top_p,
+                                                                      seeds, out, logprob, vocab));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_apply_penalties(float* logits, const int* pairs, int n, int vocab, const float* repetition,
+                                  const float* presence, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    se::penalties_kernel<<<se::ceil_div(n, 256), 256, 0, stream>>>(logits, pairs, n, vocab, repetition, presence);
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_to_float(const void* src, float* dst, long long n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 1023) / 1024 < 4096 ? (n + 1023) / 1024 : 4096);
+    SE_DISPATCH_DTYPE(dtype, T, se::to_float_kernel<T><<<blocks, 256, 0, stream>>>((const T*)src, dst, (size_t)n));
+    SE_LAUNCH_CHECK();
+}

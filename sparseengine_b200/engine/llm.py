@@ -1,0 +1,200 @@
+"""The Python entry point, in the reference's manner
+(src/sparseengine/llm.py:1-5, src/sparseengine/engine/llm_engine.py:232-348,872-1018,1754-2055):
+
+    llm = LLM(model_folder, max_num_batched_tokens=8192, dtype="bfloat16", ...)
+    outs = llm.generate([[1, 2, 3], "a string needs a tokenizer"], SamplingParams(temperature=0))
+    outs[0]["token_ids"], outs[0]["text"]
+
+``LLM(model, **options)`` takes the fields of :class:`Config` and refuses unknown names.
+``generate`` returns ``[{"text", "token_ids"}]`` in the order of the prompts; ``add_request``
+/ ``step`` / ``is_finished`` drive the engine by hand; ``step`` returns
+``(finished outputs, num_tokens)`` with ``num_tokens > 0`` the prompt tokens of the step,
+or ``-n`` for a step of ``n`` decoded tokens only.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from typing import Optional, Sequence as Seq
+
+import torch
+
+from ..config.engine_config import Config
+from ..config.registry import read_config_json
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import SampleRequest, Sampler
+from .factory import build_runner, require_cuda, resolve_dtype
+from .runner import StepEntry
+from .scheduler import Scheduler
+from .sequence import Sequence
+
+
+def _eos_from_folder(model_dir: str, raw: dict) -> tuple:
+    """EOS ids from generation_config.json, else config.json
+    (src/sparseengine/engine/llm_engine.py:206-222)."""
+    for name in ("generation_config.json",):
+        path = os.path.join(model_dir, name)
+        if os.path.isfile(path):
+            with open(path) as f:
+                v = json.load(f).get("eos_token_id")
+            if v is not None:
+                return tuple(v) if isinstance(v, list) else (int(v),)
+    v = raw.get("eos_token_id")
+    if v is None:
+        return ()
+    return tuple(v) if isinstance(v, list) else (int(v),)
+
+
+class LLM:
+    def __init__(self, model, **options):
+        self.config = Config.from_kwargs(model, **options)
+        cfg = self.config
+        device = require_cuda(cfg.device)
+        from ..csrc import ops
+        ops.library()       # compile/load the kernels now; there is no other path
+        raw = model if isinstance(model, dict) else read_config_json(model)
+        self._raw = raw
+        dt = resolve_dtype(cfg.dtype)
+        from ..config.registry import load_model_spec
+        _, spec = load_model_spec(raw)
+        self.max_model_len = min(cfg.max_model_len or spec.max_position, spec.max_position)
+
+        # weights first, then size the cache from what is left
+        from ..weights.loader import load_weights
+        from ..weights.random_init import init_random_
+        from .model import Model
+        from ..cache.manager import CacheManager
+        from .runner import ModelRunner
+        m = Model(spec, dt)
+        with torch.cuda.device(device):
+            if cfg.tiny_random or isinstance(model, dict):
+                init_random_(m, cfg.tiny_random_seed, device)
+            else:
+                load_weights(m, model, device)
+            num_pages = self._num_pages(m, dt, device)
+            cache = CacheManager(m.layout, page_size=cfg.page_size, num_pages=num_pages,
+                                 max_rows=cfg.max_num_seqs_in_gpu, max_seq_len=self.max_model_len,
+                                 dtype=dt, device=device)
+        self.runner = ModelRunner(m, cache, device)
+        eos = tuple(cfg.eos_token_ids) or ((cfg.eos,) if cfg.eos >= 0 else ())
+        if not eos and not isinstance(model, dict):
+            eos = _eos_from_folder(model, raw)
+        self.scheduler = Scheduler(cfg, cache, eos_token_ids=eos, max_model_len=self.max_model_len)
+        self.sampler = Sampler(cfg.seed)
+        self._next_id = 0
+        self._tokenizer = None
+        self._tokenizer_tried = False
+
+    # ---- sizing ------------------------------------------------------------------------
+    def _num_pages(self, model, dt, device) -> int:
+        cfg = self.config
+        if cfg.num_kvcache_slots and cfg.num_kvcache_slots > 0:
+            return max(1, -(-int(cfg.num_kvcache_slots) // cfg.page_size))
+        item = torch.empty((), dtype=dt).element_size()
+        per_page = 0
+        for req, layers in model.layout.groups:
+            per_page = max(per_page, layers * 2 * req.num_kv_heads * cfg.page_size * req.head_dim * item)
+        total_per_page = sum(layers * 2 * req.num_kv_heads * cfg.page_size * req.head_dim * item
+                             for req, layers in model.layout.groups) or 1
+        free, total = torch.cuda.mem_get_info(device)
+        spec = model.spec
+        workspace = cfg.max_num_batched_tokens * spec.hidden_size * item * 64 + (1 << 30)
+        usable = int(total * cfg.gpu_memory_utilization) - (total - free) - workspace
+        pages = usable // total_per_page
+        cap = cfg.max_num_seqs_in_gpu * (-(-self.max_model_len // cfg.page_size))
+        pages = min(pages, cap)
+        if pages * cfg.page_size < min(self.max_model_len, 64):
+            raise RuntimeError("not enough GPU memory left for a key/value cache")
+        return int(pages)
+
+    # ---- tokenizer (optional) ----------------------------------------------------------
+    def _tok(self):
+        if not self._tokenizer_tried:
+            self._tokenizer_tried = True
+            model = self.config.model
+            if isinstance(model, str) and any(os.path.isfile(os.path.join(model, f))
+                                              for f in ("tokenizer.json", "tokenizer.model")):
+                from transformers import AutoTokenizer
+                self._tokenizer = AutoTokenizer.from_pretrained(model, local_files_only=True)
+        return self._tokenizer
+
+    def _encode(self, prompt) -> list:
+        if isinstance(prompt, str):
+            tok = self._tok()
+            if tok is None:
+                raise ValueError("a string prompt needs a tokenizer in the model folder; pass token ids instead")
+            return list(tok.encode(prompt))
+        ids = [int(t) for t in prompt]
+        vocab = self.runner.model.spec.vocab_size
+        if not ids or min(ids) < 0 or max(ids) >= vocab:
+            raise ValueError(f"prompt token ids must be a non-empty list within [0, {vocab})")
+        return ids
+
+    # ---- requests ----------------------------------------------------------------------
+    def add_request(self, prompt, sampling_params: Optional[SamplingParams] = None) -> int:
+        sp = sampling_params or SamplingParams()
+        sp.validate_for_vocab(self.runner.model.spec.vocab_size)
+        seq = Sequence(self._next_id, self._encode(prompt), sp)
+        self.scheduler.add(seq)
+        self._next_id += 1
+        return seq.seq_id
+
+    def abort_request(self, seq_id: int) -> bool:
+        return self.scheduler.abort(seq_id)
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    def step(self):
+        plan = self.scheduler.schedule()
+        entries, reqs = [], []
+        for it in plan.items:
+            s = it.seq
+            toks = s.slice(it.start, it.n_tokens)
+            entries.append(StepEntry(s.seq_id, toks, [it.n_tokens - 1] if it.samples else []))
+            if it.samples:
+                reqs.append(SampleRequest(s.params, s.seq_id, len(s.output_ids), s.prompt_ids, s.output_ids))
+        decodes = plan.num_decodes
+        prefill_tokens = plan.num_tokens - decodes
+        logits = self.runner.step(entries)
+        tokens, logprobs = ([], None)
+        if reqs:
+            tokens, logprobs = self.sampler.sample(logits, reqs)
+        finished = self.scheduler.postprocess(plan, tokens, logprobs)
+        outs = [self._output(s) for s in finished]
+        return outs, (prefill_tokens if prefill_tokens > 0 else -decodes)
+
+    def _output(self, s: Sequence) -> dict:
+        tok = self._tok() if self._tokenizer_tried or isinstance(self.config.model, str) else None
+        text = tok.decode(s.output_ids, skip_special_tokens=True) if tok is not None else ""
+        out = {"seq_id": s.seq_id, "text": text, "token_ids": list(s.output_ids), "finish_reason": s.finish_reason}
+        if s.logprobs:
+            out["logprobs"] = list(s.logprobs)
+        return out
+
+    def generate(self, prompts: Seq, sampling_params=None, use_tqdm: bool = False) -> list:
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt (or a single one for all) is needed")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        done: dict = {}
+        bar = None
+        if use_tqdm:
+            from tqdm import tqdm
+            bar = tqdm(total=len(ids), desc="generate", file=sys.stderr)
+        while not self.is_finished():
+            outs, _ = self.step()
+            for o in outs:
+                done[o["seq_id"]] = o
+                if bar is not None:
+                    bar.update(1)
+        if bar is not None:
+            bar.close()
+        return [{k: v for k, v in done[i].items() if k != "seq_id"} for i in ids]
+
+    def exit(self) -> None:
+        self.runner = None
+        self.scheduler = None
+        torch.cuda.empty_cache()

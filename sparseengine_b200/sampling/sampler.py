@@ -1,0 +1,97 @@
+"""The sampler: next tokens from logits rows, on the device (kernels: csrc/sampling.cu).
+
+Greedy, temperature, top-k, top-p, presence and repetition penalties, optional
+log-probabilities — what the reference samples with (src/sparseengine/layers/sampler.py:5-142,
+src/sparseengine/engine/model_runner.py:2528-2569).  Unlike the reference's process-global
+generator, every row draws from its own counter-based stream keyed by
+(sampler seed, request id, number of tokens the request has produced), so a request's
+tokens do not depend on batch composition, chunking or preemption.
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops_sampling as sops
+from .params import SamplingParams
+
+
+@dataclass
+class SampleRequest:
+    params: SamplingParams
+    seq_id: object
+    step: int                                   # tokens produced so far by this request
+    prompt_ids: Sequence[int] = ()
+    output_ids: Sequence[int] = ()
+
+
+def row_seed(sampler_seed: int, seq_id, step: int) -> int:
+    h = hashlib.blake2b(f"{sampler_seed}|{seq_id!r}|{step}".encode(), digest_size=8).digest()
+    return int.from_bytes(h, "little")
+
+
+class Sampler:
+    def __init__(self, seed: int = 0):
+        self.seed = int(seed)
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[SampleRequest]):
+        """logits [n, vocab] (activation dtype) → (token ids list[int], logprobs list or None)."""
+        n, vocab = logits.shape
+        if n != len(requests):
+            raise ValueError("one sampling request per logits row is needed")
+        dev = logits.device
+        want_lp = any(r.params.logprobs is not None for r in requests)
+        out = torch.empty(n, dtype=torch.int32, device=dev)
+        lp = torch.empty(n, dtype=torch.float32, device=dev) if want_lp else None
+
+        if any(r.params.has_penalties for r in requests):
+            logits = self._penalised(logits, requests)
+
+        if all(r.params.greedy for r in requests):
+            sops.sample(logits, None, None, None, None, out, lp)
+        else:
+            host = np.empty((n, 5), dtype=np.uint32)
+            f = host.view(np.float32)
+            for i, r in enumerate(requests):
+                f[i, 0] = r.params.temperature
+                host[i, 1] = min(r.params.top_k, vocab)
+                f[i, 2] = r.params.top_p
+                s = row_seed(self.seed, r.seq_id, r.step)
+                host[i, 3], host[i, 4] = s & 0xFFFFFFFF, s >> 32
+            d = torch.from_numpy(host.view(np.int32)).to(dev, non_blocking=False)
+            temp = d[:, 0].contiguous().view(torch.float32)
+            top_k = d[:, 1].contiguous()
+            top_p = d[:, 2].contiguous().view(torch.float32)
+            seeds = d[:, 3:5].contiguous().view(torch.int64).view(-1)
+            sops.sample(logits, temp, top_k, top_p, seeds, out, lp)
+        tokens = out.tolist()
+        logprobs = None
+        if want_lp:
+            chosen = lp.tolist()
+            logprobs = [chosen[i] if r.params.logprobs is not None else None for i, r in enumerate(requests)]
+        return tokens, logprobs
+
+    def _penalised(self, logits, requests):
+        n, vocab = logits.shape
+        dev = logits.device
+        work = torch.empty(n, vocab, dtype=torch.float32, device=dev)
+        sops.to_float(logits, work)
+        pairs = []
+        rep = np.ones(n, dtype=np.float32)
+        pres = np.zeros(n, dtype=np.float32)
+        for i, r in enumerate(requests):
+            if not r.params.has_penalties:
+                continue
+            rep[i], pres[i] = r.params.repetition_penalty, r.params.presence_penalty
+            completion = set(int(t) for t in r.output_ids)
+            everything = completion | set(int(t) for t in r.prompt_ids)
+            for t in everything:
+                pairs.append((i, t, 1 | (2 if t in completion else 0)))
+        if pairs:
+            p = torch.tensor(pairs, dtype=torch.int32, device=dev).view(-1)
+            sops.apply_penalties(work, p, len(pairs), torch.from_numpy(rep).to(dev), torch.from_numpy(pres).to(dev))
+        return work

@@ -1,0 +1,81 @@
+"""Configuration: the architecture's typed config, the registry, engine options."""
+import json
+
+import pytest
+
+import plain_m2
+from sparseengine_b200 import models  # noqa: F401
+from sparseengine_b200.config.engine_config import Config
+from sparseengine_b200.config.registry import architectures, load_model_spec, register_architecture
+from sparseengine_b200.models.minimax_m2 import MiniMaxM2Config
+
+
+@pytest.mark.parametrize("cfg", [plain_m2.TINY_A, plain_m2.TINY_B, plain_m2.TINY_C])
+def test_m2_config_reads_every_size(cfg):
+    typed, spec = load_model_spec(cfg)
+    assert isinstance(typed, MiniMaxM2Config)
+    assert spec.vocab_size == cfg["vocab_size"] and spec.hidden_size == cfg["hidden_size"]
+    assert len(spec.layers) == cfg["num_hidden_layers"] == len(spec.order)
+    a = spec.layers[0].mixer
+    assert (a.num_heads, a.num_kv_heads, a.head_dim) == (cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                                                          cfg["head_dim"])
+    assert a.position.rotary_dim == cfg["rotary_dim"] and a.position.theta == cfg["rope_theta"]
+    assert a.qk_norm == "whole_projection" and a.qk_norm_eps == cfg["rms_norm_eps"]
+    assert a.scale == cfg["head_dim"] ** -0.5 and a.window is None
+    f = spec.layers[-1].feed_forward
+    assert (f.num_experts, f.top_k, f.intermediate_size) == (cfg["num_local_experts"], cfg["num_experts_per_tok"],
+                                                             cfg["intermediate_size"])
+    assert f.score_fn == "sigmoid" and f.selection_bias and f.renormalize
+    assert spec.layers[0].mixer_norm.eps == cfg["rms_norm_eps"]
+    assert typed.to_dict()["num_local_experts"] == cfg["num_local_experts"]
+    assert MiniMaxM2Config.from_dict(typed.to_dict()) == typed
+
+
+def test_m2_config_refuses_what_it_cannot_run():
+    bad = dict(plain_m2.TINY_A, scoring_func="softmax", qk_norm_type="per_head")
+    with pytest.raises(ValueError) as e:
+        load_model_spec(bad)
+    assert "scoring_func" in str(e.value) and "qk_norm_type" in str(e.value)
+    missing = {k: v for k, v in plain_m2.TINY_A.items() if k not in ("rotary_dim", "head_dim")}
+    with pytest.raises(ValueError) as e:
+        load_model_spec(missing)
+    assert "rotary_dim" in str(e.value) and "head_dim" in str(e.value)
+    with pytest.raises(ValueError):
+        load_model_spec(dict(plain_m2.TINY_A, num_attention_heads=5))
+    with pytest.raises(ValueError):
+        load_model_spec(dict(plain_m2.TINY_A, quantization_config={"quant_method": "fp8"}))
+    with pytest.raises(ValueError):
+        load_model_spec(dict(plain_m2.TINY_A, rope_scaling={"rope_type": "yarn", "factor": 2.0}))
+
+
+def test_rope_theta_from_rope_parameters_and_context_keys():
+    cfg = {k: v for k, v in plain_m2.TINY_A.items() if k not in ("rope_theta", "max_position_embeddings")}
+    cfg["rope_parameters"] = {"rope_theta": 12345.0, "rope_type": "default"}
+    cfg["max_seq_len"] = 77
+    typed, spec = load_model_spec(cfg)
+    assert typed.rope_theta == 12345.0 and spec.max_position == 77
+
+
+def test_registry():
+    assert "MiniMaxM2ForCausalLM" in architectures()
+    with pytest.raises(ValueError, match="unknown architecture"):
+        load_model_spec({"architectures": ["NoSuchModel"]})
+    with pytest.raises(ValueError):
+        load_model_spec({"architectures": []})
+
+
+def test_engine_options(tmp_path):
+    c = Config.from_kwargs("m", max_num_batched_tokens=128, max_num_seqs_in_batch=4)
+    assert c.max_decoding_seqs == 4 and c.max_num_seqs_in_gpu == 12 and c.engine_prefill_chunk_size == 128
+    with pytest.raises(ValueError, match="unknown engine option"):
+        Config.from_kwargs("m", no_such_option=1)
+    with pytest.raises(ValueError):
+        Config.from_kwargs("m", sparse_method="snapkv")
+    with pytest.raises(ValueError):
+        Config.from_kwargs("m", tensor_parallel_size=2)
+    assert Config.from_kwargs("m", sparse_method="vanilla").sparse_method == "vanilla"
+    p = tmp_path / "hp.json"
+    p.write_text(json.dumps({"page_size": 8, "dtype": "float32"}))
+    c = Config.from_json("m", "@" + str(p))
+    assert c.page_size == 8 and c.dtype == "float32"
+    assert Config.from_json("m", '{"seed": 3}').seed == 3

@@ -1,0 +1,310 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same op, at sizes
+other than the tiny models': widths and vocabularies that are no power of two, head
+sizes in steps of 16, odd head and group counts."""
+import math
+
+import pytest
+import torch
+
+import plain_m2
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return dict(atol=f32, rtol=f32) if dtype == torch.float32 else dict(atol=bf16, rtol=bf16)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 3072, 5000])
+def test_embed_and_gather(dtype, hidden):
+    from sparseengine_b200.csrc import ops
+    table = rnd(301, hidden, dtype=dtype)
+    ids = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, hidden, dtype=dtype, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out, table[ids.long()])
+    g = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    ops.gather_rows(out, torch.tensor([4, 0, 2], dtype=torch.int32, device=DEV), g)
+    assert torch.equal(g, out[[4, 0, 2]])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 64, 1e-6), (7, 3072, 1e-5), (33, 1000, 1e-6), (3, 20000, 1e-6)])
+def test_rmsnorm_with_and_without_residual(dtype, rows, hidden, eps):
+    from sparseengine_b200.csrc import ops
+    x, r = rnd(rows, hidden, dtype=dtype, seed=1), rnd(rows, hidden, dtype=dtype, scale=3.0, seed=2)
+    w = (1 + 0.1 * rnd(hidden, seed=3)).to(dtype)
+    y = torch.empty_like(x)
+    ops.rmsnorm(x, w, eps, y)
+    ref = plain_m2.rms_norm(x.float().cpu(), w.float().cpu(), eps, dtype)
+    torch.testing.assert_close(y.float().cpu(), ref, **tol(dtype, 2e-6, 1e-2))
+    y2, r2 = torch.empty_like(x), torch.empty_like(x)
+    ops.rmsnorm(x, w, eps, y2, residual=r, residual_out=r2)
+    ref_y, ref_r = plain_m2.add_rms_norm(x.float().cpu(), r.float().cpu(), w.float().cpu(), eps, dtype)
+    assert torch.equal(r2.float().cpu(), ref_r)                  # the residual is the rounded 32-bit sum, exactly
+    torch.testing.assert_close(y2.float().cpu(), ref_y, **tol(dtype, 2e-6, 1e-2))
+
+
+def _cache_setup(tokens_per_seq, hkv, d, page, dtype, firsts=None):
+    """Block tables with scattered pages for positions firsts[i] .. firsts[i]+tokens-1 of
+    each request; returns metadata tensors for a step that brings all of those tokens."""
+    n = len(tokens_per_seq)
+    firsts = firsts or [0] * n
+    need = [range(f // page, (f + t - 1) // page + 1) for f, t in zip(firsts, tokens_per_seq)]
+    total = sum(len(r) for r in need) + 3
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(5)).tolist()
+    width = max(r.stop for r in need) + 1
+    table = torch.full((n + 2, width), -1, dtype=torch.int32)
+    rows = [i + 1 for i in range(n)]
+    k = 0
+    for i, r in enumerate(need):
+        for j in r:
+            table[rows[i], j] = perm[k]
+            k += 1
+    positions = torch.cat([torch.arange(f, f + t) for f, t in zip(firsts, tokens_per_seq)]).int()
+    token_seq = torch.cat([torch.full((t,), i) for i, t in enumerate(tokens_per_seq)]).int()
+    cache = torch.zeros(total, 2, hkv, page, d, dtype=dtype, device=DEV)
+    return (table.to(DEV), torch.tensor(rows, dtype=torch.int32, device=DEV), positions.to(DEV), token_seq.to(DEV),
+            cache)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,rot,page,theta,norm", [
+    (4, 2, 16, 8, 4, 1e4, True), (6, 3, 32, 32, 8, 1e6, True), (5, 1, 48, 16, 16, 5e4, True),
+    (7, 7, 80, 0, 3, 1e4, False), (48, 8, 128, 64, 16, 5e6, True)])
+def test_qk_prep_norm_rotary_and_cache_write(dtype, hq, hkv, d, rot, page, theta, norm):
+    from sparseengine_b200.csrc import ops
+    lens = [5, 1, 19]
+    t = sum(lens)
+    # one request sits at large positions (large rotation angles, a far table index)
+    table, rows, positions, token_seq, cache = _cache_setup(lens, hkv, d, page, dtype, firsts=[0, 3, 1000])
+    qkv = rnd(t, (hq + 2 * hkv) * d, dtype=dtype, scale=2.0, seed=4)
+    qw = (1 + 0.1 * rnd(hq * d, seed=5)).to(dtype) if norm else None
+    kw = (1 + 0.1 * rnd(hkv * d, seed=6)).to(dtype) if norm else None
+    inv = plain_m2.rope_inv_freq(rot, theta).to(DEV) if rot else None
+    q_out = torch.empty(t, hq * d, dtype=dtype, device=DEV)
+    ops.qk_prep(qkv, qw, kw, inv, positions, token_seq, rows, table, cache, q_out, num_heads=hq, num_kv_heads=hkv,
+                head_dim=d, rotary_dim=rot, eps=1e-5, rope_scale=1.0, page_size=page)
+    c = qkv.float().cpu()
+    q, k, v = c[:, :hq * d], c[:, hq * d:(hq + hkv) * d], c[:, (hq + hkv) * d:]
+    if norm:
+        q = plain_m2.whole_projection_rms_norm(q, qw.float().cpu(), 1e-5, dtype)
+        k = plain_m2.whole_projection_rms_norm(k, kw.float().cpu(), 1e-5, dtype)
+    q, k = q.view(t, hq, d), k.view(t, hkv, d)
+    if rot:
+        q = plain_m2.partial_rotary(q, positions.cpu(), rot, theta, dtype)
+        k = plain_m2.partial_rotary(k, positions.cpu(), rot, theta, dtype)
+    # large angles: the device's sincosf and the host's cos/sin agree to an ulp of the angle
+    torch.testing.assert_close(q_out.float().cpu().view(t, hq, d), q, **tol(dtype, 3e-5, 2e-2))
+    if rot < d:
+        assert torch.equal(q_out.float().cpu().view(t, hq, d)[..., rot:], q[..., rot:])     # pass-through is exact
+    cc = cache.float().cpu()
+    for i in range(t):
+        p = int(positions[i])
+        page_id = int(table[int(rows[int(token_seq[i])]), p // page])
+        torch.testing.assert_close(cc[page_id, 0, :, p % page], k[i], **tol(dtype, 3e-5, 2e-2))
+        assert torch.equal(cc[page_id, 1, :, p % page], v[i].view(hkv, d))
+
+
+def _attention_reference(q, k, v, lens, starts, dtype, window):
+    outs = []
+    a = 0
+    for n, s in zip(lens, starts):
+        qs = torch.zeros(s + n, q.shape[1], q.shape[2])
+        qs[s:] = q[a:a + n]
+        outs.append(plain_m2.causal_attention(qs, k[len(outs)], v[len(outs)], dtype, window)[s:])
+        a += n
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,window", [
+    (4, 2, 16, 4, None), (6, 3, 32, 8, None), (5, 1, 48, 16, None), (9, 3, 80, 5, 7), (12, 2, 128, 16, None),
+    (2, 2, 256, 32, 20)])
+def test_paged_attention_plain(dtype, hq, hkv, d, page, window):
+    """Queries are the last q_len positions of each request; earlier keys come from pages
+    written before (scattered page order)."""
+    from sparseengine_b200.csrc import ops
+    kv_lens, q_lens = [37, 1, 64, 130], [5, 1, 1, 33]
+    starts = [kv - ql for kv, ql in zip(kv_lens, q_lens)]
+    table, rows, _, _, cache = _cache_setup(kv_lens, hkv, d, page, dtype)
+    ks = [rnd(n, hkv, d, dtype=dtype, seed=20 + i).cpu() for i, n in enumerate(kv_lens)]
+    vs = [rnd(n, hkv, d, dtype=dtype, seed=30 + i).cpu() for i, n in enumerate(kv_lens)]
+    for i, n in enumerate(kv_lens):
+        for p in range(n):
+            pg = int(table[int(rows[i]), p // page])
+            cache[pg, 0, :, p % page] = ks[i][p].to(DEV)
+            cache[pg, 1, :, p % page] = vs[i][p].to(DEV)
+    t = sum(q_lens)
+    q = rnd(t, hq, d, dtype=dtype, seed=7)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, q_lens)]).int().to(DEV)
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).int().to(DEV)
+    out = torch.empty_like(q)
+    ops.paged_attention_plain(q.view(t, hq * d), cache, table, rows, token_seq, positions, out.view(t, hq * d),
+                              num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5,
+                              window=window)
+    ref = _attention_reference(q.float().cpu(), [k.float() for k in ks], [v.float() for v in vs], q_lens, starts,
+                               dtype, window)
+    torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype, 2e-5, 2e-2))
+
+
+def test_attention_finds_a_far_key_among_hundreds():
+    """One key far back is made to dominate: the output must be its value, whatever page
+    it lies on (first slot of a page, last slot, first page)."""
+    from sparseengine_b200.csrc import ops
+    hq, hkv, d, page, n = 4, 2, 32, 8, 700
+    for far in (0, 7, 8, 15, 343, 696):
+        table, rows, _, _, cache = _cache_setup([n], hkv, d, page, torch.float32)
+        k = rnd(n, hkv, d, scale=0.1, seed=1).cpu()
+        v = rnd(n, hkv, d, seed=2).cpu()
+        q = rnd(1, hq, d, scale=0.1, seed=3)
+        k[far] = q.cpu()[0, ::2] * 400.0               # kv head g gets query head 2g's direction, scaled up
+        for p in range(n):
+            pg = int(table[1, p // page])
+            cache[pg, 0, :, p % page] = k[p].to(DEV)
+            cache[pg, 1, :, p % page] = v[p].to(DEV)
+        out = torch.empty_like(q)
+        ops.paged_attention_plain(q.view(1, -1), cache, table, rows, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                  torch.tensor([n - 1], dtype=torch.int32, device=DEV), out.view(1, -1),
+                                  num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5)
+        got = out.cpu()[0]
+        assert torch.allclose(got[0], v[far, 0], atol=1e-3) and torch.allclose(got[2], v[far, 1], atol=1e-3), far
+        ref = plain_m2.causal_attention(torch.cat([torch.zeros(n - 1, hq, d), q.cpu()]), k, v, torch.float32)[-1]
+        torch.testing.assert_close(got, ref, atol=2e-5, rtol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,hidden,experts,top_k,bias", [
+    (5, 64, 4, 2, False), (9, 96, 8, 3, True), (700, 80, 6, 4, True), (3, 3072, 256, 8, True), (1, 200, 37, 5, True)])
+def test_router(dtype, tokens, hidden, experts, top_k, bias):
+    from sparseengine_b200.csrc import ops
+    x = rnd(tokens, hidden, dtype=dtype, seed=1)
+    gate = rnd(experts, hidden, scale=0.2, seed=2)
+    b = rnd(experts, scale=0.3, seed=3) if bias else None
+    ids = torch.empty(tokens, top_k, dtype=torch.int32, device=DEV)
+    w = torch.empty(tokens, top_k, dtype=torch.float32, device=DEV)
+    logits = torch.empty(tokens, experts, dtype=torch.float32, device=DEV)
+    ops.router(x, gate, b, ids, w, top_k=top_k, logits_out=logits)
+    ref_ids, ref_w, ref_logits = plain_m2.router(x.float().cpu(), gate.cpu(),
+                                                 b.cpu() if bias else torch.zeros(experts), top_k)
+    torch.testing.assert_close(logits.cpu(), ref_logits, atol=2e-5, rtol=2e-5)
+    # rows whose k-th and (k+1)-th scores are further apart than the logits' rounding must agree exactly
+    score = torch.sigmoid(ref_logits) + (b.cpu() if bias else 0)
+    srt = score.sort(-1, descending=True).values
+    clear = (srt[:, :-1] - srt[:, 1:]).min(-1).values > 1e-5 if experts > 1 else torch.ones(tokens, dtype=torch.bool)
+    assert clear.float().mean() > 0.5
+    assert torch.equal(ids.cpu()[clear].long(), ref_ids[clear])
+    torch.testing.assert_close(w.cpu()[clear], ref_w[clear], atol=1e-5, rtol=1e-5)
+
+
+def test_router_tie_order_nan_and_softmax():
+    from sparseengine_b200.csrc import ops
+    x = torch.zeros(2, 8, device=DEV)
+    gate = torch.zeros(6, 8, device=DEV)
+    b = torch.tensor([0.0, 0.3, 0.0, 0.5, 0.0, 0.3], device=DEV)
+    ids = torch.empty(2, 4, dtype=torch.int32, device=DEV)
+    w = torch.empty(2, 4, dtype=torch.float32, device=DEV)
+    ops.router(x, gate, b, ids, w, top_k=4)
+    assert ids.cpu().tolist() == [[1, 3, 5, 0]] * 2 and torch.allclose(w.cpu(), torch.full((2, 4), 0.25))
+    b2 = b.clone()
+    b2[4] = float("nan")                         # a NaN score counts as +inf
+    ops.router(x, gate, b2, ids, w, top_k=2)
+    assert sorted(ids.cpu()[0].tolist()) == [3, 4]
+    x = rnd(3, 8, seed=4)
+    gate = rnd(6, 8, seed=5)
+    ops.router(x, gate, None, ids, w, top_k=4, score_fn="softmax", renormalize=False, routed_scale=2.5)
+    p = torch.softmax(x.cpu() @ gate.cpu().t(), -1)
+    top = p.topk(4).indices
+    assert [sorted(r) for r in ids.cpu().tolist()] == [sorted(r) for r in top.tolist()]
+    torch.testing.assert_close(w.cpu(), 2.5 * p.gather(1, ids.cpu().long()), atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,hidden,inter,experts,top_k", [
+    (5, 64, 32, 4, 2), (70, 96, 48, 8, 3), (33, 80, 40, 6, 4), (130, 200, 72, 16, 5), (1, 64, 32, 4, 2)])
+def test_routed_experts_plain(dtype, tokens, hidden, inter, experts, top_k):
+    from sparseengine_b200.config.specs import MoESpec
+    from sparseengine_b200.parts.moe import SparseMoE
+    x = rnd(tokens, hidden, dtype=dtype, seed=1)
+    w13 = rnd(experts, 2 * inter, hidden, dtype=dtype, scale=0.1, seed=2)
+    w2 = rnd(experts, hidden, inter, dtype=dtype, scale=0.1, seed=3)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).int().to(DEV)
+    if tokens > 40:
+        ids[:, 0] = 1                           # a crowded expert (several row tiles) ...
+        ids[ids == experts - 1] = 0             # ... and an empty one
+        ids[:, 1] = 2
+    wt = torch.rand(tokens, top_k, generator=g).to(DEV)
+    part = SparseMoE(MoESpec(hidden_size=hidden, num_experts=experts, top_k=top_k, intermediate_size=inter), dtype)
+    part.bind({"w13": w13, "w2": w2})
+    out = part.run_experts(x, ids, wt)
+    ref = plain_m2.experts(x.float().cpu(), ids.cpu().long(), wt.cpu(), w13[:, :inter].float().cpu(),
+                           w13[:, inter:].float().cpu(), w2.float().cpu(), dtype)
+    torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype, 1e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampling_greedy_and_filters(dtype):
+    from sparseengine_b200.csrc import ops_sampling as sops
+    vocab = 5003
+    logits = rnd(6, vocab, dtype=dtype, scale=2.0, seed=9)
+    logits[1, 77] = logits[1, 4000] = 50.0        # a tie: the first wins
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    sops.sample(logits, None, None, None, None, out)
+    assert out.cpu().tolist() == logits.float().argmax(-1).cpu().tolist() and int(out[1]) == 77
+    # top-k = 1 and a tiny top-p are greedy whatever the noise
+    temp = torch.full((6,), 0.9, device=DEV)
+    seeds = torch.arange(6, dtype=torch.int64, device=DEV) + 12345
+    k1 = torch.ones(6, dtype=torch.int32, device=DEV)
+    sops.sample(logits, temp, k1, torch.ones(6, device=DEV), seeds, out)
+    assert out.cpu().tolist()[0] == int(logits[0].float().argmax()) and int(out[1]) in (77, 4000)
+    sops.sample(logits, temp, torch.zeros(6, dtype=torch.int32, device=DEV), torch.full((6,), 1e-4, device=DEV), seeds, out)
+    assert out.cpu().tolist()[2:] == logits.float().argmax(-1).cpu().tolist()[2:]
+
+
+def test_sampling_distribution_topk_topp():
+    """Many draws with different seeds follow softmax(logits / T) cut by top-k and top-p
+    (the reference's rule: sorted, keep while the mass before an entry is <= top-p)."""
+    from sparseengine_b200.csrc import ops_sampling as sops
+    vocab, n = 50, 40000
+    base = torch.linspace(2.0, -2.0, vocab)
+    logits = base.repeat(n, 1).to(DEV)
+    temp = torch.full((n,), 0.7, device=DEV)
+    seeds = torch.arange(n, dtype=torch.int64, device=DEV) * 7919 + 17
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    for top_k, top_p in ((0, 1.0), (10, 1.0), (0, 0.6), (12, 0.8)):
+        sops.sample(logits, temp, torch.full((n,), top_k, dtype=torch.int32, device=DEV),
+                    torch.full((n,), top_p, device=DEV), seeds, out)
+        p = torch.softmax(base / 0.7, -1)
+        if top_k:
+            p[top_k:] = 0
+            p = p / p.sum()
+        if top_p < 1:
+            before = torch.cumsum(p, 0) - p
+            p[before > top_p] = 0
+            p = p / p.sum()
+        hist = torch.bincount(out.cpu().long(), minlength=vocab).float() / n
+        assert hist[p == 0].sum() == 0, (top_k, top_p)
+        assert (hist - p).abs().max() < 0.01, (top_k, top_p)
+    # the same seed gives the same token; the row's place in the batch does not matter
+    sops.sample(logits[:4], temp[:4], None, None, seeds[10:14].contiguous(), out[:4])
+    a = out[:4].cpu().tolist()
+    sops.sample(logits[:2], temp[:2], None, None, seeds[12:14].contiguous(), out[:2])
+    assert out[:2].cpu().tolist() == a[2:]
+
+
+def test_penalties():
+    from sparseengine_b200.csrc import ops_sampling as sops
+    logits = torch.tensor([[1.0, -2.0, 3.0, 0.5], [1.0, -2.0, 3.0, 0.5]], device=DEV)
+    pairs = torch.tensor([[0, 0, 1], [0, 1, 3], [0, 2, 3], [1, 3, 2]], dtype=torch.int32, device=DEV).view(-1)
+    sops.apply_penalties(logits, pairs, 4, torch.tensor([2.0, 1.0], device=DEV), torch.tensor([0.5, 0.25], device=DEV))
+    assert logits.cpu().tolist() == [[0.5, -4.5, 1.0, 0.5], [1.0, -2.0, 3.0, 0.25]]
