@@ -54,19 +54,20 @@ class Sampler:
         if all(r.params.greedy for r in requests):
             sops.sample(logits, None, None, None, None, out, lp)
         else:
-            host = np.empty((n, 5), dtype=np.uint32)
+            # one packed upload: seeds (2 words a row) first, then temperature, top-k, top-p
+            host = np.empty(5 * n, dtype=np.uint32)
             f = host.view(np.float32)
             for i, r in enumerate(requests):
-                f[i, 0] = r.params.temperature
-                host[i, 1] = min(r.params.top_k, vocab)
-                f[i, 2] = r.params.top_p
                 s = row_seed(self.seed, r.seq_id, r.step)
-                host[i, 3], host[i, 4] = s & 0xFFFFFFFF, s >> 32
+                host[2 * i], host[2 * i + 1] = s & 0xFFFFFFFF, s >> 32
+                f[2 * n + i] = r.params.temperature
+                host[3 * n + i] = min(r.params.top_k, vocab)
+                f[4 * n + i] = r.params.top_p
             d = torch.from_numpy(host.view(np.int32)).to(dev, non_blocking=False)
-            temp = d[:, 0].contiguous().view(torch.float32)
-            top_k = d[:, 1].contiguous()
-            top_p = d[:, 2].contiguous().view(torch.float32)
-            seeds = d[:, 3:5].contiguous().view(torch.int64).view(-1)
+            seeds = d[:2 * n].view(torch.int64)
+            temp = d[2 * n:3 * n].view(torch.float32)
+            top_k = d[3 * n:4 * n]
+            top_p = d[4 * n:5 * n].view(torch.float32)
             sops.sample(logits, temp, top_k, top_p, seeds, out, lp)
         tokens = out.tolist()
         logprobs = None
