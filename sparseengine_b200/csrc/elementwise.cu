@@ -37,7 +37,7 @@ __global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restric
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)hidden + eps);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         y[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
 }

@@ -35,8 +35,8 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
         for (int i = threadIdx.x; i < kn; i += blockDim.x) { float v = to_float(row[qn + i]); sk += v * v; }
         sq = block_sum(sq, scratch);
         sk = block_sum(sk, scratch);
-        inv_q = rsqrtf(sq / (float)qn + eps);
-        inv_k = rsqrtf(sk / (float)kn + eps);
+        inv_q = 1.0f / sqrtf(sq / (float)qn + eps);
+        inv_k = 1.0f / sqrtf(sk / (float)kn + eps);
     }
     if (inv_freq != nullptr) {
         for (int j = threadIdx.x; j < half; j += blockDim.x) {

@@ -67,6 +67,10 @@ class SparseMoE(_RoutedSwiGLU):
             out["selection_bias"] = ParamSpec((s.num_experts,), "float32", "bias")
         return out
 
+    # Debugging aid: set to a list and every call appends the chosen expert ids (a CPU
+    # copy, [tokens, top_k]), so that a test can follow the router through a near-tie.
+    capture = None
+
     def route(self, x):
         tokens = x.shape[0]
         ids = torch.empty(tokens, self.top_k, dtype=torch.int32, device=x.device)
@@ -74,6 +78,8 @@ class SparseMoE(_RoutedSwiGLU):
         s = self.spec
         ops.router(x, self.gate, self.selection_bias, ids, weights, top_k=self.top_k, score_fn=s.score_fn,
                    renormalize=s.renormalize, routed_scale=s.routed_scale)
+        if self.capture is not None:
+            self.capture.append(ids.cpu())
         return ids, weights
 
     def forward(self, x, step):

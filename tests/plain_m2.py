@@ -224,14 +224,36 @@ def attention_block(x, lt, cfg, positions, act):
     return linear(o.reshape(t, hq * d), lt["wo"], act), (q, k, v)
 
 
-def moe_block(x, lt, cfg, act):
-    """Router then experts (src/sparseengine/models/minimax_m2.py:244-269)."""
-    ids, w, _ = router(x, lt["gate"], lt["bias"], int(cfg["num_experts_per_tok"]))
+def moe_block(x, lt, cfg, act, forced_ids=None, info=None):
+    """Router then experts (src/sparseengine/models/minimax_m2.py:244-269).
+
+    ``forced_ids`` [T, k] replaces the router's own choice of experts (the weights are
+    still this router's unbiased scores of those experts, renormalised): a test uses it
+    to follow an engine through a near-tie, where rounding may pick either expert.
+    ``info`` (a dict) receives this router's own ids and, per token, the gap between its
+    k-th and (k+1)-th selection scores."""
+    k = int(cfg["num_experts_per_tok"])
+    ids, w, logits = router(x, lt["gate"], lt["bias"], k)
+    if info is not None:
+        score = torch.sigmoid(logits) + lt["bias"].to(torch.float32)
+        srt = score.sort(-1, descending=True).values
+        info.setdefault("ids", []).append(ids)
+        info.setdefault("margin", []).append(srt[:, k - 1] - srt[:, k] if srt.shape[1] > k
+                                             else torch.full((x.shape[0],), float("inf")))
+    if forced_ids is not None:
+        ids = forced_ids.long()
+        p = torch.sigmoid(logits).gather(1, ids)
+        w = p / p.sum(-1, keepdim=True)
     return experts(x, ids, w, lt["w1"], lt["w3"], lt["w2"], act)
 
 
-def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float32) -> torch.Tensor:
+def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float32, forced_ids=None,
+            info=None) -> torch.Tensor:
     """Logits [T, V] (float32) at every position of one whole sequence.
+
+    ``forced_ids``: optional list (one entry per layer) of expert ids [T, k] to use
+    instead of the router's own; ``info``: optional dict that receives the routers' own
+    ids and score gaps per layer (see :func:`moe_block`).
 
     Pre-norm residual convention of src/sparseengine/models/minimax_m2.py:381-397 and
     src/sparseengine/models/qwen3.py:291-328: the residual stream is rounded to act
@@ -254,7 +276,7 @@ def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float3
             x, residual = add_rms_norm(hidden, residual, lt["ln1"], eps, act)
         hidden, _ = attention_block(x, lt, cfg, positions, act)
         x, residual = add_rms_norm(hidden, residual, lt["ln2"], eps, act)
-        hidden = moe_block(x, lt, cfg, act)
+        hidden = moe_block(x, lt, cfg, act, None if forced_ids is None else forced_ids[i], info)
     x, _ = add_rms_norm(hidden, residual, tensors["model.norm.weight"], eps, act)
     return linear(x, tensors["lm_head.weight"], act)
 

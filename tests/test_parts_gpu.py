@@ -133,8 +133,10 @@ def toy_tensors(seed=3):
     return t
 
 
-def toy_plain(t, tokens, act=torch.float32):
-    """The toy model written out with the plain implementation's functions."""
+def toy_plain(t, tokens, act=torch.float32, forced=None):
+    """The toy model written out with the plain implementation's functions.  ``forced``:
+    expert ids [T, k] for each of the two visits of the routed layer (the engine's own
+    choice, followed through near-ties)."""
     c = TOY
     n = len(tokens)
     hq, hkv, d, inter = c["heads"], c["kv_heads"], c["head_dim"], c["inter"]
@@ -164,9 +166,19 @@ def toy_plain(t, tokens, act=torch.float32):
         mean = torch.cumsum(x.float(), 0) / torch.arange(1, n + 1)[:, None]
         return plain_m2.linear(plain_m2._round(mean, act), t["l1.w"], act)
 
+    visits = []
+
     def moe(x):
         p = torch.softmax(x.float() @ t["l1.gate"].t(), -1)
         thr_ids, _, _ = plain_m2.router(x, t["l1.gate"], torch.zeros(c["experts"]), c["top_k"])   # sigmoid is monotone
+        if forced is not None:
+            own, thr_ids = thr_ids, forced[len(visits)].long()
+            srt = p.sort(-1, descending=True).values
+            gap = srt[:, c["top_k"] - 1] - srt[:, c["top_k"]]
+            for i in range(n):
+                if gap[i] > 2e-3:
+                    assert sorted(own[i].tolist()) == sorted(thr_ids[i].tolist()), (len(visits), i)
+        visits.append(1)
         w = p.gather(1, thr_ids) * c["routed_scale"]
         return plain_m2.experts(x, thr_ids, w, t["l1.w13"][:, :inter], t["l1.w13"][:, inter:], t["l1.w2"], act)
 
@@ -223,13 +235,14 @@ def test_toy_model_steps_like_its_plain_form(toy_folder, dtype):
     folder, t = toy_folder
     act = torch.float32 if dtype == "float32" else torch.bfloat16
     seqs = {f"s{i}": tu.random_prompt(TOY["vocab_size"], n, i) for i, n in enumerate([3, 11, 26, 40, 17])}
-    ref = {sid: toy_plain(t, toks, act).numpy() for sid, toks in seqs.items()}
     for cut in (tu.trace_whole, tu.trace_chunks, tu.trace_mixed):
         steps = cut(seqs)
         page = 4
         runner = build_runner(folder, dtype=dtype, page_size=page, num_pages=tu.max_live_tokens(steps) // page,
                               max_rows=4)
-        got = tu.run_trace_runner(runner, steps)
+        got, routed = tu.run_trace_runner(runner, steps, capture=True)
+        ref = {sid: toy_plain(t, toks, act, routed[sid] if dtype == "bfloat16" else None).numpy()
+               for sid, toks in seqs.items()}
         tu.compare(got, ref, *((2e-5, 2e-5) if dtype == "float32" else (3e-2, 3e-2)), what=f"toy {dtype} {cut.__name__}")
         for g in runner.cache.groups:
             assert g.pool.free == g.pool.num_pages

@@ -30,17 +30,42 @@ def folders(tmp_path_factory):
 
 
 _REF = {}
+NEAR_TIE = {"float32": 1e-5, "bfloat16": 4e-3}    # gap of router scores below which either expert may win
 
 
-def reference(name, dtype, tensors, seqs):
+def reference(name, dtype, tensors, seqs, routed=None):
+    """Plain logits per request.  In bfloat16 the plain implementation is made to follow
+    the engine's choice of experts (``routed``, captured from the engine): where two
+    experts' scores are closer than the rounding noise either may win, and the logits
+    jump.  Wherever the plain router's own gap is clear the engine must have chosen the
+    same experts."""
     cfg = tu.TINY[name][0]
     out = {}
     for sid, toks in seqs.items():
-        key = (name, dtype, tuple(toks))
+        forced = routed[sid] if routed is not None else None
+        key = (name, dtype, tuple(toks), None if forced is None else tuple(tuple(map(tuple, f.tolist())) for f in forced))
         if key not in _REF:
-            _REF[key] = plain_m2.forward(cfg, tensors, toks, ACT[dtype]).numpy()
+            info = {}
+            logits = plain_m2.forward(cfg, tensors, toks, ACT[dtype], forced_ids=forced, info=info).numpy()
+            if forced is not None:
+                for layer, (own, gap, eng) in enumerate(zip(info["ids"], info["margin"], forced)):
+                    for t in range(len(toks)):
+                        if gap[t] > NEAR_TIE[dtype]:
+                            assert sorted(own[t].tolist()) == sorted(eng[t].tolist()), (
+                                f"{name} {dtype} request {sid} layer {layer} position {t}: engine routed to "
+                                f"{eng[t].tolist()}, plain to {own[t].tolist()} with a clear gap {float(gap[t]):.2e}")
+            _REF[key] = logits
         out[sid] = _REF[key]
     return out
+
+
+def first_near_tie(name, dtype, tensors, toks):
+    """First position at which some router of the plain implementation has a near-tie."""
+    info = {}
+    plain_m2.forward(tu.TINY[name][0], tensors, toks, ACT[dtype], info=info)
+    gap = torch.stack(info["margin"]).min(0).values
+    bad = (gap <= NEAR_TIE[dtype]).nonzero()
+    return int(bad[0]) if len(bad) else len(toks)
 
 
 def sequences(name, lengths=LENGTHS):
@@ -76,9 +101,10 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
         assert max(len(s["entries"]) for s in steps) == 4
         assert any(len({len(e["tokens"]) > 1 for e in s["entries"]}) == 2 for s in steps)   # portion beside a decode
     runner = runner_for(folder, name, dtype, steps)
-    got = tu.run_trace_runner(runner, steps)
+    got, routed = tu.run_trace_runner(runner, steps, capture=True)
     assert len(got) == sum(len(t) for t in seqs.values())
-    tu.compare(got, reference(name, dtype, tensors, seqs), *TOL[dtype], what=f"{name} {dtype} {cut}")
+    ref = reference(name, dtype, tensors, seqs, routed if dtype == "bfloat16" else None)
+    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} {cut}")
     pool = runner.cache.groups[0].pool
     assert pool.free == pool.num_pages and pool.reused_total > 0      # everything came back; pages were reused
     runner.cache.check()
@@ -88,13 +114,15 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
 def test_cuts_agree_with_each_other_more_tightly_than_with_the_plain(folders, dtype):
     """The same request through different cuts and page sets: the logits differ by
     rounding only (in 32-bit: a few ulp of the order of sums)."""
-    folder, _ = folders["B", dtype]
+    folder, tensors = folders["B", dtype]
     seqs = sequences("B", [41])
+    upto = first_near_tie("B", dtype, tensors, seqs["r0"]) if dtype == "bfloat16" else 41
+    assert upto >= 3
     base = None
     for cut in CUTS:
         steps = CUTS[cut](seqs)
         got = tu.run_trace_runner(runner_for(folder, "B", dtype, steps), steps)
-        arr = np.stack([got["r0", p] for p in range(41)])
+        arr = np.stack([got["r0", p] for p in range(upto)])
         if base is None:
             base = arr
         else:
@@ -110,8 +138,8 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     toks = tu.random_prompt(256, 201, 99)
     steps = [{"step": i, "entries": [{"id": "d", "tokens": [t], "want": [0]}], "end": ["d"] if i == 200 else []}
              for i, t in enumerate(toks)]
-    got = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps)
-    ref = reference("A", dtype, tensors, {"d": toks})
+    got, routed = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps, capture=True)
+    ref = reference("A", dtype, tensors, {"d": toks}, routed if dtype == "bfloat16" else None)
     tu.compare({k: v for k, v in got.items() if k[1] < 3}, ref, *TOL[dtype], what="first tokens")
     tu.compare(got, ref, *TOL[dtype], what="long decoding")
 
@@ -147,4 +175,10 @@ def test_trace_run_program(folders, dtype, tmp_path):
         s["entries"][0]["want"] = []
     got = tu.run_trace_cli(folder, dtype, steps, str(tmp_path / "out"), tu.max_live_tokens(steps))
     assert got
+    if dtype == "bfloat16":
+        # the program cannot tell which experts it chose: compare up to each request's first near-tie
+        upto = {sid: first_near_tie("B", dtype, tensors, toks) for sid, toks in seqs.items()}
+        kept = {k: v for k, v in got.items() if k[1] < upto[k[0]]}
+        assert len(kept) >= 20
+        got = kept
     tu.compare(got, reference("B", dtype, tensors, seqs), *TOL[dtype], what=f"trace_run {dtype}")

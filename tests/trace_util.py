@@ -176,11 +176,23 @@ def collect(steps: list, out_dir: str, vocab: int | None = None) -> dict:
     return out
 
 
-def run_trace_runner(runner, steps: list) -> dict:
-    """Run a trace in-process on a ModelRunner; returns {(id, position): logits row}."""
+def run_trace_runner(runner, steps: list, capture: bool = False):
+    """Run a trace in-process on a ModelRunner; returns {(id, position): logits row}.
+
+    With ``capture`` it also returns the experts each routed feed-forward chose:
+    ``{id: [visit][position] -> tuple of expert ids}``, one visit per routed feed-forward
+    in the order the model runs them (a layer that runs twice counts twice)."""
     from sparseengine_b200.engine.runner import StepEntry
     out = {}
     pos: dict = {}
+    routed: dict = {}
+    parts = []
+    if capture:
+        for entry in runner.model.spec.order:
+            ff = runner.model.blocks[entry.layer].feed_forward
+            if hasattr(ff, "route"):
+                ff.capture = []
+                parts.append(ff)
     for s in steps:
         entries = []
         for e in s["entries"]:
@@ -188,6 +200,20 @@ def run_trace_runner(runner, steps: list) -> dict:
                 runner.admit(e["id"])
             entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
         logits = runner.step(entries)
+        if capture:
+            seen: dict = {}
+            for visit, ff in enumerate(parts):          # a part visited twice appended twice, in order
+                k = seen.get(id(ff), 0)
+                seen[id(ff)] = k + 1
+                ids = ff.capture[k].tolist()
+                row = 0
+                for e in s["entries"]:
+                    store = routed.setdefault(e["id"], {}).setdefault(visit, {})
+                    for j in range(len(e["tokens"])):
+                        store[pos.get(e["id"], 0) + j] = tuple(ids[row])
+                        row += 1
+            for ff in parts:
+                ff.capture = []
         wanted = [(e["id"], pos.get(e["id"], 0) + w) for e in s["entries"] for w in e["want"]]
         for e in s["entries"]:
             pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
@@ -198,6 +224,12 @@ def run_trace_runner(runner, steps: list) -> dict:
         for sid in s["end"]:
             runner.release(sid)
             pos.pop(sid, None)
+    if capture:
+        for ff in parts:
+            ff.capture = None
+        as_lists = {sid: [torch.tensor([v[p] for p in range(len(v))]) for _, v in sorted(visits.items())]
+                    for sid, visits in routed.items()}
+        return out, as_lists
     return out
 
 
