@@ -222,6 +222,8 @@ def test_router_tie_order_nan_and_softmax():
     assert sorted(ids2.cpu()[0].tolist()) == [3, 4]
     x = rnd(3, 8, seed=4)
     gate = rnd(6, 8, seed=5)
+    ids = torch.empty(3, 4, dtype=torch.int32, device=DEV)
+    w = torch.empty(3, 4, dtype=torch.float32, device=DEV)
     ops.router(x, gate, None, ids, w, top_k=4, score_fn="softmax", renormalize=False, routed_scale=2.5)
     p = torch.softmax(x.cpu() @ gate.cpu().t(), -1)
     top = p.topk(4).indices

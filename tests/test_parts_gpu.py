@@ -139,6 +139,7 @@ def toy_plain(t, tokens, act=torch.float32, forced=None):
     choice, followed through near-ties)."""
     c = TOY
     n = len(tokens)
+    t = {k: (v if k == "l1.gate" else plain_m2._round(v, act)) for k, v in t.items()}   # the router stays 32-bit
     hq, hkv, d, inter = c["heads"], c["kv_heads"], c["head_dim"], c["inter"]
     pos = torch.arange(n)
 
