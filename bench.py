@@ -1,0 +1,298 @@
+#!/usr/bin/env python3
+"""Decode throughput of the engine at MiniMax M2 layer sizes, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one decode step of the whole batch (default: batch 8,
+prompts of 2,048 tokens, context limit 4,096, bfloat16, random weights N(0, 0.02),
+seed 2; layer sizes of MiniMax M2 at reduced depth).  ``value`` is decoded tokens per
+second of the step function (device-timed, tokens stay on the device); ``e2e`` is the
+same through ``LLM.add_request`` / ``LLM.step`` with host tokens in and out; ``prefill``
+times one 2,048-token prompt; ``points`` are decode at batch 1 and 64; ``roofline`` is the
+bytes a decode step has to read (every weight it uses once, the cache of the live
+requests) over its time, against the measured copy bandwidth.
+
+For --gpus N > 1 it prints one line that says so and exits with 2: the engine runs on
+one GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# MiniMax M2 layer sizes (the benchmark configuration), config.json keys.
+M2_LAYER_SIZES = {
+    "architectures": ["MiniMaxM2ForCausalLM"], "model_type": "minimax_m2",
+    "hidden_size": 3072, "num_attention_heads": 48, "num_key_value_heads": 8, "head_dim": 128,
+    "rotary_dim": 64, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6,
+    "num_local_experts": 256, "num_experts_per_tok": 8, "intermediate_size": 1536,
+    "vocab_size": 200064, "max_position_embeddings": 4096, "tie_word_embeddings": False,
+    "hidden_act": "silu", "qk_norm_type": "per_layer", "use_qk_norm": True, "scoring_func": "sigmoid",
+    "use_routing_bias": True, "use_mtp": True, "shared_intermediate_size": 0, "torch_dtype": "bfloat16",
+}
+FULL_MODEL_LAYERS = 62
+BENCH_LAYERS = 16
+PROMPT_LEN = 2048
+CONTEXT_LEN = 4096
+PAGE_SIZE = 16
+SEED = 2
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS)
+    src = "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if k in d and d[k]:
+                    out[k] = float(d[k])
+            src = "measured"
+        except Exception:
+            pass
+    out["source"] = src
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi samples of the SM clock and throttle reasons while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(self.NAMES, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_bytes(cfg: dict, layers: int):
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    e, inter, v = cfg["num_local_experts"], cfg["intermediate_size"], cfg["vocab_size"]
+    dense_layer = ((hq + 2 * hkv) * d * h + h * hq * d) * 2 + e * h * 4 + e * 4 + (2 * h + (hq + hkv) * d) * 2
+    expert = 3 * inter * h * 2
+    kv_token_layer = 2 * hkv * d * 2
+    return {"dense_layer": dense_layer, "expert": expert, "lm_head": v * h * 2, "kv_token_layer": kv_token_layer,
+            "weights_total": layers * (dense_layer + e * expert) + 2 * v * h * 2 + h * 2}
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    e, k, inter, v = cfg["num_local_experts"], cfg["num_experts_per_tok"], cfg["intermediate_size"], cfg["vocab_size"]
+    per_token = 2 * h * (hq + 2 * hkv) * d + 2 * hq * d * h + 2 * h * e + k * 3 * 2 * h * inter
+    attn = 4 * d * hq * tokens * (tokens + 1) / 2          # QK^T and PV, causal
+    return layers * (tokens * per_token + attn) + 2 * h * v
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from sparseengine_b200 import LLM, SamplingParams
+    from sparseengine_b200.csrc import ops
+    from sparseengine_b200.csrc import ops_sampling as sops
+    from sparseengine_b200.engine.runner import StepEntry
+
+    torch.cuda.set_device(0)
+    cfg = dict(M2_LAYER_SIZES, num_hidden_layers=args.layers)
+    pk = peaks()
+    batch = args.batch
+    max_rows = 64
+    slots = max_rows * CONTEXT_LEN
+    t0 = time.time()
+    llm = LLM(cfg, tiny_random=True, tiny_random_seed=SEED, dtype="bfloat16", page_size=PAGE_SIZE,
+              num_kvcache_slots=slots, max_model_len=CONTEXT_LEN, max_num_seqs_in_gpu=max_rows,
+              max_num_seqs_in_batch=max_rows, max_decoding_seqs=max_rows, max_num_batched_tokens=8192,
+              decode_reservation_tokens=0)
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+    runner = llm.runner
+    vocab = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(SEED)
+    mb = model_bytes(cfg, args.layers)
+
+    def fill(seq_ids, ctx):
+        """Requests that already hold ``ctx`` tokens: pages are taken and the lengths set
+        without a forward pass (the cache content does not matter for timing)."""
+        for s in seq_ids:
+            runner.admit(s)
+            runner.cache.reserve(s, ctx)
+            runner.cache.commit(s, ctx)
+
+    def decode_steps(seq_ids, n):
+        toks = torch.randint(0, vocab, (n, len(seq_ids)), generator=gen).tolist()
+        out = torch.empty(len(seq_ids), dtype=torch.int32, device="cuda")
+        for i in range(n):
+            logits = runner.step([StepEntry(s, [toks[i][j]], [0]) for j, s in enumerate(seq_ids)])
+            sops.sample(logits, None, None, None, None, out)
+
+    def timed_decode(b, ctx, warmup, steps, sample_clocks=False):
+        ids = [f"b{b}_{i}" for i in range(b)]
+        fill(ids, ctx)
+        decode_steps(ids, warmup)
+        torch.cuda.synchronize()
+        sampler = ClockSampler()
+        if sample_clocks:
+            sampler.start()
+        l0 = ops.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        decode_steps(ids, steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = ops.launch_count - l0
+        clocks = sampler.stop() if sample_clocks else None
+        # distinct experts the batch touches per layer, measured on one more step
+        ffs = [b_.feed_forward for b_ in runner.model.blocks]
+        for f in ffs:
+            f.capture = []
+        decode_steps(ids, 1)
+        distinct = [len(set(f.capture[0].view(-1).tolist())) for f in ffs]
+        for f in ffs:
+            f.capture = None
+        for s in ids:
+            runner.release(s)
+        kv_ctx = ctx + warmup + steps // 2
+        bytes_step = (args.layers * mb["dense_layer"] + sum(distinct) * mb["expert"] + mb["lm_head"]
+                      + b * kv_ctx * args.layers * mb["kv_token_layer"])
+        return {"ms": ms, "tok_s": b * 1000.0 / ms, "launches": launches, "clocks": clocks,
+                "bytes": bytes_step, "distinct_experts_per_layer": sum(distinct) / len(distinct), "kv_ctx": kv_ctx}
+
+    # ---- headline: decode at the default batch ------------------------------------------
+    main = timed_decode(batch, PROMPT_LEN, args.warmup, args.steps, sample_clocks=True)
+    points = {}
+    for b in (1, 64):
+        r = timed_decode(b, PROMPT_LEN, max(3, args.warmup), max(5, args.steps // 2))
+        points[f"decode_b{b}"] = round(r["tok_s"], 2)
+        points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+
+    # ---- prefill of one 2,048-token prompt ----------------------------------------------
+    prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
+    pre_ms = []
+    for i in range(3):
+        runner.admit(f"p{i}")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(f"p{i}", prompt, [PROMPT_LEN - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+        runner.release(f"p{i}")
+    pms = min(pre_ms[1:])
+    flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
+    prefill = {"value": round(PROMPT_LEN * 1000.0 / pms, 1), "tokens": PROMPT_LEN, "ms": round(pms, 3),
+               "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
+
+    # ---- end to end through the public API -----------------------------------------------
+    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 2, ignore_eos=True)
+    for _ in range(batch):
+        llm.add_request(torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist(), sp)
+    while any(not s.in_decode for s in llm.scheduler.running) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(args.warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _, n = llm.step()
+        assert n == -batch, n
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    while not llm.is_finished():
+        llm.step()
+    h2d = 4 * (4 * (-(-batch // 4) * 4) + (-(-(batch + 1) // 4) * 4) + 4)      # packed int32 step metadata
+    e2e = {"value": round(batch * args.steps / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * batch}
+
+    hbm = main["bytes"] / (main["ms"] * 1e-3) / 1e9
+    return {
+        "metric": "decode tokens/s (MiniMax M2 layer sizes, batch 8, context 4096)",
+        "value": round(main["tok_s"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main["ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0,0.02) seed 2)",
+        "impl": "ours",
+        "config": {"model": "MiniMax-M2 layer sizes", "layers": args.layers, "layers_full_model": FULL_MODEL_LAYERS,
+                   "hidden": 3072, "q_heads": 48, "kv_heads": 8, "head_dim": 128, "rotary_dim": 64,
+                   "experts": 256, "top_k": 8, "expert_inter": 1536, "vocab": 200064, "global_batch": batch,
+                   "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE, "parallelism": "1gpu",
+                   "l2": "working set per step >> L2 (no flush needed)", "cache": "prefilled without a forward pass"},
+        "clocks": main["clocks"], "e2e": e2e, "gpu_launches": main["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(hbm, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(hbm / pk["hbm_gbs"], 4), "peaks": pk["source"],
+                     "distinct_experts_per_layer": round(main["distinct_experts_per_layer"], 1)},
+        "points": points, "setup_s": round(setup_s, 1),
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=BENCH_LAYERS)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference's MiniMax M2 path is FP8-only and its fused expert kernel requires SM90 "
+                          "(src/sparseengine/models/spec.py:161-173, src/sparseengine/operators/moe.py:777); "
+                          "it has no bfloat16 M2 path to time on a B200"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -23,12 +23,19 @@ _ERRORS = {-2: "a size this kernel does not support", -3: "an inconsistent argum
 
 _fns: dict = {}
 
+# Kernels launched through these bindings since the process started (a launcher that
+# starts two kernels counts two).  Benchmarks read the difference around a timed region.
+KERNELS_PER_CALL = {"se_moe_route_build": 2}
+launch_count = 0
+
 
 def library():
     return _build.load()
 
 
 def _fn(name: str, sig: str):
+    global launch_count
+    launch_count += KERNELS_PER_CALL.get(name, 1)
     f = _fns.get(name)
     if f is None:
         f = getattr(library(), name)
