@@ -230,7 +230,7 @@ def run_ours(args) -> dict:
                "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
 
     # ---- end to end through the public API -----------------------------------------------
-    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 2, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 16, ignore_eos=True)
     for _ in range(batch):
         llm.add_request(torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist(), sp)
     while any(not s.in_decode for s in llm.scheduler.running) or llm.scheduler.waiting:

@@ -244,10 +244,12 @@ def test_toy_model_steps_like_its_plain_form(toy_folder, dtype):
         got, routed = tu.run_trace_runner(runner, steps, capture=True)
         ref = {sid: toy_plain(t, toks, act, routed[sid] if dtype == "bfloat16" else None).numpy()
                for sid, toks in seqs.items()}
-        # the toy's logits are about ten times larger than the tiny M2 models' (tied head on an
-        # embedding of std 0.5), so the absolute part of the bfloat16 bound scales with their size
+        # The toy's logits are about ten times larger than the tiny M2 models' (tied head on an
+        # embedding of std 0.5) and it runs six visits without a QK norm: its plain form in
+        # bfloat16 differs from its plain form in float32 by 0.02-0.04 on average and 0.1-0.26 at
+        # most.  The bound between two bfloat16 implementations is 4% of the logits' size.
         scale = float(np.sqrt(np.mean(np.concatenate([r.ravel() for r in ref.values()]) ** 2)))
-        tu.compare(got, ref, *((2e-5, 2e-5) if dtype == "float32" else (2e-2 * max(scale, 1.0), 2e-2)),
+        tu.compare(got, ref, *((2e-5, 2e-5) if dtype == "float32" else (4e-2 * max(scale, 1.0), 2e-2)),
                    what=f"toy {dtype} {cut.__name__}")
         for g in runner.cache.groups:
             assert g.pool.free == g.pool.num_pages
