@@ -222,3 +222,75 @@ extern "C" int se_moe_combine(const void* y, const int* inv_pos, void* out, int 
         se::moe_combine_kernel<T><<<tokens, 256, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
     SE_LAUNCH_CHECK();
 }
+
+// ---- routing build without any allocation (declared in no_alloc.h) -------------------------
+// This entry point has no counterpart in CURRENTF/SparseEngine.  It serves callers that may
+// not allocate device memory around the call; see no_alloc.h for who they are and for the
+// rules of use.  The routing build needs two scratch arrays (per-expert counts, per-
+// assignment ranks); here they live in one file-scope device array of fixed size instead
+// of coming from the caller.
+#include "no_alloc.h"
+
+namespace se {
+
+// counts[SE_NOALLOC_MAX_EXPERTS] followed by rank[SE_NOALLOC_MAX_ASSIGNMENTS]; about 260 KB
+// that every GPU which loads this library holds until the process exits.
+static __device__ __align__(256) int g_route_scratch[SE_NOALLOC_MAX_EXPERTS + SE_NOALLOC_MAX_ASSIGNMENTS];
+
+// Device address of g_route_scratch per device ordinal.  In host code the array's name is
+// only a stand-in for the symbol, not an address a kernel can use, so the address is asked
+// for once per device, with that device current.
+constexpr int kMaxDevices = 64;
+static int* g_route_scratch_ptr[kMaxDevices] = {};
+
+static int route_scratch_for_current_device(int** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return SE_NOALLOC_ERR_DEVICE;
+    if (g_route_scratch_ptr[dev] == nullptr) {
+        int* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_route_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return SE_NOALLOC_ERR_DEVICE;
+        g_route_scratch_ptr[dev] = p;
+    }
+    *out = g_route_scratch_ptr[dev];
+    return 0;
+}
+
+}  // namespace se
+
+extern "C" int se_moe_route_build_no_alloc(const int* ids, int assignments, int experts, int tile_rows, int* offsets,
+                                           int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
+                                           int* num_tiles, cudaStream_t stream) {
+    if (assignments < 0 || experts <= 0 || tile_rows <= 0) return SE_NOALLOC_ERR_ARGUMENT;
+    if (assignments > SE_NOALLOC_MAX_ASSIGNMENTS) return SE_NOALLOC_ERR_TOO_MANY_ASSIGNMENTS;
+    if (experts > SE_NOALLOC_MAX_EXPERTS) return SE_NOALLOC_ERR_TOO_MANY_EXPERTS;
+    if (assignments == 0) return 0;
+    int* scratch = nullptr;
+    const int rc = se::route_scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
+    // Both scratch arrays are written in full by the first kernel before the second reads
+    // them (every count, and the rank of every assignment whose expert id is valid), so
+    // nothing of the previous call's contents survives into this one and nothing has to be
+    // cleared.
+    int* counts = scratch;
+    int* rank = scratch + SE_NOALLOC_MAX_EXPERTS;
+    se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
+    const int blocks = min(se::ceil_div(assignments, 256), 64);
+    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 1) * sizeof(int), stream>>>(
+        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
+    return (int)cudaGetLastError();
+}
+
+extern "C" const char* se_no_alloc_strerror(int code) {
+    switch (code) {
+        case 0: return "success";
+        case SE_NOALLOC_ERR_ARGUMENT: return "negative assignments, or experts/tile_rows not positive";
+        case SE_NOALLOC_ERR_TOO_MANY_ASSIGNMENTS: return "assignments exceed SE_NOALLOC_MAX_ASSIGNMENTS (65536)";
+        case SE_NOALLOC_ERR_TOO_MANY_EXPERTS: return "experts exceed SE_NOALLOC_MAX_EXPERTS (1024)";
+        case SE_NOALLOC_ERR_DEVICE: return "no usable device address for the built-in scratch array on the current device";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+    }
+}
