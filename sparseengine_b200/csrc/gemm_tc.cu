@@ -1,0 +1,420 @@
+// Tensor-core GEMMs for sm_100a: TMA (cp.async.bulk.tensor) -> shared memory (128-byte
+// swizzle) -> tcgen05.mma with the accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+// One kernel, three epilogues, all "weights on the M side" (swap-AB): a CTA owns 128 rows
+// of a weight matrix W[n, k] and up to NT activation rows X[t, k] and computes
+// D[n, t] = sum_k W[n, k] X[t, k].  Decode and small expert batches have few rows per
+// expert and are bound by streaming W, so W takes the 128-wide M side of the MMA and the
+// few tokens the N side (16..128); large prefill tiles use NT = 128.
+//
+//   MODE_GATE_UP  grouped: W = w13[e] (gate rows, then up rows); two accumulators share the
+//                 X tile; epilogue rounds gate/up to bf16, SiLU in fp32, product -> act[p, n]
+//   MODE_DOWN     grouped: W = w2[e]; epilogue multiplies by the routing weight -> y[p, n]
+//   MODE_DENSE    one weight matrix for all rows -> out[t, n]
+//
+// Rows are "sorted positions" p: the routing build sorts the (token, slot) assignments by
+// expert and lists tiles (expert, first row).  X for MODE_GATE_UP is the token rows
+// gathered into that order (se_moe_permute_rows).  Rounding points follow the reference's
+// bf16 pipeline (src/sparseengine/kernels/triton/moe.py:557-563,726-732,1374-1440).
+//
+// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
+// issues the MMAs (one elected lane), warps 2-5 run the epilogue (one TMEM lane quarter
+// each).  Every wait on an mbarrier is bounded; on a timeout the CTA records an error code,
+// drains its outstanding copies, frees its tensor memory and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace se {
+namespace tc {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;          // bf16 elements: 128 bytes, one swizzle span
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kTileABytes = kBlockM * kBlockK * 2;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+enum Mode { MODE_GATE_UP = 0, MODE_DOWN = 1, MODE_DENSE = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false on timeout or when another role of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (tile bases are 1024-byte aligned).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset: 1024 bytes between 8-row groups
+    d |= (uint64_t)1 << 46;                 // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                 // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, both operands K-major.
+__device__ __forceinline__ uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr)
+        : "memory");
+}
+
+struct Params {
+    const int* sorted;          // [assignments] flat assignment of each sorted row (MODE_DOWN: routing weight index)
+    const int* offsets;         // [experts + 1]
+    const int* tile_expert;     // null: dense (one weight matrix, tiles are consecutive row blocks)
+    const int* tile_row0;
+    const int* num_tiles;
+    const float* route_w;       // [assignments] (MODE_DOWN)
+    __nv_bfloat16* out;         // [rows, n_out]
+    int* error;                 // device word: 0 ok, else a code of the first failure
+    int n_out;                  // weight rows per expert that are outputs (I for gate/up, H for down)
+    int k_dim;
+    int w_rows_per_expert;      // rows of the 2-D weight view per expert (2I or H)
+    int up_offset;              // row offset of the "up" half (MODE_GATE_UP)
+    int total_rows;             // dense: number of activation rows
+    int nt;                     // activation rows per tile: 16, 32, 64 or 128
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+    int tile = blockIdx.y, expert = 0, row0, row_end;
+    if (p.tile_expert != nullptr) {
+        if (tile >= p.num_tiles[0]) return;
+        expert = p.tile_expert[tile];
+        row0 = p.tile_row0[tile];
+        row_end = p.offsets[expert + 1];
+    } else {
+        row0 = tile * p.nt;
+        row_end = p.total_rows;
+        if (row0 >= row_end) return;
+    }
+    const int n0 = blockIdx.x * kBlockM;
+    const int nt = p.nt;
+    const int valid = min(nt, row_end - row0);
+    const int num_kb = (p.k_dim + kBlockK - 1) / kBlockK;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t stage_bytes = NA * kTileABytes + nt * kBlockK * 2;
+    __shared__ __align__(8) uint64_t bars[2 * kStages + 1];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+    __shared__ float route_s[128];
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]), accum = smem_u32(&bars[2 * kStages]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    uint32_t cols = 32;
+    while ((int)cols < NA * nt) cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                     "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            const int wy = expert * p.w_rows_per_expert + n0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t ph = (kb / kStages) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) {
+                    abort_s = 1;
+                    atomicCAS(p.error, 0, 1);
+                    break;
+                }
+                const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+                mbar_expect_tx(full0 + 8 * s, stage_bytes);
+                tma_load_2d(a, &map_w, full0 + 8 * s, kb * kBlockK, wy);
+                if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * s, kb * kBlockK, wy + p.up_offset);
+                tma_load_2d(a + NA * kTileABytes, &map_x, full0 + 8 * s, kb * kBlockK, row0);
+                issued = kb + 1;
+            }
+            if (abort_s) {
+                // let copies already in flight land before the CTA's shared memory goes away
+                for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
+                    const uint32_t bar = full0 + 8 * (kb % kStages);
+                    const uint32_t ph = (kb / kStages) & 1;
+                    for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(bar, ph); ++i) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(nt);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t ph = (kb / kStages) & 1;
+                if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) {
+                    abort_s = 1;
+                    atomicCAS(p.error, 0, 2);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint64_t da = smem_desc(a), db = smem_desc(a + NA * kTileABytes);
+#pragma unroll
+                for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                    const uint64_t adv = (uint64_t)((kk * kUmmaK * 2) >> 4);      // 32 bytes per K step
+                    const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                    umma(tmem_base, da + adv, db + adv, idesc, acc);
+                    if (NA == 2) umma(tmem_base + (uint32_t)nt, smem_desc(a + kTileABytes) + adv, db + adv, idesc, acc);
+                }
+                umma_commit(empty0 + 8 * s);     // frees the stage when these MMAs have read it
+            }
+            umma_commit(accum);                  // arrives when every MMA above has finished
+        }
+    } else {
+        const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
+        const int et = threadIdx.x - 64;         // 0..127 among the epilogue threads
+        if (MODE == MODE_DOWN) {
+            if (et < nt) route_s[et] = et < valid ? p.route_w[p.sorted[row0 + et]] : 0.f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        const bool ready = mbar_wait(accum, 0, &abort_s);
+        if (!ready) {
+            abort_s = 1;
+            atomicCAS(p.error, 0, 3);
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int n = n0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            for (int c0 = 0; c0 < nt; c0 += 16) {
+                if (c0 >= valid) break;          // warp-uniform
+                uint32_t g[16], u[16];
+                tmem_ld16(taddr + c0, g);
+                if (NA == 2) tmem_ld16(taddr + nt + c0, u);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.n_out) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j >= valid) break;
+                        float v = __uint_as_float(g[j]);
+                        if (MODE == MODE_GATE_UP) {
+                            const float gate = round_act<__nv_bfloat16>(v);
+                            const float up = round_act<__nv_bfloat16>(__uint_as_float(u[j]));
+                            v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
+                        } else if (MODE == MODE_DOWN) {
+                            v *= route_s[c0 + j];
+                        }
+                        p.out[(size_t)(row0 + c0 + j) * p.n_out + n] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(cols) : "memory");
+    }
+}
+
+// out[p, :] = x[sorted[p] / top_k, :]  (activation rows gathered into expert order)
+__global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted,
+                                    __nv_bfloat16* __restrict__ out, int width, int top_k) {
+    const uint4* src = (const uint4*)(x + (size_t)(sorted[blockIdx.x] / top_k) * width);
+    uint4* dst = (uint4*)(out + (size_t)blockIdx.x * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    uint64_t rows, cols;
+    uint32_t box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (k.rows * 1000003u) ^ (k.cols * 10007u) ^ k.box_rows;
+    }
+};
+
+// 2-D bf16 row-major [rows, cols] -> map with box [box_rows, 64 cols], 128-byte swizzle.
+static int make_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return SE_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return SE_ERR_ARGUMENT;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int MODE>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
+    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+    const size_t smem = (size_t)kStages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(ceil_div(p.n_out, kBlockM), tiles);
+    gemm_tc_kernel<MODE><<<grid, kThreads, smem, stream>>>(mw, mx, p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace tc
+}  // namespace se
+
+using namespace se::tc;
+
+// 1 if the tensor-core path takes these sizes (bf16 only; row pitches must be 16-byte
+// multiples for TMA), else 0.
+extern "C" int se_gemm_tc_supported(int k_dim, int n_out, int nt) {
+    return (k_dim % 8 == 0 && k_dim >= 8 && n_out >= 1 && (nt == 16 || nt == 32 || nt == 64 || nt == 128)) ? 1 : 0;
+}
+
+extern "C" int se_moe_permute_rows(const void* x, const int* sorted, void* out, int rows, int width, int top_k,
+                                   cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width % 8) return SE_ERR_UNSUPPORTED;
+    permute_rows_kernel<<<rows, 128, 0, stream>>>((const __nv_bfloat16*)x, sorted, (__nv_bfloat16*)out, width, top_k);
+    SE_LAUNCH_CHECK();
+}
+
+// Grouped expert GEMM on tensor cores (bf16).
+//   mode 0: a = x rows in sorted order [assignments, k_dim]; w = w13 [experts, 2*n_out, k_dim]; out [assignments, n_out]
+//   mode 1: a = act [assignments, k_dim];                    w = w2 [experts, n_out, k_dim];    out [assignments, n_out]
+// The tile list must have been built with tile_rows = nt.
+extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
+                                      const int* tile_expert, const int* tile_row0, const int* num_tiles,
+                                      const float* route_w, void* out, int* error, int assignments, int experts,
+                                      int max_tiles, int n_out, int k_dim, int nt, cudaStream_t stream) {
+    if (assignments <= 0 || max_tiles <= 0) return 0;
+    if (!se_gemm_tc_supported(k_dim, n_out, nt) || (mode != 0 && mode != 1)) return SE_ERR_UNSUPPORTED;
+    const int w_rows = mode == 0 ? 2 * n_out : n_out;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, (uint64_t)experts * w_rows, k_dim, kBlockM);
+    if (rc) return rc;
+    rc = make_map(&mx, a, assignments, k_dim, nt);
+    if (rc) return rc;
+    Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
+             n_out,  k_dim,   w_rows,      n_out,     assignments, nt};
+    return mode == 0 ? launch<MODE_GATE_UP>(mw, mx, p, max_tiles, stream) : launch<MODE_DOWN>(mw, mx, p, max_tiles, stream);
+}
+
+// Dense projection on tensor cores: out[rows, n_out] = x[rows, k_dim] · w[n_out, k_dim]ᵀ (bf16, fp32 accumulate).
+extern "C" int se_gemm_tc_dense(const void* x, const void* w, void* out, int* error, int rows, int n_out, int k_dim,
+                                int nt, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!se_gemm_tc_supported(k_dim, n_out, nt)) return SE_ERR_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, n_out, k_dim, kBlockM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, rows, k_dim, nt);
+    if (rc) return rc;
+    Params p{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (__nv_bfloat16*)out, error,
+             n_out,   k_dim,   n_out,   0,       rows,    nt};
+    return launch<MODE_DENSE>(mw, mx, p, se::ceil_div(rows, nt), stream);
+}

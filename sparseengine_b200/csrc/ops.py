@@ -199,3 +199,73 @@ def moe_combine(y, inv_pos, out, top_k: int):
         _ptr(y, out.dtype, "y"), _ptr(inv_pos, torch.int32, "inv_pos"), _ptr(out), tokens, hidden, top_k,
         dtype_code(out.dtype), _stream()), "moe_combine")
     return out
+
+
+# ---- tensor-core GEMMs (bf16; csrc/gemm_tc.cu) ---------------------------------------------
+
+_tc_error = {}
+
+
+def tc_error_flag(device) -> torch.Tensor:
+    """The device word the tensor-core kernels write when one of their bounded waits runs
+    out (0 = all fine).  One per device, created on first use."""
+    key = torch.device(device)
+    t = _tc_error.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=key)
+        _tc_error[key] = t
+    return t
+
+
+def tc_check(device) -> None:
+    """Raise if a tensor-core kernel gave up on a wait (reads one word from the device)."""
+    t = _tc_error.get(torch.device(device))
+    if t is not None:
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise RuntimeError(f"a tensor-core kernel timed out waiting on a barrier (role code {code}); "
+                               "its results are not valid")
+
+
+def gemm_tc_supported(k_dim: int, n_out: int, nt: int = 16) -> bool:
+    f = library().se_gemm_tc_supported
+    f.restype = _I
+    f.argtypes = [_I, _I, _I]
+    return bool(f(k_dim, n_out, nt))
+
+
+def moe_tile_rows_tc(assignments: int, experts: int) -> int:
+    """Activation rows per tile for the tensor-core grouped GEMM: about twice the mean
+    number of rows per expert, a power of two in [16, 128]."""
+    want = max(1, -(-2 * assignments // max(experts, 1)))
+    nt = 16
+    while nt < want and nt < 128:
+        nt *= 2
+    return nt
+
+
+def moe_permute_rows(x, sorted_rows, out, top_k: int):
+    rows, width = out.shape
+    _check(_fn("se_moe_permute_rows", "pppiiip")(
+        _ptr(x, torch.bfloat16, "x"), _ptr(sorted_rows, torch.int32, "sorted"), _ptr(out, torch.bfloat16, "out"),
+        rows, width, top_k, _stream()), "moe_permute_rows")
+    return out
+
+
+def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, nt):
+    _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiii" "p")(
+        mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
+        _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
+        _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(tc_error_flag(a.device)),
+        a.shape[0], experts, max_tiles, n_out, k_dim, nt, _stream()), "moe_grouped_gemm_tc")
+    return out
+
+
+def gemm_tc_dense(x, w, out, nt: int = 128):
+    rows, k_dim = x.shape
+    n_out = w.shape[0]
+    _check(_fn("se_gemm_tc_dense", "pppp" "iiii" "p")(
+        _ptr(x, torch.bfloat16, "x"), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
+        _ptr(tc_error_flag(x.device)), rows, n_out, k_dim, nt, _stream()), "gemm_tc_dense")
+    return out
