@@ -355,7 +355,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     const size_t smem = (size_t)kStages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kStages * (NA * kTileABytes + 128 * kBlockK * 2) + 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }

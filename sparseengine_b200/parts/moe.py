@@ -22,11 +22,21 @@ class _RoutedSwiGLU(FeedForward):
     hidden: int
     inter: int
 
+    # None: tensor cores whenever the sizes allow (bfloat16, row pitches that TMA takes);
+    # False: always the CUDA-core kernels (the float32 path uses them in any case).
+    use_tensor_cores = None
+
+    def tensor_cores_usable(self, x) -> bool:
+        if self.use_tensor_cores is False or x.dtype != torch.bfloat16:
+            return False
+        return ops.gemm_tc_supported(self.hidden, self.inter) and ops.gemm_tc_supported(self.inter, self.hidden)
+
     def run_experts(self, x, ids, weights):
         tokens = x.shape[0]
         a = tokens * self.top_k
         dev = x.device
-        tile_rows = ops.moe_plain_tile_rows()
+        tc = self.tensor_cores_usable(x)
+        tile_rows = ops.moe_tile_rows_tc(a, self.num_experts) if tc else ops.moe_plain_tile_rows()
         max_tiles = ops.moe_max_tiles(a, self.num_experts, tile_rows)
         i32 = dict(dtype=torch.int32, device=dev)
         ws = {"counts": torch.empty(self.num_experts, **i32), "rank": torch.empty(a, **i32),
@@ -35,11 +45,19 @@ class _RoutedSwiGLU(FeedForward):
               "tile_row0": torch.empty(max_tiles, **i32), "num_tiles": torch.empty(1, **i32)}
         ops.moe_route_build(ids, self.num_experts, tile_rows, ws)
         act = torch.empty(a, self.inter, dtype=x.dtype, device=dev)
-        ops.moe_grouped_gemm_plain(0, x, self.w13, ws, None, act, max_tiles=max_tiles, n_out=self.inter,
-                                   k_dim=self.hidden, top_k=self.top_k)
         y = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
-        ops.moe_grouped_gemm_plain(1, act, self.w2, ws, weights, y, max_tiles=max_tiles, n_out=self.hidden,
-                                   k_dim=self.inter, top_k=self.top_k)
+        if tc:
+            xs = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
+            ops.moe_permute_rows(x, ws["sorted"], xs, self.top_k)
+            ops.moe_grouped_gemm_tc(0, xs, self.w13, ws, None, act, experts=self.num_experts, max_tiles=max_tiles,
+                                    n_out=self.inter, k_dim=self.hidden, nt=tile_rows)
+            ops.moe_grouped_gemm_tc(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,
+                                    n_out=self.hidden, k_dim=self.inter, nt=tile_rows)
+        else:
+            ops.moe_grouped_gemm_plain(0, x, self.w13, ws, None, act, max_tiles=max_tiles, n_out=self.inter,
+                                       k_dim=self.hidden, top_k=self.top_k)
+            ops.moe_grouped_gemm_plain(1, act, self.w2, ws, weights, y, max_tiles=max_tiles, n_out=self.hidden,
+                                       k_dim=self.inter, top_k=self.top_k)
         out = torch.empty(tokens, self.hidden, dtype=x.dtype, device=dev)
         ops.moe_combine(y, ws["inv_pos"], out, self.top_k)
         return out

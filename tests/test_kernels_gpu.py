@@ -231,11 +231,18 @@ def test_router_tie_order_nan_and_softmax():
     torch.testing.assert_close(w.cpu(), 2.5 * p.gather(1, ids.cpu().long()), atol=1e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("path", ["cuda_cores", "tensor_cores"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,hidden,inter,experts,top_k", [
-    (5, 64, 32, 4, 2), (70, 96, 48, 8, 3), (33, 80, 40, 6, 4), (130, 200, 72, 16, 5), (1, 64, 32, 4, 2)])
-def test_routed_experts_plain(dtype, tokens, hidden, inter, experts, top_k):
+    (5, 64, 32, 4, 2), (70, 96, 48, 8, 3), (33, 80, 40, 6, 4), (130, 200, 72, 16, 5), (1, 64, 32, 4, 2),
+    (300, 264, 136, 3, 2)])
+def test_routed_experts(dtype, tokens, hidden, inter, experts, top_k, path):
+    """Grouped gate/up + SwiGLU, grouped down x routing weight and the combine, on CUDA cores
+    (any dtype) and on tensor cores (bfloat16: TMA + tcgen05), against the plain loop."""
+    if path == "tensor_cores" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernels are bfloat16 kernels")
     from sparseengine_b200.config.specs import MoESpec
+    from sparseengine_b200.csrc import ops
     from sparseengine_b200.parts.moe import SparseMoE
     x = rnd(tokens, hidden, dtype=dtype, seed=1)
     w13 = rnd(experts, 2 * inter, hidden, dtype=dtype, scale=0.1, seed=2)
@@ -249,7 +256,10 @@ def test_routed_experts_plain(dtype, tokens, hidden, inter, experts, top_k):
     wt = torch.rand(tokens, top_k, generator=g).to(DEV)
     part = SparseMoE(MoESpec(hidden_size=hidden, num_experts=experts, top_k=top_k, intermediate_size=inter), dtype)
     part.bind({"w13": w13, "w2": w2})
+    part.use_tensor_cores = None if path == "tensor_cores" else False
+    assert part.tensor_cores_usable(x) == (path == "tensor_cores")
     out = part.run_experts(x, ids, wt)
+    ops.tc_check(DEV)
     ref = plain_m2.experts(x.float().cpu(), ids.cpu().long(), wt.cpu(), w13[:, :inter].float().cpu(),
                            w13[:, inter:].float().cpu(), w2.float().cpu(), dtype)
     torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype, 1e-5, 2e-2))
@@ -311,3 +321,40 @@ def test_penalties():
     pairs = torch.tensor([[0, 0, 1], [0, 1, 3], [0, 2, 3], [1, 3, 2]], dtype=torch.int32, device=DEV).view(-1)
     sops.apply_penalties(logits, pairs, 4, torch.tensor([2.0, 1.0], device=DEV), torch.tensor([0.5, 0.25], device=DEV))
     assert logits.cpu().tolist() == [[0.5, -4.5, 1.0, 0.5], [1.0, -2.0, 3.0, 0.25]]
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 64, 700])
+def test_tensor_core_experts_at_m2_layer_sizes(tokens):
+    """256 experts, top-8, width 3072, expert width 1536: the tensor-core path against the
+    CUDA-core path of the same engine (the plain loop on a CPU would take minutes)."""
+    from sparseengine_b200.config.specs import MoESpec
+    from sparseengine_b200.csrc import ops
+    from sparseengine_b200.parts.moe import SparseMoE
+    hidden, inter, experts, top_k = 3072, 1536, 256, 8
+    g = torch.Generator(device=DEV).manual_seed(1)
+    w13 = (torch.randn(experts, 2 * inter, hidden, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(experts, hidden, inter, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    x = torch.randn(tokens, hidden, generator=g, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(experts, generator=g, device=DEV)[:top_k] for _ in range(tokens)]).int()
+    wt = torch.rand(tokens, top_k, generator=g, device=DEV)
+    part = SparseMoE(MoESpec(hidden_size=hidden, num_experts=experts, top_k=top_k, intermediate_size=inter),
+                     torch.bfloat16)
+    part.bind({"w13": w13, "w2": w2})
+    fast = part.run_experts(x, ids, wt)
+    ops.tc_check(DEV)
+    part.use_tensor_cores = False
+    slow = part.run_experts(x, ids, wt)
+    torch.testing.assert_close(fast.float(), slow.float(), atol=2e-3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("rows,n_out,k_dim,nt", [(1, 128, 64, 16), (16, 8192, 3072, 16), (100, 384, 200, 32),
+                                                 (333, 3072, 6144, 128), (64, 1000, 3072, 64)])
+def test_tensor_core_dense_gemm(rows, n_out, k_dim, nt):
+    from sparseengine_b200.csrc import ops
+    x = rnd(rows, k_dim, dtype=torch.bfloat16, scale=0.5, seed=1)
+    w = rnd(n_out, k_dim, dtype=torch.bfloat16, scale=0.1, seed=2)
+    out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_dense(x, w, out, nt)
+    ops.tc_check(DEV)
+    ref = plain_m2.linear(x.float().cpu(), w.float().cpu(), torch.bfloat16)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
