@@ -205,6 +205,9 @@ def run_ours(args) -> dict:
 
     # ---- headline: decode at the default batch ------------------------------------------
     main = timed_decode(batch, PROMPT_LEN, args.warmup, args.steps, sample_clocks=True)
+    if args.only_decode:
+        return {"metric": "decode tokens/s", "value": round(main["tok_s"], 2), "ms_per_step": round(main["ms"], 4),
+                "layers": args.layers, "global_batch": batch, "gpu_launches": main["launches"], "partial": True}
     points = {}
     for b in (1, 64):
         r = timed_decode(b, PROMPT_LEN, max(3, args.warmup), max(5, args.steps // 2))
@@ -279,6 +282,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=BENCH_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only-decode", action="store_true",
+                    help="time the headline decode only (no points, prefill or end-to-end run): for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
