@@ -1,0 +1,329 @@
+// Paged decode attention for bfloat16, split over the keys (flash decoding): one CTA per
+// (query token, KV head, key split).  The query heads that share the KV head (the GQA
+// group, up to 16) are the 16 rows of m16n8k16 tensor-core tiles, so keys and values are
+// read once per group.  K/V rows go from their pages to shared memory with cp.async
+// (three 64-key stages), the four warps of the CTA take 16 keys each, keep their own
+// running softmax state in 32-bit and are merged at the end; key splits are merged by a
+// second kernel through their log-sum-exp.
+//
+// Arithmetic as in the plain kernel and the reference's split-KV decode
+// (src/sparseengine/kernels/triton/gqa_flash_decoding_stage1.py:69-120,
+// src/sparseengine/kernels/triton/flash_decoding_stage2.py:27-45): scores and softmax in
+// 32-bit, probabilities rounded to bfloat16 before they multiply V, the output rounded once.
+//
+// Any page size; head sizes 64 and 128 (others use the plain kernel); a window is honoured.
+#include "common.cuh"
+
+namespace se {
+namespace dec {
+
+constexpr int kTileKeys = 64;
+constexpr int kStages = 3;
+constexpr int kWarps = 4;
+constexpr int kThreads = 32 * kWarps;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;     // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `c` of row `r` in a [rows][D] bf16 tile whose chunks are
+// XOR-swizzled within each row (conflict-free ldmatrix).
+template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
+    constexpr int kChunks = D / 8;
+    return (uint32_t)((r * kChunks + (c ^ (r & 7))) * 16);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                   const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
+                   const int* __restrict__ token_seq, const int* __restrict__ positions,
+                   __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
+                   int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split) {
+    constexpr int kChunks = D / 8;                   // 16-byte chunks per row
+    constexpr int kTileBytes = kTileKeys * D * 2;    // one K or V tile
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int t = blockIdx.x;
+    const int group = hq / hkv;
+    const int gtiles = (group + 15) / 16;
+    const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+    const int split = blockIdx.z;
+    const int rows_valid = min(16, group - gt * 16);
+    const int head0 = kvh * group + gt * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int ks = lo + split * keys_per_split;
+    const int ke = min(pos + 1, ks + keys_per_split);
+    const int* row_table = table + (size_t)seq_rows[token_seq[t]] * table_stride;
+    const size_t page_elems = (size_t)2 * hkv * page_size * D;
+    const size_t head_off = (size_t)kvh * page_size * D;
+    const size_t v_off = (size_t)hkv * page_size * D;
+
+    // Q fragments (A operand, 16 rows x D): rows g and g+8 of this lane
+    uint32_t qa[D / 16][4];
+    {
+        const __nv_bfloat16* q0 = q + ((size_t)t * hq + head0 + g) * D;
+        const __nv_bfloat16* q1 = q + ((size_t)t * hq + head0 + g + 8) * D;
+        const bool v0 = g < rows_valid, v1 = g + 8 < rows_valid;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int c = kk * 16 + 2 * t4;
+            qa[kk][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+            qa[kk][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+            qa[kk][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+            qa[kk][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+        }
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int num_tiles = ks < ke ? (ke - ks + kTileKeys - 1) / kTileKeys : 0;
+
+    auto load_tile = [&](int tile, int stage) {
+        uint8_t* kbase = smem + (size_t)stage * 2 * kTileBytes;
+        uint8_t* vbase = kbase + kTileBytes;
+        const int base = ks + tile * kTileKeys;
+        for (int i = threadIdx.x; i < kTileKeys * kChunks; i += kThreads) {
+            const int r = i / kChunks, c = i % kChunks;
+            const int j = base + r;
+            const bool ok = j < ke;
+            const int jj = ok ? j : ks;          // any valid key: the copy is zero-filled when !ok
+            const int page = row_table[jj / page_size];
+            const __nv_bfloat16* src = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            cp_async16(smem_u32(kbase) + tile_off<D>(r, c), src, ok);
+            cp_async16(smem_u32(vbase) + tile_off<D>(r, c), src + v_off, ok);
+        }
+    };
+
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < num_tiles) load_tile(s, s);
+        cp_async_commit();
+    }
+
+    for (int tile = 0; tile < num_tiles; ++tile) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        // prefetch the tile that reuses the stage everyone has just finished with
+        if (tile + kStages - 1 < num_tiles) load_tile(tile + kStages - 1, (tile + kStages - 1) % kStages);
+        cp_async_commit();
+
+        const int stage = tile % kStages;
+        const uint32_t kaddr = smem_u32(smem + (size_t)stage * 2 * kTileBytes);
+        const uint32_t vaddr = kaddr + kTileBytes;
+        const int r0 = warp * 16;                       // this warp's 16 keys of the tile
+        const int key0 = ks + tile * kTileKeys + r0;
+        if (key0 < ke) {                                // warp-uniform
+            float s[2][4] = {};
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t b0, b1, b2, b3;
+                const int mat = lane >> 3, rr = lane & 7;
+                ldmatrix_x4(kaddr + tile_off<D>(r0 + (mat >> 1) * 8 + rr, 2 * kk + (mat & 1)), b0, b1, b2, b3);
+                mma_bf16(s[0], qa[kk], b0, b1);
+                mma_bf16(s[1], qa[kk], b2, b3);
+            }
+            // mask keys beyond the range (rows share the token, hence the range)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
+                    if (j >= ke) s[nt][e] = -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);   // finite: key0 < ke, so some key is valid
+                corr[h] = exp2f((m_run[h] - m_new) * scale_log2);
+                m_run[h] = m_new;
+            }
+            float psum[2] = {0.f, 0.f};
+            uint32_t pa[4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float p0 = exp2f((s[nt][0] - m_run[0]) * scale_log2);
+                const float p1 = exp2f((s[nt][1] - m_run[0]) * scale_log2);
+                const float p2 = exp2f((s[nt][2] - m_run[1]) * scale_log2);
+                const float p3 = exp2f((s[nt][3] - m_run[1]) * scale_log2);
+                psum[0] += p0 + p1;
+                psum[1] += p2 + p3;
+                pa[nt * 2 + 0] = pack_bf16(p0, p1);
+                pa[nt * 2 + 1] = pack_bf16(p2, p3);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int n2 = 0; n2 < D / 16; ++n2) {       // two 8-wide dim tiles per ldmatrix
+                uint32_t b0, b1, b2, b3;
+                const int mat = lane >> 3, rr = lane & 7;
+                ldmatrix_x4_trans(vaddr + tile_off<D>(r0 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
+                mma_bf16(o[2 * n2], pa, b0, b1);
+                mma_bf16(o[2 * n2 + 1], pa, b2, b3);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps (shared memory is free now) ----------------------------------
+    for (int h = 0; h < 2; ++h) {        // row sums live in 4 lanes each
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* sm_m = reinterpret_cast<float*>(smem);                 // [warps][16]
+    float* sm_l = sm_m + kWarps * 16;
+    float* sm_o = sm_l + kWarps * 16;                             // [warps][16][D]
+    if (t4 == 0) {
+        sm_m[warp * 16 + g] = m_run[0];
+        sm_m[warp * 16 + g + 8] = m_run[1];
+        sm_l[warp * 16 + g] = l_run[0];
+        sm_l[warp * 16 + g + 8] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        const int c = i * 8 + 2 * t4;
+        float* r_lo = sm_o + ((size_t)warp * 16 + g) * D + c;
+        float* r_hi = sm_o + ((size_t)warp * 16 + g + 8) * D + c;
+        r_lo[0] = o[i][0]; r_lo[1] = o[i][1];
+        r_hi[0] = o[i][2]; r_hi[1] = o[i][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows_valid * D; i += kThreads) {
+        const int r = i / D, d = i % D;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, sm_m[w * 16 + r]);
+        float acc = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = sm_m[w * 16 + r];
+            const float f = mw == -INFINITY ? 0.f : exp2f((mw - mt) * scale_log2);
+            acc += sm_o[((size_t)w * 16 + r) * D + d] * f;
+            lt += sm_l[w * 16 + r] * f;
+        }
+        const int head = head0 + r;
+        if (splits == 1) {
+            out[((size_t)t * hq + head) * D + d] = __float2bfloat16_rn(acc / lt);
+        } else {
+            const size_t pidx = ((size_t)t * hq + head) * splits + split;
+            part_o[pidx * D + d] = acc;
+            if (d == 0) {
+                part_ml[pidx * 2] = mt == -INFINITY ? -INFINITY : mt * scale_log2;
+                part_ml[pidx * 2 + 1] = lt;
+            }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, int d, int splits) {
+    const size_t th = blockIdx.x;
+    float mt = -INFINITY;
+    for (int s = 0; s < splits; ++s) mt = fmaxf(mt, part_ml[(th * splits + s) * 2]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.f, lt = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(th * splits + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float f = exp2f(ms - mt);
+            acc += part_o[(th * splits + s) * d + i] * f;
+            lt += part_ml[(th * splits + s) * 2 + 1] * f;
+        }
+        out[th * d + i] = __float2bfloat16_rn(acc / lt);
+    }
+}
+
+template <int D>
+static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
+                  const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int tokens,
+                  int hq, int hkv, int page_size, float scale, int window, int splits, int keys_per_split,
+                  cudaStream_t stream) {
+    const int group = hq / hkv;
+    const int gtiles = (group + 15) / 16;
+    const size_t stage_smem = (size_t)kStages * 2 * kTileKeys * D * 2;
+    const size_t merge_smem = (size_t)kWarps * 16 * (D + 2) * sizeof(float);
+    const size_t smem = stage_smem > merge_smem ? stage_smem : merge_smem;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(tokens, hkv * gtiles, splits);
+    attn_decode_kernel<D><<<grid, kThreads, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, token_seq, positions,
+        (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits,
+        keys_per_split);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1) {
+        attn_combine_kernel<<<tokens * hq, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, D, splits);
+        e = cudaGetLastError();
+    }
+    return (int)e;
+}
+
+}  // namespace dec
+}  // namespace se
+
+extern "C" int se_attn_decode_supported(int head_dim, int hq, int hkv) {
+    return ((head_dim == 64 || head_dim == 128) && hkv > 0 && hq % hkv == 0) ? 1 : 0;
+}
+
+// part_o: float [tokens, hq, splits, head_dim]; part_ml: float [tokens, hq, splits, 2] (unused when splits == 1).
+// keys_per_split is a multiple of 64; split s of a token covers keys lo + s*keys_per_split ...
+extern "C" int se_attn_decode(const void* q, const void* cache, const int* table, int table_stride,
+                              const int* seq_rows, const int* token_seq, const int* positions, void* out,
+                              float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int page_size,
+                              float scale, int window, int splits, int keys_per_split, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (!se_attn_decode_supported(head_dim, hq, hkv) || splits < 1 || keys_per_split <= 0 || keys_per_split % 64)
+        return SE_ERR_UNSUPPORTED;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
+    if (head_dim == 64)
+        return se::dec::launch<64>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
+                                   tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, stream);
+    return se::dec::launch<128>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
+                                tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, stream);
+}

@@ -25,7 +25,7 @@ _fns: dict = {}
 
 # Kernels launched through these bindings since the process started (a launcher that
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
-KERNELS_PER_CALL = {"se_moe_route_build": 2}
+KERNELS_PER_CALL = {"se_moe_route_build": 2, "se_attn_decode": 2, "se_router": 2}
 launch_count = 0
 
 
@@ -155,6 +155,8 @@ def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormaliz
     experts = gate.shape[0]
     if gate.shape != (experts, hidden):
         raise ValueError("router weight shape does not match the activations")
+    if logits_out is None:
+        logits_out = torch.empty(tokens, experts, dtype=torch.float32, device=x.device)
     _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ip")(
         _ptr(x, None, "x"), _ptr(gate, torch.float32, "gate"), _ptr(bias, torch.float32, "bias"),
         _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"),
@@ -268,4 +270,41 @@ def gemm_tc_dense(x, w, out, nt: int = 128):
     _check(_fn("se_gemm_tc_dense", "pppp" "iiii" "p")(
         _ptr(x, torch.bfloat16, "x"), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
         _ptr(tc_error_flag(x.device)), rows, n_out, k_dim, nt, _stream()), "gemm_tc_dense")
+    return out
+
+
+# ---- decode attention on tensor cores (bf16; csrc/attention_decode.cu) ----------------------
+
+def attn_decode_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
+    f = library().se_attn_decode_supported
+    f.restype = _I
+    f.argtypes = [_I, _I, _I]
+    return bool(f(head_dim, num_heads, num_kv_heads))
+
+
+def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: int, sms: int = 148):
+    """How many key splits, and how many keys each: enough CTAs for two per SM, at least 256
+    keys per split."""
+    group = num_heads // num_kv_heads
+    base = tokens * num_kv_heads * (-(-group // 16))
+    splits = max(1, min(-(-2 * sms // base), -(-max_keys // 256)))
+    per = -(-(-(-max_keys // splits)) // 64) * 64
+    splits = max(1, -(-max_keys // per))
+    return splits, per
+
+
+def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,
+                scale, window=None, max_keys: int):
+    tokens = q.shape[0]
+    splits, per = attn_decode_plan(tokens, num_heads, num_kv_heads, max_keys)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty(tokens * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(tokens * num_heads * splits * 2, dtype=torch.float32, device=q.device)
+    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "p")(
+        _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
+        table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
+        _ptr(positions, torch.int32, "positions"), _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml),
+        tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per, _stream()),
+        "attn_decode")
     return out

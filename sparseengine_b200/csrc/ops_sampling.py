@@ -8,6 +8,14 @@ from .ops import _check, _fn, _ptr, _stream, dtype_code
 
 def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None):
     rows, vocab = logits.shape
+    if temperature is None and logprob is None and vocab >= 16384:
+        # greedy over a large vocabulary: two stages, many blocks per row
+        pval = torch.empty(rows * 64, dtype=torch.float32, device=logits.device)
+        pidx = torch.empty(rows * 64, dtype=torch.int32, device=logits.device)
+        _check(_fn("se_argmax", "pppp" "iii" "p")(
+            _ptr(logits, None, "logits"), _ptr(out, torch.int32, "out"), _ptr(pval), _ptr(pidx), rows, vocab,
+            dtype_code(logits.dtype), _stream()), "argmax")
+        return out
     _check(_fn("se_sample", "ppppppp" "iii" "p")(
         _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
         _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),

@@ -12,28 +12,23 @@
 
 namespace se {
 
-constexpr int kRouterTokens = 8;   // tokens that share one read of the gate weight
+constexpr int kRouterTokens = 8;   // tokens that share one read of a gate row
+constexpr int kRouterWarps = 8;
 
+// logits[t, e] = sum_i float(x[t, i]) * gate[e, i], 32-bit.  Block (bx, by): tokens
+// bx*8 .. +7 (their rows converted to 32-bit in shared memory), experts by*8*epw .. ; each
+// warp walks `epw` gate rows.
 template <typename T>
-__global__ void router_kernel(const T* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ bias,
-                              int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out,
-                              int tokens, int hidden, int experts, int top_k, int score_fn, int renormalize,
-                              float routed_scale, int tokens_per_block) {
-    extern __shared__ float smem[];
-    float* xs = smem;                                        // [tokens_per_block][hidden]
-    float* prob = xs + (size_t)tokens_per_block * hidden;    // [tokens_per_block][experts]
-    float* score = prob + (size_t)tokens_per_block * experts;
-    int* ranks = (int*)(score + (size_t)tokens_per_block * experts);   // [experts]
-    float* thr_s = (float*)(ranks + experts);
-    const int t0 = blockIdx.x * tokens_per_block;
-    const int nt = min(tokens_per_block, tokens - t0);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-
-    for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x)
-        xs[i] = to_float(x[(size_t)t0 * hidden + i]);
+__global__ void router_logits_kernel(const T* __restrict__ x, const float* __restrict__ gate,
+                                     float* __restrict__ logits, int tokens, int hidden, int experts, int epw) {
+    extern __shared__ float xs[];                            // [kRouterTokens][hidden]
+    const int t0 = blockIdx.x * kRouterTokens;
+    const int nt = min(kRouterTokens, tokens - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t0 * hidden + i]);
     __syncthreads();
-
-    for (int e = warp; e < experts; e += nwarps) {
+    const int e0 = (blockIdx.y * kRouterWarps + warp) * epw;
+    for (int e = e0; e < min(e0 + epw, experts); ++e) {
         float acc[kRouterTokens];
 #pragma unroll
         for (int j = 0; j < kRouterTokens; ++j) acc[j] = 0.f;
@@ -48,106 +43,117 @@ __global__ void router_kernel(const T* __restrict__ x, const float* __restrict__
         for (int j = 0; j < kRouterTokens; ++j) {
             if (j < nt) {
                 const float v = warp_sum(acc[j]);
-                if (lane == 0) prob[j * experts + e] = v;   // logits for now
+                if (lane == 0) logits[(size_t)(t0 + j) * experts + e] = v;
             }
         }
     }
-    __syncthreads();
+}
 
-    for (int j = 0; j < nt; ++j) {
-        float* pj = prob + j * experts;
-        float* sj = score + j * experts;
-        if (score_fn == 1) {   // softmax over experts
-            float mx = -INFINITY;
-            for (int e = threadIdx.x; e < experts; e += blockDim.x) mx = fmaxf(mx, pj[e]);
-            __shared__ float red[33];
-            mx = warp_max(mx);
-            __syncthreads();
-            if (lane == 0) red[warp] = mx;
-            __syncthreads();
-            mx = -INFINITY;
-            for (int w = 0; w < nwarps; ++w) mx = fmaxf(mx, red[w]);
-            float sum = 0.f;
-            for (int e = threadIdx.x; e < experts; e += blockDim.x) sum += expf(pj[e] - mx);
-            sum = block_sum(sum, red);
-            for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-                if (logits_out) logits_out[(size_t)(t0 + j) * experts + e] = pj[e];
-                pj[e] = expf(pj[e] - mx) / sum;
-            }
-        } else {
-            for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-                if (logits_out) logits_out[(size_t)(t0 + j) * experts + e] = pj[e];
-                pj[e] = 1.f / (1.f + expf(-pj[e]));
-            }
-        }
+// One block per token: score function, selection bias, top-k in the reference's order,
+// renormalisation.
+__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                     int* __restrict__ ids, float* __restrict__ weights, int experts, int top_k,
+                                     int score_fn, int renormalize, float routed_scale) {
+    extern __shared__ float sel[];
+    float* pj = sel;                     // [experts] probabilities
+    float* sj = pj + experts;            // [experts] selection scores
+    int* ranks = (int*)(sj + experts);   // [experts]
+    __shared__ float red[33];
+    __shared__ float thr_s;
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const float* lg = logits + (size_t)t * experts;
+    if (score_fn == 1) {   // softmax over experts
+        float mx = -INFINITY;
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) mx = fmaxf(mx, lg[e]);
+        mx = warp_max(mx);
+        if (lane == 0) red[warp] = mx;
         __syncthreads();
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-            float s = pj[e] + (bias ? bias[e] : 0.f);
-            sj[e] = (s == s) ? s : INFINITY;
+        mx = -INFINITY;
+        for (int w = 0; w < nwarps; ++w) mx = fmaxf(mx, red[w]);
+        float sum = 0.f;
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) sum += expf(lg[e] - mx);
+        sum = block_sum(sum, red);
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) pj[e] = expf(lg[e] - mx) / sum;
+    } else {
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) pj[e] = 1.f / (1.f + expf(-lg[e]));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const float s = pj[e] + (bias ? bias[e] : 0.f);
+        sj[e] = (s == s) ? s : INFINITY;
+    }
+    __syncthreads();
+    // rank of e = number of experts that precede it in (score descending, index ascending);
+    // ranks are a permutation, the chosen are the ranks below top_k and the threshold is
+    // the score of rank top_k-1.
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const float s = sj[e];
+        int rank = 0;
+        for (int o = 0; o < experts; ++o) {
+            const float so = sj[o];
+            rank += (so > s) || (so == s && o < e);
         }
-        __syncthreads();
-        // rank of e = number of experts that precede it in (score descending, index
-        // ascending); ranks are a permutation, the chosen are the ranks below top_k and
-        // the threshold is the score of rank top_k-1.
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-            const float s = sj[e];
-            int rank = 0;
-            for (int o = 0; o < experts; ++o) {
-                const float so = sj[o];
-                rank += (so > s) || (so == s && o < e);
-            }
-            ranks[e] = rank;
-            if (rank == top_k - 1) *thr_s = s;
+        ranks[e] = rank;
+        if (rank == top_k - 1) thr_s = s;
+    }
+    __syncthreads();
+    const float thr = thr_s;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        if (ranks[e] >= top_k) continue;
+        // slot order: strictly greater than the threshold by ascending index, then ties
+        // with it by ascending index.
+        const float s = sj[e];
+        int n_greater = 0, before_greater = 0, before_equal = 0;
+        for (int o = 0; o < experts; ++o) {
+            const float so = sj[o];
+            n_greater += so > thr;
+            before_greater += (so > thr) && o < e;
+            before_equal += (so == thr) && o < e && ranks[o] < top_k;
         }
-        __syncthreads();
-        const float thr = *thr_s;
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-            if (ranks[e] >= top_k) continue;
-            // slot order: strictly greater than the threshold by ascending index, then
-            // ties with it by ascending index.
-            const float s = sj[e];
-            int n_greater = 0, before_greater = 0, before_equal = 0;
-            for (int o = 0; o < experts; ++o) {
-                const float so = sj[o];
-                n_greater += so > thr;
-                before_greater += (so > thr) && o < e;
-                before_equal += (so == thr) && o < e && ranks[o] < top_k;
-            }
-            const int slot = s > thr ? before_greater : n_greater + before_equal;
-            ids[(size_t)(t0 + j) * top_k + slot] = e;
-            weights[(size_t)(t0 + j) * top_k + slot] = pj[e];
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float* w = weights + (size_t)(t0 + j) * top_k;
-            float sum = 0.f;
-            for (int s = 0; s < top_k; ++s) sum += w[s];
-            for (int s = 0; s < top_k; ++s) w[s] = (renormalize ? w[s] / sum : w[s]) * routed_scale;
-        }
-        __syncthreads();
+        const int slot = s > thr ? before_greater : n_greater + before_equal;
+        ids[(size_t)t * top_k + slot] = e;
+        weights[(size_t)t * top_k + slot] = pj[e];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float* w = weights + (size_t)t * top_k;
+        float sum = 0.f;
+        for (int s = 0; s < top_k; ++s) sum += w[s];
+        for (int s = 0; s < top_k; ++s) w[s] = (renormalize ? w[s] / sum : w[s]) * routed_scale;
     }
 }
 
 }  // namespace se
 
+// logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
-                         float* logits_out, int tokens, int hidden, int experts, int top_k, int score_fn,
+                         float* logits, int tokens, int hidden, int experts, int top_k, int score_fn,
                          int renormalize, float routed_scale, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (top_k <= 0 || top_k > experts) return SE_ERR_ARGUMENT;
-    int tpb = se::kRouterTokens;
-    while (tpb > 1 && ((size_t)tpb * (hidden + 2 * experts) + experts + 1) * sizeof(float) > 160 * 1024) tpb >>= 1;
-    if (tokens < 4 * 148) tpb = 1;   // few tokens: spread them over the SMs
-    const size_t smem = ((size_t)tpb * (hidden + 2 * experts) + experts + 1) * sizeof(float);
-    if (smem > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
+    const size_t smem = (size_t)se::kRouterTokens * hidden * sizeof(float);
+    const size_t smem_sel = (size_t)experts * 3 * sizeof(float);
+    if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    // few tokens: one gate row per warp (many blocks); many tokens: several rows per warp so
+    // that the token tile in shared memory is reused
+    const int token_blocks = se::ceil_div(tokens, se::kRouterTokens);
+    int epw = 1;
+    while (epw < 8 && token_blocks * se::ceil_div(experts, se::kRouterWarps * epw) > 4 * 148) epw *= 2;
+    dim3 grid(token_blocks, se::ceil_div(experts, se::kRouterWarps * epw));
     SE_DISPATCH_DTYPE(dtype, T, {
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(se::router_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        se::router_kernel<T><<<se::ceil_div(tokens, tpb), 256, smem, stream>>>(
-            (const T*)x, gate, bias, ids, weights, logits_out, tokens, hidden, experts, top_k, score_fn, renormalize,
-            routed_scale, tpb);
+        se::router_logits_kernel<T><<<grid, 32 * se::kRouterWarps, smem, stream>>>((const T*)x, gate, logits, tokens, hidden,
+                                                                                    experts, epw);
     });
+    if (smem_sel > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);
+        if (e != cudaSuccess) return (int)e;
+    }
+    se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(logits, bias, ids, weights, experts, top_k, score_fn,
+                                                                renormalize, routed_scale);
     SE_LAUNCH_CHECK();
 }

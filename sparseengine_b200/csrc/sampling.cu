@@ -162,6 +162,36 @@ __global__ void sample_kernel(const T* __restrict__ logits, const float* __restr
     }
 }
 
+// Greedy over a large vocabulary with few rows: stage 1 reduces `chunks` slices of each row
+// in parallel, stage 2 reduces the partial results (ties still go to the lower index).
+template <typename T>
+__global__ void argmax_partial_kernel(const T* __restrict__ logits, float* __restrict__ pval, int* __restrict__ pidx,
+                                      int vocab, int chunks) {
+    __shared__ ArgMax am[33];
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int a = chunk * per, b = min(vocab, a + per);
+    const T* x = logits + (size_t)row * vocab;
+    ArgMax best{0.f, -1};
+    for (int i = a + threadIdx.x; i < b; i += blockDim.x) best = better(best, ArgMax{to_float(x[i]), i});
+    best = block_argmax(best, am);
+    if (threadIdx.x == 0) {
+        pval[row * chunks + chunk] = best.v;
+        pidx[row * chunks + chunk] = best.i;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out,
+                                    int chunks) {
+    __shared__ ArgMax am[33];
+    const int row = blockIdx.x;
+    ArgMax best{0.f, -1};
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x)
+        best = better(best, ArgMax{pval[row * chunks + i], pidx[row * chunks + i]});
+    best = block_argmax(best, am);
+    if (threadIdx.x == 0) out[row] = best.i;
+}
+
 // pairs: n entries (row, token, flags); flags bit 0 = in prompt or completion (repetition),
 // bit 1 = in completion (presence).  logits is float32 [rows, vocab], changed in place.
 __global__ void penalties_kernel(float* logits, const int* __restrict__ pairs, int n, int vocab,
@@ -194,6 +224,18 @@ extern "C" int se_sample(const void* logits, const float* temperature, const int
     SE_DISPATCH_DTYPE(dtype, T,
         se::sample_kernel<T><<<rows, se::kSampleThreads, 0, stream>>>((const T*)logits, temperature, top_k, top_p,
                                                                       seeds, out, logprob, vocab));
+    SE_LAUNCH_CHECK();
+}
+
+// Greedy tokens only (no log-probabilities).  pval/pidx: workspaces of rows * 64 entries.
+extern "C" int se_argmax(const void* logits, int* out, float* pval, int* pidx, int rows, int vocab, int dtype,
+                         cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int chunks = 64;
+    dim3 grid(rows, chunks);
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::argmax_partial_kernel<T><<<grid, 256, 0, stream>>>((const T*)logits, pval, pidx, vocab, chunks));
+    se::argmax_final_kernel<<<rows, 64, 0, stream>>>(pval, pidx, out, chunks);
     SE_LAUNCH_CHECK();
 }
 

@@ -55,8 +55,21 @@ class PagedAttention(Mixer):
         self.attend(q, attn, step, slot)
         return linear(attn, self.o)
 
+    # Steps with at most this many tokens go to the split-key tensor-core kernel (one CTA per
+    # token, KV head and key split); larger ones are prompt portions.
+    decode_kernel_max_tokens = 512
+    use_tensor_cores = None      # False: always the plain kernel
+
     def attend(self, q, out, step, slot):
         s = self.spec
+        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
+                and step.num_tokens <= self.decode_kernel_max_tokens
+                and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
+            max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
+            ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
+                            num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+                            page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys)
+            return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
                                   page_size=slot.page_size, scale=s.scale, window=s.window)

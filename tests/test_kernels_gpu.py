@@ -274,6 +274,11 @@ def test_sampling_greedy_and_filters(dtype):
     out = torch.empty(6, dtype=torch.int32, device=DEV)
     sops.sample(logits, None, None, None, None, out)
     assert out.cpu().tolist() == logits.float().argmax(-1).cpu().tolist() and int(out[1]) == 77
+    big = rnd(3, 200064, dtype=dtype, scale=2.0, seed=10)          # the two-stage path of large vocabularies
+    big[2, 199999] = big[2, 5] = 60.0
+    out3 = torch.empty(3, dtype=torch.int32, device=DEV)
+    sops.sample(big, None, None, None, None, out3)
+    assert out3.cpu().tolist() == big.float().argmax(-1).cpu().tolist() and int(out3[2]) == 5
     # top-k = 1 and a tiny top-p are greedy whatever the noise
     temp = torch.full((6,), 0.9, device=DEV)
     seeds = torch.arange(6, dtype=torch.int64, device=DEV) + 12345
@@ -361,3 +366,39 @@ def test_tensor_core_dense_gemm(rows, n_out, k_dim, nt):
     ops.tc_check(DEV)
     ref = plain_m2.linear(x.float().cpu(), w.float().cpu(), torch.bfloat16)
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(12, 2, 128, 16, None), (48, 8, 128, 16, None), (6, 6, 64, 8, None),
+                                                  (40, 2, 64, 5, None), (8, 2, 128, 32, 100), (5, 1, 128, 1, None)])
+def test_decode_attention_tensor_cores(hq, hkv, d, page, window):
+    """The split-key tensor-core kernel against the plain attention of the plain
+    implementation: single tokens and short portions, contexts from 1 key to thousands
+    (several key splits), scattered pages, groups of 1..20 query heads per KV head."""
+    from sparseengine_b200.csrc import ops
+    kv_lens, q_lens = [1, 70, 1300, 4100, 257], [1, 3, 1, 1, 2]
+    starts = [kv - ql for kv, ql in zip(kv_lens, q_lens)]
+    dtype = torch.bfloat16
+    table, rows, _, _, cache = _cache_setup(kv_lens, hkv, d, page, dtype)
+    ks = [rnd(n, hkv, d, dtype=dtype, seed=20 + i) for i, n in enumerate(kv_lens)]
+    vs = [rnd(n, hkv, d, dtype=dtype, seed=30 + i) for i, n in enumerate(kv_lens)]
+    for i, n in enumerate(kv_lens):
+        p = torch.arange(n, device=DEV)
+        pg = table[int(rows[i]), (p // page).long()].long()
+        cache[pg, 0, :, (p % page).long()] = ks[i]
+        cache[pg, 1, :, (p % page).long()] = vs[i]
+    t = sum(q_lens)
+    q = rnd(t, hq, d, dtype=dtype, seed=7)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, q_lens)]).int().to(DEV)
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).int().to(DEV)
+    out = torch.empty_like(q)
+    ops.attn_decode(q.view(t, hq * d), cache, table, rows, token_seq, positions, out.view(t, hq * d), num_heads=hq,
+                    num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window, max_keys=max(kv_lens))
+    assert ops.attn_decode_plan(t, hq, hkv, max(kv_lens))[0] > 1          # several key splits are merged
+    ref = _attention_reference(q.float().cpu(), [k.float().cpu() for k in ks], [v.float().cpu() for v in vs], q_lens,
+                               starts, dtype, window)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    one = torch.empty_like(q)                                             # and without splitting
+    plain = torch.empty_like(q)
+    ops.paged_attention_plain(q.view(t, hq * d), cache, table, rows, token_seq, positions, plain.view(t, hq * d),
+                              num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
+    torch.testing.assert_close(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
