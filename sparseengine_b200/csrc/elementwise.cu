@@ -55,6 +55,14 @@ __global__ void table_update_kernel(int* table, int stride, const int* __restric
     if (i < n) table[(size_t)updates[3 * i] * stride + updates[3 * i + 1]] = updates[3 * i + 2];
 }
 
+// The same with the number of triples read from device memory (for replayed CUDA graphs,
+// where the launch is fixed and the count changes from step to step).
+__global__ void table_update_dyn_kernel(int* table, int stride, const int* __restrict__ updates,
+                                        const int* __restrict__ count, int max_n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < min(count[0], max_n)) table[(size_t)updates[3 * i] * stride + updates[3 * i + 1]] = updates[3 * i + 2];
+}
+
 }  // namespace se
 
 extern "C" int se_embed_gather(const void* table, const int* ids, void* out, int tokens, int hidden,
@@ -93,5 +101,12 @@ extern "C" int se_gather_rows(const void* src, const int* idx, void* dst, int ro
 extern "C" int se_table_update(int* table, int stride, const int* updates, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
     se::table_update_kernel<<<se::ceil_div(n, 256), 256, 0, stream>>>(table, stride, updates, n);
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_table_update_dyn(int* table, int stride, const int* updates, const int* count, int max_n,
+                                   cudaStream_t stream) {
+    if (max_n <= 0) return 0;
+    se::table_update_dyn_kernel<<<se::ceil_div(max_n, 256), 256, 0, stream>>>(table, stride, updates, count, max_n);
     SE_LAUNCH_CHECK();
 }

@@ -51,26 +51,45 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
                                    int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ inv_pos,
                                    int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                    int* __restrict__ num_tiles) {
-    extern __shared__ int off[];   // experts + 1 offsets, then experts counts
-    int* cnt = off + experts + 1;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = counts[e];
+    extern __shared__ int off[];   // experts + 1 row offsets, then experts + 1 tile offsets
+    int* toff = off + experts + 1;
+    __shared__ int carry[2];
+    // Exclusive scans of the counts and of the tiles per expert, 256 experts at a time.
+    if (threadIdx.x == 0) carry[0] = carry[1] = 0;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, tiles = 0;
-        for (int e = 0; e < experts; ++e) {
-            off[e] = run;
-            const int c = cnt[e];
-            if (blockIdx.x == 0) {
-                for (int r = 0; r < c; r += tile_rows) {
-                    tile_expert[tiles] = e;
-                    tile_row0[tiles] = run + r;
-                    ++tiles;
-                }
-            }
-            run += c;
+    for (int base = 0; base < experts; base += blockDim.x) {
+        const int e = base + threadIdx.x;
+        const int c = e < experts ? counts[e] : 0;
+        const int tl = (c + tile_rows - 1) / tile_rows;
+        // inclusive scan within the block: warp scans, then the warp totals
+        int vc = c, vt = tl;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int uc = __shfl_up_sync(0xffffffffu, vc, o), ut = __shfl_up_sync(0xffffffffu, vt, o);
+            if (lane >= o) { vc += uc; vt += ut; }
         }
-        off[experts] = run;
-        if (blockIdx.x == 0) num_tiles[0] = tiles;
+        __shared__ int wsum[2][32];
+        if (lane == 31) { wsum[0][warp] = vc; wsum[1][warp] = vt; }
+        __syncthreads();
+        int pc = carry[0], pt = carry[1];
+        for (int w = 0; w < warp; ++w) { pc += wsum[0][w]; pt += wsum[1][w]; }
+        if (e < experts) { off[e] = pc + vc - c; toff[e] = pt + vt - tl; }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) { carry[0] = pc + vc; carry[1] = pt + vt; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { off[experts] = carry[0]; toff[experts] = carry[1]; }
+    __syncthreads();
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+            const int first = toff[e], n = toff[e + 1] - first;
+            for (int i = 0; i < n; ++i) {
+                tile_expert[first + i] = e;
+                tile_row0[first + i] = off[e] + i * tile_rows;
+            }
+        }
+        if (threadIdx.x == 0) num_tiles[0] = toff[experts];
     }
     __syncthreads();
     if (blockIdx.x == 0)
@@ -171,11 +190,11 @@ template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, T* __restrict__ out,
                                    int hidden, int top_k) {
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float s = 0.f;
-        for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
-        out[(size_t)t * hidden + i] = from_float<T>(s);
-    }
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= hidden) return;
+    float s = 0.f;
+    for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
+    out[(size_t)t * hidden + i] = from_float<T>(s);
 }
 
 }  // namespace se
@@ -187,7 +206,7 @@ extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, 
     if (tile_rows <= 0 || experts <= 0) return SE_ERR_ARGUMENT;
     se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
-    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 1) * sizeof(int), stream>>>(
+    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
         ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
     SE_LAUNCH_CHECK();
 }
@@ -219,7 +238,7 @@ extern "C" int se_moe_combine(const void* y, const int* inv_pos, void* out, int 
                               int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::moe_combine_kernel<T><<<tokens, 256, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
+        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 256)), 256, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
     SE_LAUNCH_CHECK();
 }
 
@@ -279,7 +298,7 @@ extern "C" int se_moe_route_build_no_alloc(const int* ids, int assignments, int 
     int* rank = scratch + SE_NOALLOC_MAX_EXPERTS;
     se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
-    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 1) * sizeof(int), stream>>>(
+    se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
         ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
     return (int)cudaGetLastError();
 }

@@ -114,6 +114,12 @@ def table_update(table, updates, n: int):
         "table_update")
 
 
+def table_update_dyn(table, updates, count, max_n: int):
+    _check(_fn("se_table_update_dyn", "pippip")(
+        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(updates, torch.int32, "updates"),
+        _ptr(count, torch.int32, "count"), max_n, _stream()), "table_update_dyn")
+
+
 # ---- attention ---------------------------------------------------------------------------
 
 def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads,

@@ -21,7 +21,7 @@ constexpr int kRouterWarps = 8;
 template <typename T>
 __global__ void router_logits_kernel(const T* __restrict__ x, const float* __restrict__ gate,
                                      float* __restrict__ logits, int tokens, int hidden, int experts, int epw) {
-    extern __shared__ float xs[];                            // [kRouterTokens][hidden]
+    extern __shared__ __align__(16) float xs[];              // [kRouterTokens][hidden]
     const int t0 = blockIdx.x * kRouterTokens;
     const int nt = min(kRouterTokens, tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -33,11 +33,31 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
 #pragma unroll
         for (int j = 0; j < kRouterTokens; ++j) acc[j] = 0.f;
         const float* g = gate + (size_t)e * hidden;
-        for (int i = lane; i < hidden; i += 32) {
-            const float gv = g[i];
+        if ((hidden & 3) == 0) {
+            // 16-byte loads, several in flight per lane
+            const float4* g4 = reinterpret_cast<const float4*>(g);
+            const int n4 = hidden >> 2;
+#pragma unroll 4
+            for (int i = lane; i < n4; i += 32) {
+                const float4 gv = __ldg(g4 + i);
 #pragma unroll
-            for (int j = 0; j < kRouterTokens; ++j)
-                if (j < nt) acc[j] = fmaf(xs[j * hidden + i], gv, acc[j]);
+                for (int j = 0; j < kRouterTokens; ++j) {
+                    if (j < nt) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
+                        acc[j] = fmaf(xv.x, gv.x, acc[j]);
+                        acc[j] = fmaf(xv.y, gv.y, acc[j]);
+                        acc[j] = fmaf(xv.z, gv.z, acc[j]);
+                        acc[j] = fmaf(xv.w, gv.w, acc[j]);
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < hidden; i += 32) {
+                const float gv = g[i];
+#pragma unroll
+                for (int j = 0; j < kRouterTokens; ++j)
+                    if (j < nt) acc[j] = fmaf(xs[j * hidden + i], gv, acc[j]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < kRouterTokens; ++j) {

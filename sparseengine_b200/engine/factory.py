@@ -36,7 +36,7 @@ def require_cuda(device) -> torch.device:
 
 def build_runner(model, *, dtype="bfloat16", page_size: int = 16, num_pages: int, max_rows: int,
                  max_seq_len: Optional[int] = None, device="cuda:0", random_weights: bool = False,
-                 seed: int = 0, random_std: float = 0.02) -> ModelRunner:
+                 seed: int = 0, random_std: float = 0.02, decode_graphs: bool = True) -> ModelRunner:
     """``model`` is a folder (config.json + safetensors) or, with ``random_weights``, a
     folder or a config.json dictionary."""
     device = require_cuda(device)
@@ -52,4 +52,4 @@ def build_runner(model, *, dtype="bfloat16", page_size: int = 16, num_pages: int
         limit = min(limit, spec.max_position)
         cache = CacheManager(m.layout, page_size=page_size, num_pages=num_pages, max_rows=max_rows,
                              max_seq_len=limit, dtype=dt, device=device)
-    return ModelRunner(m, cache, device)
+    return ModelRunner(m, cache, device, decode_graphs=decode_graphs)

@@ -76,7 +76,7 @@ class LLM:
             cache = CacheManager(m.layout, page_size=cfg.page_size, num_pages=num_pages,
                                  max_rows=cfg.max_num_seqs_in_gpu, max_seq_len=self.max_model_len,
                                  dtype=dt, device=device)
-        self.runner = ModelRunner(m, cache, device)
+        self.runner = ModelRunner(m, cache, device, decode_graphs=cfg.decode_graph)
         eos = tuple(cfg.eos_token_ids) or ((cfg.eos,) if cfg.eos >= 0 else ())
         if not eos and not isinstance(model, dict):
             eos = _eos_from_folder(model, raw)

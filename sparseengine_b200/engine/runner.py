@@ -61,8 +61,17 @@ class _Staging:
         self.events[i].record()
 
 
+@dataclass
+class _DecodeGraph:
+    graph: object
+    meta: torch.Tensor            # persistent device copy of the step's packed metadata
+    logits: torch.Tensor          # static output of the captured forward
+
+
 class ModelRunner:
-    def __init__(self, model: Model, cache: CacheManager, device="cuda:0"):
+    KV_BUCKET = 512               # decode graphs are planned for context lengths rounded up to this
+
+    def __init__(self, model: Model, cache: CacheManager, device="cuda:0", decode_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.device = torch.device(device)
@@ -72,6 +81,13 @@ class ModelRunner:
         self._staging = _Staging()
         self.steps = 0
         self.tokens = 0
+        # Decode-only steps (every entry brings one token) replay a CUDA graph per
+        # (batch size, context bucket); anything else runs launch by launch.
+        parts = [p for b in model.blocks for p in b.parts().values()] + [model.final_norm]
+        self.decode_graphs = bool(decode_graphs) and all(getattr(p, "graph_safe", False) for p in parts)
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ---- life cycle of a request -------------------------------------------------------
     def admit(self, seq_id) -> None:
@@ -85,7 +101,8 @@ class ModelRunner:
         """Run one batch.  Returns logits ``[wanted, vocab]`` (activation dtype) in the
         order of the entries and of each entry's ``want``, or ``None`` if nothing is wanted.
 
-        Raises :class:`OutOfPages` (and changes nothing) if the pages do not suffice."""
+        Raises :class:`OutOfPages` (and changes nothing) if the pages do not suffice.
+        The returned tensor may be overwritten by the next step."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -111,17 +128,99 @@ class ModelRunner:
                 self.cache.cancel(s)
             raise
 
-        step, want_rows, updates = self._pack(entries)
-        with torch.cuda.device(self.device):
-            for g, (upd, n) in zip(self.cache.groups, updates):
-                if n:
-                    ops.table_update(g.table, upd, n)
-            logits = self.model.forward(step, self.slots, want_rows)
+        if self.decode_graphs and all(len(e.tokens) == 1 for e in entries):
+            logits = self._step_graph(entries)
+        else:
+            logits = None
+        if logits is None:
+            step, want_rows, updates = self._pack(entries)
+            with torch.cuda.device(self.device):
+                for g, (upd, n) in zip(self.cache.groups, updates):
+                    if n:
+                        ops.table_update(g.table, upd, n)
+                logits = self.model.forward(step, self.slots, want_rows)
         for e in entries:
             self.cache.commit(e.seq_id, len(e.tokens))
         self.steps += 1
-        self.tokens += step.num_tokens
+        self.tokens += sum(len(e.tokens) for e in entries)
         return logits
+
+    # ---- decode steps as replayed CUDA graphs ------------------------------------------
+    def _step_graph(self, entries):
+        """Run a decode-only step through a captured graph.  Returns the logits of the wanted
+        rows, or ``None`` if this step cannot use a graph (too many block-table updates
+        pending, or capture is not possible), in which case nothing has been done."""
+        n = len(entries)
+        groups = self.cache.groups
+        if any(len(g.pending) > n for g in groups):
+            return None
+        q_starts = [self.cache.length(e.seq_id) for e in entries]
+        bound = -(-(max(q_starts) + 1) // self.KV_BUCKET) * self.KV_BUCKET
+        key = (n, bound)
+        # fixed layout for n entries: ids, positions, token->entry, rows, cu_q, kv_len, wanted rows,
+        # then per group one count word and up to n update triples
+        sizes = [n, n, n, n, n + 1, n, n] + [4, 3 * n] * len(groups)
+        offs = np.concatenate(([0], np.cumsum([-(-s // 4) * 4 for s in sizes]))).astype(np.int64)
+        total = int(offs[-1])
+        slot, host = self._staging.get(total)
+        h = host.numpy()
+        rows = [self.cache.row(e.seq_id) for e in entries]
+        h[offs[0]:offs[0] + n] = [e.tokens[0] for e in entries]
+        h[offs[1]:offs[1] + n] = q_starts
+        h[offs[2]:offs[2] + n] = np.arange(n, dtype=np.int32)
+        h[offs[3]:offs[3] + n] = rows
+        h[offs[4]:offs[4] + n + 1] = np.arange(n + 1, dtype=np.int32)
+        h[offs[5]:offs[5] + n] = [s + 1 for s in q_starts]
+        h[offs[6]:offs[6] + n] = np.arange(n, dtype=np.int32)
+        for gi in range(len(groups)):
+            u = self.cache.drain_updates(gi)
+            h[offs[7 + 2 * gi]] = len(u)
+            if u:
+                h[offs[8 + 2 * gi]:offs[8 + 2 * gi] + 3 * len(u)] = np.asarray(u, dtype=np.int32).reshape(-1)
+
+        with torch.cuda.device(self.device):
+            entry = self._graphs.get(key)
+            meta = entry.meta if entry is not None else torch.empty(total, dtype=torch.int32, device=self.device)
+            meta.copy_(host[:total], non_blocking=True)
+            self._staging.mark(slot)
+
+            def view(i, length):
+                return meta[int(offs[i]):int(offs[i]) + length]
+
+            def forward():
+                step = StepContext(
+                    num_tokens=n, num_seqs=n, token_ids=view(0, n), positions=view(1, n), token_seq=view(2, n),
+                    seq_rows=view(3, n), cu_q=view(4, n + 1), kv_len=view(5, n), q_lens=[1] * n,
+                    q_starts=list(q_starts), kv_lens=[s + 1 for s in q_starts], rows=list(rows),
+                    dtype=self.model.dtype, max_kv_bound=bound)
+                for gi, g in enumerate(groups):
+                    ops.table_update_dyn(g.table, view(8 + 2 * gi, 3 * n), view(7 + 2 * gi, 1), n)
+                return self.model.forward(step, self.slots, view(6, n))
+
+            if entry is None:
+                logits = forward()                       # this step's work, launch by launch
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    if self._graph_pool is None:
+                        self._graph_pool = torch.cuda.graph_pool_handle()
+                    torch.cuda.synchronize(self.device)
+                    with torch.cuda.graph(graph, pool=self._graph_pool):
+                        static_logits = forward()        # recorded, not run
+                    self._graphs[key] = _DecodeGraph(graph, meta, static_logits)
+                except Exception as exc:                 # capture is an optimisation only
+                    self.decode_graphs = False
+                    print(f"[sparseengine_b200] CUDA graph capture failed ({exc!r}); decode runs without graphs",
+                          flush=True)
+            else:
+                entry.graph.replay()
+                self.graph_replays += 1
+                logits = entry.logits
+        want = [i for i, e in enumerate(entries) for _ in e.want]
+        if not want:
+            return logits[:0]
+        if want == list(range(n)):
+            return logits
+        return logits[torch.tensor(want, device=self.device)]
 
     def _pack(self, entries):
         n = len(entries)

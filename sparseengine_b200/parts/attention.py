@@ -16,6 +16,8 @@ from .linear import linear
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         s = spec

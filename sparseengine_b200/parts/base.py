@@ -74,6 +74,7 @@ class StepContext:
     rows: list = field(default_factory=list)         # host copy of seq_rows
     dtype: torch.dtype = torch.float32
     extras: dict = field(default_factory=dict)       # scratch shared by parts within a step
+    max_kv_bound: Optional[int] = None               # an upper bound to plan launches with, if set
 
     @property
     def max_q_len(self) -> int:
@@ -81,11 +82,22 @@ class StepContext:
 
     @property
     def max_kv_len(self) -> int:
+        """Most keys any entry has; launch plans use ``max_kv_bound`` when it is set (a
+        replayed CUDA graph is planned for a bound, not for the step's exact lengths)."""
+        if self.max_kv_bound is not None:
+            return self.max_kv_bound
         return max(self.kv_lens) if self.kv_lens else 0
 
 
 class Part:
-    """Base of every part: owns parameters, bound after loading."""
+    """Base of every part: owns parameters, bound after loading.
+
+    ``graph_safe``: the part's ``forward`` may be captured into a CUDA graph and replayed
+    for other steps of the same shape, i.e. everything that changes from step to step is
+    read on the device from the step's tensors, nothing from host-side lists.  The
+    built-in parts are; a part that does not say so keeps its model out of graphs."""
+
+    graph_safe = False
 
     def __init__(self, spec: Any, dtype: torch.dtype):
         self.spec = spec

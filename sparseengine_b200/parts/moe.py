@@ -17,6 +17,8 @@ from .base import FeedForward, register_feed_forward
 class _RoutedSwiGLU(FeedForward):
     """Shared machinery: given ids [T, k] int32 and weights [T, k] float32, run experts."""
 
+    graph_safe = True
+
     num_experts: int
     top_k: int
     hidden: int

@@ -12,6 +12,8 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def parameters(self):
         return {"weight": ParamSpec((self.spec.size,), "act", "norm")}
 

@@ -14,6 +14,8 @@ from .base import PositionEncoding, register_position
 
 
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         if spec.pairing != "split_half":

@@ -101,9 +101,15 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
         assert max(len(s["entries"]) for s in steps) == 4
         assert any(len({len(e["tokens"]) > 1 for e in s["entries"]}) == 2 for s in steps)   # portion beside a decode
     runner = runner_for(folder, name, dtype, steps)
-    got, routed = tu.run_trace_runner(runner, steps, capture=True)
+    routed = None
+    if dtype == "bfloat16":
+        got, routed = tu.run_trace_runner(runner, steps, capture=True)
+    else:
+        got = tu.run_trace_runner(runner, steps)
+        if cut in ("tail32", "mixed"):
+            assert runner.graph_replays > 0        # single-token steps replay CUDA graphs
     assert len(got) == sum(len(t) for t in seqs.values())
-    ref = reference(name, dtype, tensors, seqs, routed if dtype == "bfloat16" else None)
+    ref = reference(name, dtype, tensors, seqs, routed)
     tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} {cut}")
     pool = runner.cache.groups[0].pool
     assert pool.free == pool.num_pages and pool.reused_total > 0      # everything came back; pages were reused
@@ -143,8 +149,12 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     toks = tu.random_prompt(256, 201, 99)
     steps = [{"step": i, "entries": [{"id": "d", "tokens": [t], "want": [0]}], "end": ["d"] if i == 200 else []}
              for i, t in enumerate(toks)]
-    got, routed = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps, capture=True)
-    ref = reference("A", dtype, tensors, {"d": toks}, routed if dtype == "bfloat16" else None)
+    routed = None
+    if dtype == "bfloat16":
+        got, routed = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps, capture=True)
+    else:
+        got = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps)
+    ref = reference("A", dtype, tensors, {"d": toks}, routed)
     tu.compare({k: v for k, v in got.items() if k[1] < 3}, ref, *TOL[dtype], what="first tokens")
     tu.compare(got, ref, *TOL[dtype], what="long decoding")
 
@@ -187,3 +197,23 @@ def test_trace_run_program(folders, dtype, tmp_path):
         assert len(kept) >= 5
         got = kept
     tu.compare(got, reference("B", dtype, tensors, seqs), *TOL[dtype], what=f"trace_run {dtype}")
+
+
+@pytest.mark.parametrize("dtype", list(ACT))
+def test_decode_graphs_give_what_single_launches_give(folders, dtype):
+    """Decode steps replayed as CUDA graphs against the same steps launch by launch: batch
+    sizes 1..4, requests joining and leaving, block-table updates inside the graph."""
+    from sparseengine_b200.engine.factory import build_runner
+    folder, _ = folders["C", dtype]
+    seqs = sequences("C", [40, 55, 33, 47])
+    steps = tu.trace_mixed(seqs, chunk=7, decode_tail=30, seed=5)
+    results = []
+    for graphs in (True, False):
+        r = build_runner(folder, dtype=dtype, page_size=16, num_pages=tu.max_live_tokens(steps) // 16, max_rows=4)
+        r.decode_graphs = graphs
+        results.append(tu.run_trace_runner(r, steps))
+        assert (r.graph_replays > 20) == graphs
+    a, b = results
+    assert a.keys() == b.keys()
+    for k in a:
+        assert np.array_equal(a[k], b[k]), k        # same kernels, same plans at these lengths: bit-equal

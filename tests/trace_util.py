@@ -188,6 +188,7 @@ def run_trace_runner(runner, steps: list, capture: bool = False):
     routed: dict = {}
     parts = []
     if capture:
+        runner.decode_graphs = False            # the capture hook copies to the host
         for entry in runner.model.spec.order:
             ff = runner.model.blocks[entry.layer].feed_forward
             if hasattr(ff, "route"):
