@@ -23,23 +23,51 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 template <typename T>
 __global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restrict__ w,
                                T* y, T* residual_out, int hidden, float eps) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
+    const bool vec = (hidden & 7) == 0 && aligned8(x) && aligned8(y) && aligned8(w) &&
+                     (residual == nullptr || (aligned8(residual) && aligned8(residual_out)));
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = to_float(x[base + i]);
-        if (residual != nullptr) {
-            v += to_float(residual[base + i]);
-            residual_out[base + i] = from_float<T>(v);
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            load8(x + base + i, v);
+            if (residual != nullptr) {
+                float r[8];
+                load8(residual + base + i, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += r[j];
+                store8(residual_out + base + i, v);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { row[i + j] = v[j]; ss += v[j] * v[j]; }
         }
-        row[i] = v;
-        ss += v * v;
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = to_float(x[base + i]);
+            if (residual != nullptr) {
+                v += to_float(residual[base + i]);
+                residual_out[base + i] = from_float<T>(v);
+            }
+            row[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        y[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float wv[8], o[8];
+            load8(w + i, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = row[i + j] * inv * wv[j];
+            store8(y + base + i, o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            y[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
+    }
 }
 
 template <typename T>
@@ -78,7 +106,7 @@ extern "C" int se_rmsnorm(const void* x, const void* residual, const void* w, vo
     if (rows <= 0) return 0;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return SE_ERR_UNSUPPORTED;
-    const int threads = hidden >= 2048 ? 512 : 256;
+    const int threads = hidden >= 8192 ? 512 : hidden >= 2048 ? 256 : 128;
     SE_DISPATCH_DTYPE(dtype, T, {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(se::rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

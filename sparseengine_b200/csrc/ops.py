@@ -314,3 +314,13 @@ def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_hea
         tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per, _stream()),
         "attn_decode")
     return out
+
+
+def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
+                 head_dim, page_size, scale, window=None):
+    _check(_fn("se_attn_prefill", "pppipppp" "iiiiii" "f" "ip")(
+        _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
+        table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
+        _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), entries, max_q_len, num_heads,
+        num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()), "attn_prefill")
+    return out

@@ -40,7 +40,16 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
         const T* part = row + (is_q ? 0 : qn);
         const int n = is_q ? qn : kn;
         float ss = 0.f;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
+        if ((n & 7) == 0 && aligned8(part)) {
+            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+                float v[8];
+                load8(part + i, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
+        }
         ss = block_sum(ss, scratch);
         inv = 1.0f / sqrtf(ss / (float)n + eps);
     }

@@ -25,7 +25,12 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
     const int t0 = blockIdx.x * kRouterTokens;
     const int nt = min(kRouterTokens, tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t0 * hidden + i]);
+    const T* xt = x + (size_t)t0 * hidden;
+    if ((hidden & 7) == 0 && aligned8(xt)) {
+        for (int i = threadIdx.x * 8; i < nt * hidden; i += blockDim.x * 8) load8(xt + i, xs + i);
+    } else {
+        for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x) xs[i] = to_float(xt[i]);
+    }
     __syncthreads();
     const int e0 = (blockIdx.y * kRouterWarps + warp) * epw;
     for (int e = e0; e < min(e0 + epw, experts); ++e) {
@@ -119,21 +124,35 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     }
     __syncthreads();
     const float thr = thr_s;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        if (ranks[e] >= top_k) continue;
-        // slot order: strictly greater than the threshold by ascending index, then ties
-        // with it by ascending index.
-        const float s = sj[e];
-        int n_greater = 0, before_greater = 0, before_equal = 0;
-        for (int o = 0; o < experts; ++o) {
-            const float so = sj[o];
-            n_greater += so > thr;
-            before_greater += (so > thr) && o < e;
-            before_equal += (so == thr) && o < e && ranks[o] < top_k;
+    // Slot order: strictly greater than the threshold by ascending index, then ties with it
+    // by ascending index: two prefix counts over the experts in index order.
+    float cnt = 0.f;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt += (ranks[e] < top_k && sj[e] > thr) ? 1.f : 0.f;
+    const int n_greater = (int)block_sum(cnt, red);
+    __shared__ int wcount[2][32];
+    __shared__ int run[2];
+    if (threadIdx.x == 0) run[0] = run[1] = 0;
+    __syncthreads();
+    for (int base = 0; base < experts; base += blockDim.x) {
+        const int e = base + threadIdx.x;
+        const bool chosen = e < experts && ranks[e] < top_k;
+        const bool gr = chosen && sj[e] > thr, tie = chosen && !gr;
+        const unsigned bg = __ballot_sync(0xffffffffu, gr), bt = __ballot_sync(0xffffffffu, tie);
+        if (lane == 0) { wcount[0][warp] = __popc(bg); wcount[1][warp] = __popc(bt); }
+        __syncthreads();
+        int pg = run[0], pt = run[1];
+        for (int w = 0; w < warp; ++w) { pg += wcount[0][w]; pt += wcount[1][w]; }
+        pg += __popc(bg & ((1u << lane) - 1u));
+        pt += __popc(bt & ((1u << lane) - 1u));
+        if (chosen) {
+            const int slot = gr ? pg : n_greater + pt;
+            ids[(size_t)t * top_k + slot] = e;
+            weights[(size_t)t * top_k + slot] = pj[e];
         }
-        const int slot = s > thr ? before_greater : n_greater + before_equal;
-        ids[(size_t)t * top_k + slot] = e;
-        weights[(size_t)t * top_k + slot] = pj[e];
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int w = 0; w < nwarps; ++w) { run[0] += wcount[0][w]; run[1] += wcount[1][w]; }
+        __syncthreads();
     }
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -65,12 +65,17 @@ class PagedAttention(Mixer):
     def attend(self, q, out, step, slot):
         s = self.spec
         if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
-                and step.num_tokens <= self.decode_kernel_max_tokens
                 and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
-            max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
-            ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
-                            num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
-                            page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys)
+            if step.num_tokens <= self.decode_kernel_max_tokens:
+                max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
+                ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
+                                num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+                                page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys)
+            else:
+                ops.attn_prefill(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out,
+                                 entries=step.num_seqs, max_q_len=step.max_q_len, num_heads=s.num_heads,
+                                 num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, page_size=slot.page_size,
+                                 scale=s.scale, window=s.window)
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,

@@ -3,6 +3,7 @@ other than the tiny models': widths and vocabularies that are no power of two, h
 sizes in steps of 16, odd head and group counts."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -402,3 +403,33 @@ def test_decode_attention_tensor_cores(hq, hkv, d, page, window):
     ops.paged_attention_plain(q.view(t, hq * d), cache, table, rows, token_seq, positions, plain.view(t, hq * d),
                               num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
     torch.testing.assert_close(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(12, 2, 128, 16, None), (48, 8, 128, 16, None), (6, 6, 64, 8, None),
+                                                  (20, 4, 64, 5, None), (8, 2, 128, 32, 100), (5, 1, 128, 1, 33)])
+def test_prefill_attention_tensor_cores(hq, hkv, d, page, window):
+    """The prompt-portion kernel: whole prompts, portions that continue a cached prefix,
+    single tokens beside them, row tiles that straddle tokens and requests' ends."""
+    from sparseengine_b200.csrc import ops
+    kv_lens, q_lens = [300, 70, 1, 700, 129, 64], [300, 3, 1, 257, 129, 1]
+    starts = [kv - ql for kv, ql in zip(kv_lens, q_lens)]
+    dtype = torch.bfloat16
+    table, rows, _, _, cache = _cache_setup(kv_lens, hkv, d, page, dtype)
+    ks = [rnd(n, hkv, d, dtype=dtype, seed=20 + i) for i, n in enumerate(kv_lens)]
+    vs = [rnd(n, hkv, d, dtype=dtype, seed=30 + i) for i, n in enumerate(kv_lens)]
+    for i, n in enumerate(kv_lens):
+        p = torch.arange(n, device=DEV)
+        pg = table[int(rows[i]), (p // page).long()].long()
+        cache[pg, 0, :, (p % page).long()] = ks[i]
+        cache[pg, 1, :, (p % page).long()] = vs[i]
+    t = sum(q_lens)
+    q = rnd(t, hq, d, dtype=dtype, seed=7)
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    out = torch.zeros_like(q)
+    ops.attn_prefill(q.view(t, hq * d), cache, table, rows, cu_q, kv_len, out.view(t, hq * d), entries=len(q_lens),
+                     max_q_len=max(q_lens), num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
+                     scale=d ** -0.5, window=window)
+    ref = _attention_reference(q.float().cpu(), [k.float().cpu() for k in ks], [v.float().cpu() for v in vs], q_lens,
+                               starts, dtype, window)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
