@@ -191,7 +191,9 @@ def run_ours(args) -> dict:
         ffs = [b_.feed_forward for b_ in runner.model.blocks]
         for f in ffs:
             f.capture = []
+        graphs, runner.decode_graphs = runner.decode_graphs, False     # the hook copies to the host
         decode_steps(ids, 1)
+        runner.decode_graphs = graphs
         distinct = [len(set(f.capture[0].view(-1).tolist())) for f in ffs]
         for f in ffs:
             f.capture = None
