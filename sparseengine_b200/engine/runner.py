@@ -66,6 +66,7 @@ class _DecodeGraph:
     graph: object
     meta: torch.Tensor            # persistent device copy of the step's packed metadata
     logits: torch.Tensor          # static output of the captured forward
+    kernels: int = 0              # kernels of this library that one replay launches
 
 
 class ModelRunner:
@@ -204,9 +205,12 @@ class ModelRunner:
                     if self._graph_pool is None:
                         self._graph_pool = torch.cuda.graph_pool_handle()
                     torch.cuda.synchronize(self.device)
+                    before = ops.launch_count
                     with torch.cuda.graph(graph, pool=self._graph_pool):
                         static_logits = forward()        # recorded, not run
-                    self._graphs[key] = _DecodeGraph(graph, meta, static_logits)
+                    recorded = ops.launch_count - before
+                    ops.launch_count = before            # nothing ran during capture
+                    self._graphs[key] = _DecodeGraph(graph, meta, static_logits, recorded)
                 except Exception as exc:                 # capture is an optimisation only
                     self.decode_graphs = False
                     print(f"[sparseengine_b200] CUDA graph capture failed ({exc!r}); decode runs without graphs",
@@ -214,6 +218,7 @@ class ModelRunner:
             else:
                 entry.graph.replay()
                 self.graph_replays += 1
+                ops.launch_count += entry.kernels
                 logits = entry.logits
         want = [i for i, e in enumerate(entries) for _ in e.want]
         if not want:

@@ -32,7 +32,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, *, page_si
                 runner.admit(e["id"])
             entries.append(StepEntry(e["id"], list(e["tokens"]), list(e.get("want", []))))
         logits = runner.step(entries)
-        if logits is not None:
+        if logits is not None and logits.shape[0] > 0:
             arr = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
             arr.tofile(os.path.join(out_dir, f"{rec['step']}.f32"))
         else:
