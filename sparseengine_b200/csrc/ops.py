@@ -155,6 +155,12 @@ def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, 
 SCORE_FN = {"sigmoid": 0, "softmax": 1}
 
 
+# From this many tokens on the router's logits come from a library 32-bit product (the
+# reference computes them with F.linear on float32 operands,
+# src/sparseengine/models/minimax_m2.py:166); below it from this library's own kernels.
+ROUTER_LIBRARY_GEMM_TOKENS = 64
+
+
 def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
            logits_out=None):
     tokens, hidden = x.shape
@@ -163,11 +169,15 @@ def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormaliz
         raise ValueError("router weight shape does not match the activations")
     if logits_out is None:
         logits_out = torch.empty(tokens, experts, dtype=torch.float32, device=x.device)
-    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ip")(
+    skip = 0
+    if tokens >= ROUTER_LIBRARY_GEMM_TOKENS:
+        torch.matmul(x.float(), gate.t(), out=logits_out)      # true 32-bit: reduced-precision modes are off
+        skip = 1
+    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "iip")(
         _ptr(x, None, "x"), _ptr(gate, torch.float32, "gate"), _ptr(bias, torch.float32, "bias"),
         _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"),
         _ptr(logits_out, torch.float32, "logits_out"), tokens, hidden, experts, top_k, SCORE_FN[score_fn],
-        int(renormalize), float(routed_scale), dtype_code(x.dtype), _stream()), "router")
+        int(renormalize), float(routed_scale), skip, dtype_code(x.dtype), _stream()), "router")
     return ids, weights
 
 
@@ -288,15 +298,26 @@ def attn_decode_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> b
     return bool(f(head_dim, num_heads, num_kv_heads))
 
 
-def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: int, sms: int = 148):
-    """How many key splits, and how many keys each: enough CTAs for two per SM, at least 256
-    keys per split."""
+def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: int, sms: int = 148,
+                     ctas_per_sm: int = 2):
+    """How many key splits, and how many keys each.  CTAs = tokens x KV heads x splits run in
+    waves of ``sms * ctas_per_sm``; a CTA costs its 64-key tiles plus about three tiles of
+    fixed work.  Pick the split count with the least waves x cost."""
     group = num_heads // num_kv_heads
     base = tokens * num_kv_heads * (-(-group // 16))
-    splits = max(1, min(-(-2 * sms // base), -(-max_keys // 256)))
-    per = -(-(-(-max_keys // splits)) // 64) * 64
-    splits = max(1, -(-max_keys // per))
-    return splits, per
+    slots = sms * ctas_per_sm
+    tiles = -(-max_keys // 64)
+    best = None
+    for s in range(1, max(1, tiles // 2) + 1):
+        per_tiles = -(-tiles // s)
+        if s > 1 and -(-tiles // per_tiles) != s:
+            continue                                  # the same split size as a smaller count
+        waves = -(-base * s // slots)
+        cost = waves * (per_tiles + 3)
+        if best is None or cost < best[0]:
+            best = (cost, s, per_tiles)
+    _, splits, per_tiles = best
+    return splits, per_tiles * 64
 
 
 def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,

@@ -74,15 +74,70 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
     }
 }
 
+// Few tokens (decode): the latency of one warp walking a whole gate row dominates, so a
+// block of 8 warps takes 2 experts, 4 warps each on a quarter of the row; partial sums
+// meet in shared memory.  Same 32-bit arithmetic, another order of the sum.
+template <typename T>
+__global__ void router_logits_small_kernel(const T* __restrict__ x, const float* __restrict__ gate,
+                                           float* __restrict__ logits, int tokens, int hidden, int experts) {
+    extern __shared__ __align__(16) float xs[];              // [tokens <= kRouterTokens][hidden]
+    __shared__ float part[kRouterWarps][kRouterTokens];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if ((hidden & 7) == 0 && aligned8(x)) {
+        for (int i = threadIdx.x * 8; i < tokens * hidden; i += blockDim.x * 8) load8(x + i, xs + i);
+    } else {
+        for (int i = threadIdx.x; i < tokens * hidden; i += blockDim.x) xs[i] = to_float(x[i]);
+    }
+    __syncthreads();
+    const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3;
+    float acc[kRouterTokens];
+#pragma unroll
+    for (int j = 0; j < kRouterTokens; ++j) acc[j] = 0.f;
+    if (e < experts) {
+        const float* g = gate + (size_t)e * hidden;
+        const int n4 = hidden >> 2;                           // hidden % 4 == 0 (checked by the launcher)
+        const int per = (n4 + 3) / 4, a = quarter * per, b = min(n4, a + per);
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+#pragma unroll 8
+        for (int i = a + lane; i < b; i += 32) {
+            const float4 gv = __ldg(g4 + i);
+#pragma unroll
+            for (int j = 0; j < kRouterTokens; ++j) {
+                if (j < tokens) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
+                    acc[j] = fmaf(xv.x, gv.x, acc[j]);
+                    acc[j] = fmaf(xv.y, gv.y, acc[j]);
+                    acc[j] = fmaf(xv.z, gv.z, acc[j]);
+                    acc[j] = fmaf(xv.w, gv.w, acc[j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kRouterTokens; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0) part[warp][j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * kRouterTokens) {
+        const int which = threadIdx.x / kRouterTokens, j = threadIdx.x % kRouterTokens;
+        const int ee = blockIdx.x * 2 + which;
+        if (ee < experts && j < tokens)
+            logits[(size_t)j * experts + ee] = (part[which * 4][j] + part[which * 4 + 1][j]) +
+                                               (part[which * 4 + 2][j] + part[which * 4 + 3][j]);
+    }
+}
+
 // One block per token: score function, selection bias, top-k in the reference's order,
 // renormalisation.
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      int* __restrict__ ids, float* __restrict__ weights, int experts, int top_k,
                                      int score_fn, int renormalize, float routed_scale) {
-    extern __shared__ float sel[];
+    extern __shared__ __align__(16) float sel[];
+    const int padded = (experts + 3) & ~3;
     float* pj = sel;                     // [experts] probabilities
-    float* sj = pj + experts;            // [experts] selection scores
-    int* ranks = (int*)(sj + experts);   // [experts]
+    float* sj = pj + padded;             // [experts] selection scores (16-byte aligned)
+    int* ranks = (int*)(sj + padded);    // [experts]
     __shared__ float red[33];
     __shared__ float thr_s;
     const int t = blockIdx.x;
@@ -115,7 +170,15 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         const float s = sj[e];
         int rank = 0;
-        for (int o = 0; o < experts; ++o) {
+        int o = 0;
+        for (; o + 4 <= experts; o += 4) {           // sj is 16-byte aligned: experts*4 bytes per array
+            const float4 v = *reinterpret_cast<const float4*>(sj + o);
+            rank += (v.x > s) || (v.x == s && o < e);
+            rank += (v.y > s) || (v.y == s && o + 1 < e);
+            rank += (v.z > s) || (v.z == s && o + 2 < e);
+            rank += (v.w > s) || (v.w == s && o + 3 < e);
+        }
+        for (; o < experts; ++o) {
             const float so = sj[o];
             rank += (so > s) || (so == s && o < e);
         }
@@ -166,13 +229,15 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
 }  // namespace se
 
 // logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
+// With skip_logits != 0 the caller has already filled `logits` (a library 32-bit product for
+// large batches) and only the selection runs.
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
                          float* logits, int tokens, int hidden, int experts, int top_k, int score_fn,
-                         int renormalize, float routed_scale, int dtype, cudaStream_t stream) {
+                         int renormalize, float routed_scale, int skip_logits, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
     const size_t smem = (size_t)se::kRouterTokens * hidden * sizeof(float);
-    const size_t smem_sel = (size_t)experts * 3 * sizeof(float);
+    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 3 * sizeof(float);
     if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
     // few tokens: one gate row per warp (many blocks); many tokens: several rows per warp so
     // that the token tile in shared memory is reused
@@ -180,6 +245,19 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
     int epw = 1;
     while (epw < 8 && token_blocks * se::ceil_div(experts, se::kRouterWarps * epw) > 4 * 148) epw *= 2;
     dim3 grid(token_blocks, se::ceil_div(experts, se::kRouterWarps * epw));
+    if (skip_logits) {
+    } else if (tokens <= se::kRouterTokens && (hidden & 3) == 0) {
+        const size_t small_smem = (size_t)tokens * hidden * sizeof(float);
+        SE_DISPATCH_DTYPE(dtype, T, {
+            if (small_smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(se::router_logits_small_kernel<T>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_smem);
+                if (e != cudaSuccess) return (int)e;
+            }
+            se::router_logits_small_kernel<T><<<se::ceil_div(experts, 2), 32 * se::kRouterWarps, small_smem, stream>>>(
+                (const T*)x, gate, logits, tokens, hidden, experts);
+        });
+    } else
     SE_DISPATCH_DTYPE(dtype, T, {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
