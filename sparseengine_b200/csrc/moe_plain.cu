@@ -19,28 +19,31 @@ __global__ void moe_count_rank_kernel(const int* __restrict__ ids, int assignmen
                                       int* __restrict__ rank) {
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    __shared__ int warp_count[32];
-    __shared__ int running;
-    if (threadIdx.x == 0) running = 0;
-    __syncthreads();
-    for (int base = 0; base < assignments; base += blockDim.x) {
-        const int a = base + threadIdx.x;
-        const bool mine = a < assignments && ids[a] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-        if (lane == 0) warp_count[warp] = __popc(ballot);
-        __syncthreads();
-        int before = running;
-        for (int w = 0; w < warp; ++w) before += warp_count[w];
-        if (mine) rank[a] = before + __popc(ballot & ((1u << lane) - 1u));
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < nwarps; ++w) tot += warp_count[w];
-            running += tot;
-        }
-        __syncthreads();
+    __shared__ int warp_total[32];
+    // each warp owns a contiguous chunk (a multiple of 32 assignments)
+    const int per = ((assignments + nwarps - 1) / nwarps + 31) & ~31;
+    const int a0 = warp * per, a1 = min(assignments, a0 + per);
+    int mine = 0;
+    for (int base = a0; base < a1; base += 32) {
+        const int a = base + lane;
+        mine += __popc(__ballot_sync(0xffffffffu, a < a1 && ids[a] == e));
     }
-    if (threadIdx.x == 0) counts[e] = running;
+    if (lane == 0) warp_total[warp] = mine;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_total[w];
+    for (int base = a0; base < a1; base += 32) {
+        const int a = base + lane;
+        const bool hit = a < a1 && ids[a] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+        if (hit) rank[a] = before + __popc(ballot & ((1u << lane) - 1u));
+        before += __popc(ballot);
+    }
+    if (threadIdx.x == 0) {
+        int tot = 0;
+        for (int w = 0; w < nwarps; ++w) tot += warp_total[w];
+        counts[e] = tot;
+    }
 }
 
 // One block: exclusive scan of counts -> offsets[experts+1], tile list for rows-per-tile
@@ -190,11 +193,25 @@ template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, T* __restrict__ out,
                                    int hidden, int top_k) {
     const int t = blockIdx.x;
-    const int i = blockIdx.y * blockDim.x + threadIdx.x;
-    if (i >= hidden) return;
-    float s = 0.f;
-    for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
-    out[(size_t)t * hidden + i] = from_float<T>(s);
+    if ((hidden & 7) == 0 && aligned8(y) && aligned8(out)) {
+        const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+        if (i >= hidden) return;
+        float acc[8] = {};
+        for (int k = 0; k < top_k; ++k) {
+            float v[8];
+            load8(y + (size_t)inv_pos[t * top_k + k] * hidden + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        store8(out + (size_t)t * hidden + i, acc);
+        return;
+    }
+    for (int i = blockIdx.y * blockDim.x * 8 + threadIdx.x; i < min(hidden, (int)(blockIdx.y + 1) * (int)blockDim.x * 8);
+         i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
+        out[(size_t)t * hidden + i] = from_float<T>(s);
+    }
 }
 
 }  // namespace se
@@ -204,7 +221,7 @@ extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, 
                                   int* num_tiles, cudaStream_t stream) {
     if (assignments <= 0) return 0;
     if (tile_rows <= 0 || experts <= 0) return SE_ERR_ARGUMENT;
-    se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
+    se::moe_count_rank_kernel<<<experts, assignments > 2048 ? 1024 : 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
     se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
         ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
@@ -238,7 +255,7 @@ extern "C" int se_moe_combine(const void* y, const int* inv_pos, void* out, int 
                               int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 256)), 256, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
+        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 128 * 8)), 128, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
     SE_LAUNCH_CHECK();
 }
 
@@ -296,7 +313,7 @@ extern "C" int se_moe_route_build_no_alloc(const int* ids, int assignments, int 
     // cleared.
     int* counts = scratch;
     int* rank = scratch + SE_NOALLOC_MAX_EXPERTS;
-    se::moe_count_rank_kernel<<<experts, 256, 0, stream>>>(ids, assignments, counts, rank);
+    se::moe_count_rank_kernel<<<experts, assignments > 2048 ? 1024 : 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
     se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
         ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);

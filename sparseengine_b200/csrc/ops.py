@@ -25,7 +25,7 @@ _fns: dict = {}
 
 # Kernels launched through these bindings since the process started (a launcher that
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
-KERNELS_PER_CALL = {"se_moe_route_build": 2, "se_attn_decode": 2, "se_router": 2}
+KERNELS_PER_CALL = {"se_moe_route_build": 2, "se_attn_decode": 2, "se_router": 2}   # upper bounds per call
 launch_count = 0
 
 
@@ -128,13 +128,16 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
     dt = qkv.dtype
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
         raise ValueError("qkv width does not match the head counts")
-    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iiip")(
+    inv_rms = None
+    if q_w is not None and tokens > 64:      # many tokens: norm statistics once per token, not once per head
+        inv_rms = torch.empty(tokens, 2, dtype=torch.float32, device=qkv.device)
+    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iipip")(
         _ptr(qkv, None, "qkv"), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
         _ptr(inv_freq, torch.float32, "inv_freq"), _ptr(positions, torch.int32, "positions"),
         _ptr(token_seq, torch.int32, "token_seq"), _ptr(seq_rows, torch.int32, "seq_rows"),
         _ptr(table, torch.int32, "table"), table.shape[1], _ptr(cache, dt, "cache"), _ptr(q_out, dt, "q_out"),
         tokens, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), float(rope_scale),
-        page_size, int(write_cache), dtype_code(dt), _stream()), "qk_prep")
+        page_size, int(write_cache), _ptr(inv_rms), dtype_code(dt), _stream()), "qk_prep")
     return q_out
 
 

@@ -22,7 +22,7 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
                                const int* __restrict__ token_seq, const int* __restrict__ seq_rows,
                                const int* __restrict__ table, int table_stride, T* __restrict__ cache,
                                T* __restrict__ q_out, int hq, int hkv, int d, int rot, float eps,
-                               float rope_scale, int page_size, int write_cache) {
+                               float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -36,7 +36,9 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     const T* w = is_q ? q_w : k_w;
 
     float inv = 1.f;
-    if (w != nullptr) {
+    if (w != nullptr && inv_rms != nullptr) {
+        inv = inv_rms[2 * t + (is_q ? 0 : 1)];
+    } else if (w != nullptr) {
         const T* part = row + (is_q ? 0 : qn);
         const int n = is_q ? qn : kn;
         float ss = 0.f;
@@ -96,21 +98,53 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     }
 }
 
+// inv_rms[t] = (1/sqrt(mean(q^2)+eps), 1/sqrt(mean(k^2)+eps)) of token t's whole projections:
+// for many tokens the statistics are taken once here instead of once per head.
+template <typename T>
+__global__ void qk_inv_rms_kernel(const T* __restrict__ qkv, float* __restrict__ inv_rms, int qn, int kn, float eps) {
+    __shared__ float scratch[33];
+    const T* row = qkv + (size_t)blockIdx.x * (qn + 2 * kn);
+    for (int which = 0; which < 2; ++which) {
+        const T* part = row + (which ? qn : 0);
+        const int n = which ? kn : qn;
+        float ss = 0.f;
+        if ((n & 7) == 0 && aligned8(part)) {
+            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+                float v[8];
+                load8(part + i, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
+        }
+        ss = block_sum(ss, scratch);
+        if (threadIdx.x == 0) inv_rms[2 * blockIdx.x + which] = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+}
+
 }  // namespace se
 
 extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, const float* inv_freq,
                           const int* positions, const int* token_seq, const int* seq_rows, const int* table,
                           int table_stride, void* cache, void* q_out, int tokens, int hq, int hkv, int d,
-                          int rot, float eps, float rope_scale, int page_size, int write_cache, int dtype,
-                          cudaStream_t stream) {
+                          int rot, float eps, float rope_scale, int page_size, int write_cache, float* inv_rms,
+                          int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1)) return SE_ERR_ARGUMENT;
     if (inv_freq == nullptr) rot = 0;
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    // inv_rms: optional float [tokens, 2] workspace; when given (many tokens) the statistics
+    // are computed once per token by a first kernel
+    const bool two_pass = inv_rms != nullptr && q_w != nullptr;
+    if (two_pass) {
+        SE_DISPATCH_DTYPE(dtype, T,
+            se::qk_inv_rms_kernel<T><<<tokens, 256, 0, stream>>>((const T*)qkv, inv_rms, hq * d, hkv * d, eps));
+    }
     SE_DISPATCH_DTYPE(dtype, T,
         se::qk_prep_kernel<T><<<dim3(tokens, hq + hkv), 128, smem, stream>>>(
             (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
             seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
-            write_cache));
+            write_cache, two_pass ? inv_rms : nullptr));
     SE_LAUNCH_CHECK();
 }
