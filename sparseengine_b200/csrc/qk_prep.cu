@@ -13,48 +13,26 @@
 
 namespace se {
 
-// grid (tokens, hq + hkv): block (t, h) handles query head h, or KV head h - hq (its key
-// and its value).  Each block recomputes the sum of squares of its whole projection (the
-// rows are a few KB and sit in L2), which keeps every (token, head) independent.
+// grid (tokens, blocks of heads): a block handles `heads_per_block` of the hq query heads
+// and hkv KV heads (a KV head means its key and its value) of one token.  With few tokens
+// every head gets a block of its own, which recomputes the sum of squares of its whole
+// projection (the rows are a few KB and sit in L2); with many tokens one block takes all
+// heads of a token and the statistics come from a first kernel.
 template <typename T>
 __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
                                const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                const int* __restrict__ token_seq, const int* __restrict__ seq_rows,
                                const int* __restrict__ table, int table_stride, T* __restrict__ cache,
                                T* __restrict__ q_out, int hq, int hkv, int d, int rot, float eps,
-                               float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms) {
+                               float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms,
+                               int heads_per_block) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
     const int t = blockIdx.x;
-    const bool is_q = (int)blockIdx.y < hq;
-    const int h = is_q ? blockIdx.y : blockIdx.y - hq;
-    if (!is_q && !write_cache) return;
     const int qn = hq * d, kn = hkv * d;
     const T* row = qkv + (size_t)t * (qn + 2 * kn);
     const int pos = positions[t];
     const int half = rot / 2;
-    const T* w = is_q ? q_w : k_w;
-
-    float inv = 1.f;
-    if (w != nullptr && inv_rms != nullptr) {
-        inv = inv_rms[2 * t + (is_q ? 0 : 1)];
-    } else if (w != nullptr) {
-        const T* part = row + (is_q ? 0 : qn);
-        const int n = is_q ? qn : kn;
-        float ss = 0.f;
-        if ((n & 7) == 0 && aligned8(part)) {
-            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
-                float v[8];
-                load8(part + i, v);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-            }
-        } else {
-            for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
-        }
-        ss = block_sum(ss, scratch);
-        inv = 1.0f / sqrtf(ss / (float)n + eps);
-    }
     if (inv_freq != nullptr) {
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             float s, c;
@@ -63,38 +41,69 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
             cs[half + j] = s * rope_scale;
         }
     }
-    __syncthreads();
-
-    T* k_dst = nullptr;
-    if (!is_q) {
-        const int page = table[(size_t)seq_rows[token_seq[t]] * table_stride + pos / page_size];
-        const size_t page_elems = (size_t)2 * hkv * page_size * d;
-        k_dst = cache + (size_t)page * page_elems + (size_t)h * page_size * d + (size_t)(pos % page_size) * d;
-    }
-    const T* src = row + (is_q ? 0 : qn) + h * d;
-    T* dst = is_q ? q_out + (size_t)t * qn + h * d : k_dst;
-    auto normed = [&](int dim) -> float {
-        const float v = to_float(src[dim]);
-        if (w == nullptr) return v;
-        // cast(x32 * inv) * cast(w), the product rounded once more
-        return round_act<T>(round_act<T>(v * inv) * to_float(w[h * d + dim]));
-    };
-    // items i over [0, d - half): i < half is a rotated pair (dims i, i + half), the rest
-    // are the pass-through dims i + half
-    for (int i = threadIdx.x; i < d - half; i += blockDim.x) {
-        if (i < half) {
-            const float x1 = normed(i), x2 = normed(i + half);
-            const float c = cs[i], s = cs[half + i];
-            dst[i] = from_float<T>(x1 * c - x2 * s);
-            dst[i + half] = from_float<T>(x2 * c + x1 * s);
-        } else {
-            dst[i + half] = from_float<T>(normed(i + half));
+    const int total_heads = hq + (write_cache ? hkv : 0);
+    const int h_begin = blockIdx.y * heads_per_block, h_end = min(total_heads, h_begin + heads_per_block);
+    float inv_cached[2] = {-1.f, -1.f};       // statistics of the q and of the k projection, once per block
+    for (int hh = h_begin; hh < h_end; ++hh) {
+        const bool is_q = hh < hq;
+        const int h = is_q ? hh : hh - hq;
+        const T* w = is_q ? q_w : k_w;
+        float inv = 1.f;
+        if (w != nullptr && inv_rms != nullptr) {
+            inv = inv_rms[2 * t + (is_q ? 0 : 1)];
+        } else if (w != nullptr) {
+            if (inv_cached[is_q ? 0 : 1] < 0.f) {
+                const T* part = row + (is_q ? 0 : qn);
+                const int n = is_q ? qn : kn;
+                float ss = 0.f;
+                if ((n & 7) == 0 && aligned8(part)) {
+                    for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+                        float v[8];
+                        load8(part + i, v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+                    }
+                } else {
+                    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
+                }
+                ss = block_sum(ss, scratch);
+                inv_cached[is_q ? 0 : 1] = 1.0f / sqrtf(ss / (float)n + eps);
+            }
+            inv = inv_cached[is_q ? 0 : 1];
         }
-    }
-    if (!is_q) {
-        const T* vsrc = row + qn + kn + h * d;
-        T* v_dst = k_dst + (size_t)hkv * page_size * d;
-        for (int i = threadIdx.x; i < d; i += blockDim.x) v_dst[i] = vsrc[i];
+        __syncthreads();      // cos/sin are in shared memory (first pass) 
+
+        T* k_dst = nullptr;
+        if (!is_q) {
+            const int page = table[(size_t)seq_rows[token_seq[t]] * table_stride + pos / page_size];
+            const size_t page_elems = (size_t)2 * hkv * page_size * d;
+            k_dst = cache + (size_t)page * page_elems + (size_t)h * page_size * d + (size_t)(pos % page_size) * d;
+        }
+        const T* src = row + (is_q ? 0 : qn) + h * d;
+        T* dst = is_q ? q_out + (size_t)t * qn + h * d : k_dst;
+        auto normed = [&](int dim) -> float {
+            const float v = to_float(src[dim]);
+            if (w == nullptr) return v;
+            // cast(x32 * inv) * cast(w), the product rounded once more
+            return round_act<T>(round_act<T>(v * inv) * to_float(w[h * d + dim]));
+        };
+        // items i over [0, d - half): i < half is a rotated pair (dims i, i + half), the rest
+        // are the pass-through dims i + half
+        for (int i = threadIdx.x; i < d - half; i += blockDim.x) {
+            if (i < half) {
+                const float x1 = normed(i), x2 = normed(i + half);
+                const float c = cs[i], s = cs[half + i];
+                dst[i] = from_float<T>(x1 * c - x2 * s);
+                dst[i + half] = from_float<T>(x2 * c + x1 * s);
+            } else {
+                dst[i + half] = from_float<T>(normed(i + half));
+            }
+        }
+        if (!is_q) {
+            const T* vsrc = row + qn + kn + h * d;
+            T* v_dst = k_dst + (size_t)hkv * page_size * d;
+            for (int i = threadIdx.x; i < d; i += blockDim.x) v_dst[i] = vsrc[i];
+        }
     }
 }
 
@@ -141,10 +150,11 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
         SE_DISPATCH_DTYPE(dtype, T,
             se::qk_inv_rms_kernel<T><<<tokens, 256, 0, stream>>>((const T*)qkv, inv_rms, hq * d, hkv * d, eps));
     }
+    const int heads_per_block = tokens > 64 ? 8 : 1;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::qk_prep_kernel<T><<<dim3(tokens, hq + hkv), 128, smem, stream>>>(
+        se::qk_prep_kernel<T><<<dim3(tokens, se::ceil_div(hq + hkv, heads_per_block)), 128, smem, stream>>>(
             (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
             seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
-            write_cache, two_pass ? inv_rms : nullptr));
+            write_cache, two_pass ? inv_rms : nullptr, heads_per_block));
     SE_LAUNCH_CHECK();
 }
