@@ -158,29 +158,21 @@ def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, 
 SCORE_FN = {"sigmoid": 0, "softmax": 1}
 
 
-# From this many tokens on the router's logits come from a library 32-bit product (the
-# reference computes them with F.linear on float32 operands,
-# src/sparseengine/models/minimax_m2.py:166); below it from this library's own kernels.
-ROUTER_LIBRARY_GEMM_TOKENS = 64
-
-
 def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
            logits_out=None):
+    """32-bit router logits, scores, top-k and weights.  A token's logits are summed in one
+    fixed order whatever the batch, so its experts do not depend on what shares its step."""
     tokens, hidden = x.shape
     experts = gate.shape[0]
     if gate.shape != (experts, hidden):
         raise ValueError("router weight shape does not match the activations")
     if logits_out is None:
         logits_out = torch.empty(tokens, experts, dtype=torch.float32, device=x.device)
-    skip = 0
-    if tokens >= ROUTER_LIBRARY_GEMM_TOKENS:
-        torch.matmul(x.float(), gate.t(), out=logits_out)      # true 32-bit: reduced-precision modes are off
-        skip = 1
-    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "iip")(
+    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ip")(
         _ptr(x, None, "x"), _ptr(gate, torch.float32, "gate"), _ptr(bias, torch.float32, "bias"),
         _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"),
         _ptr(logits_out, torch.float32, "logits_out"), tokens, hidden, experts, top_k, SCORE_FN[score_fn],
-        int(renormalize), float(routed_scale), skip, dtype_code(x.dtype), _stream()), "router")
+        int(renormalize), float(routed_scale), dtype_code(x.dtype), _stream()), "router")
     return ids, weights
 
 

@@ -12,112 +12,116 @@
 
 namespace se {
 
-constexpr int kRouterTokens = 8;   // tokens that share one read of a gate row
+constexpr int kRouterTokens = 8;   // tokens per block
 constexpr int kRouterWarps = 8;
+constexpr int kRouterExperts = 4;  // gate rows a warp walks at once in the many-token kernel
 
-// logits[t, e] = sum_i float(x[t, i]) * gate[e, i], 32-bit.  Block (bx, by): tokens
-// bx*8 .. +7 (their rows converted to 32-bit in shared memory), experts by*8*epw .. ; each
-// warp walks `epw` gate rows.
+// The one order in which a router logit is summed, whatever the batch: the row is cut into
+// four quarters; within a quarter lane l takes elements (or 16-byte groups) l, l+32, ... in
+// increasing order with fused multiply-adds, the 32 lanes are combined by a butterfly, and
+// the quarters are added as (q0 + q1) + (q2 + q3).  Both kernels below use it, so a token's
+// logits do not depend on how many tokens share its step.
+template <int NTOK, int NEXP>
+__device__ __forceinline__ void quarter_dot(const float* __restrict__ xs, int hidden, int ntok,
+                                            const float* const* __restrict__ g, int quarter, int lane,
+                                            float (&acc)[NTOK][NEXP]) {
+#pragma unroll
+    for (int j = 0; j < NTOK; ++j)
+#pragma unroll
+        for (int e = 0; e < NEXP; ++e) acc[j][e] = 0.f;
+    if ((hidden & 3) == 0) {
+        const int n4 = hidden >> 2;
+        const int per = (n4 + 3) / 4, a = quarter * per, b = min(n4, a + per);
+#pragma unroll 2
+        for (int i = a + lane; i < b; i += 32) {
+            float4 gv[NEXP];
+#pragma unroll
+            for (int e = 0; e < NEXP; ++e) gv[e] = __ldg(reinterpret_cast<const float4*>(g[e]) + i);
+#pragma unroll
+            for (int j = 0; j < NTOK; ++j) {
+                if (j < ntok) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
+#pragma unroll
+                    for (int e = 0; e < NEXP; ++e) {
+                        acc[j][e] = fmaf(xv.x, gv[e].x, acc[j][e]);
+                        acc[j][e] = fmaf(xv.y, gv[e].y, acc[j][e]);
+                        acc[j][e] = fmaf(xv.z, gv[e].z, acc[j][e]);
+                        acc[j][e] = fmaf(xv.w, gv[e].w, acc[j][e]);
+                    }
+                }
+            }
+        }
+    } else {
+        const int per = (hidden + 3) / 4, a = quarter * per, b = min(hidden, a + per);
+        for (int i = a + lane; i < b; i += 32) {
+#pragma unroll
+            for (int j = 0; j < NTOK; ++j)
+                if (j < ntok)
+#pragma unroll
+                    for (int e = 0; e < NEXP; ++e) acc[j][e] = fmaf(xs[j * hidden + i], g[e][i], acc[j][e]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NTOK; ++j)
+#pragma unroll
+        for (int e = 0; e < NEXP; ++e) acc[j][e] = warp_sum(acc[j][e]);
+}
+
+template <typename T>
+__device__ __forceinline__ void load_tokens(const T* __restrict__ xt, float* xs, int n) {
+    if ((n & 7) == 0 && aligned8(xt)) {
+        for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) load8(xt + i, xs + i);
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) xs[i] = to_float(xt[i]);
+    }
+}
+
+// Many tokens: block (bx, by) takes tokens bx*8 .. +7 (converted to 32-bit in shared memory)
+// and experts by*32 .. +31; each warp walks 4 gate rows at once for the 8 tokens.
 template <typename T>
 __global__ void router_logits_kernel(const T* __restrict__ x, const float* __restrict__ gate,
-                                     float* __restrict__ logits, int tokens, int hidden, int experts, int epw) {
+                                     float* __restrict__ logits, int tokens, int hidden, int experts) {
     extern __shared__ __align__(16) float xs[];              // [kRouterTokens][hidden]
     const int t0 = blockIdx.x * kRouterTokens;
     const int nt = min(kRouterTokens, tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const T* xt = x + (size_t)t0 * hidden;
-    if ((hidden & 7) == 0 && aligned8(xt)) {
-        for (int i = threadIdx.x * 8; i < nt * hidden; i += blockDim.x * 8) load8(xt + i, xs + i);
-    } else {
-        for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x) xs[i] = to_float(xt[i]);
-    }
+    load_tokens(x + (size_t)t0 * hidden, xs, nt * hidden);
     __syncthreads();
-    const int e0 = (blockIdx.y * kRouterWarps + warp) * epw;
-    for (int e = e0; e < min(e0 + epw, experts); ++e) {
-        float acc[kRouterTokens];
+    const int e0 = (blockIdx.y * kRouterWarps + warp) * kRouterExperts;
+    if (e0 >= experts) return;
+    const float* g[kRouterExperts];
 #pragma unroll
-        for (int j = 0; j < kRouterTokens; ++j) acc[j] = 0.f;
-        const float* g = gate + (size_t)e * hidden;
-        if ((hidden & 3) == 0) {
-            // 16-byte loads, several in flight per lane
-            const float4* g4 = reinterpret_cast<const float4*>(g);
-            const int n4 = hidden >> 2;
-#pragma unroll 4
-            for (int i = lane; i < n4; i += 32) {
-                const float4 gv = __ldg(g4 + i);
+    for (int e = 0; e < kRouterExperts; ++e) g[e] = gate + (size_t)min(e0 + e, experts - 1) * hidden;
+    float q[4][kRouterTokens][kRouterExperts];
 #pragma unroll
-                for (int j = 0; j < kRouterTokens; ++j) {
-                    if (j < nt) {
-                        const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
-                        acc[j] = fmaf(xv.x, gv.x, acc[j]);
-                        acc[j] = fmaf(xv.y, gv.y, acc[j]);
-                        acc[j] = fmaf(xv.z, gv.z, acc[j]);
-                        acc[j] = fmaf(xv.w, gv.w, acc[j]);
-                    }
-                }
-            }
-        } else {
-            for (int i = lane; i < hidden; i += 32) {
-                const float gv = g[i];
+    for (int quarter = 0; quarter < 4; ++quarter) quarter_dot<kRouterTokens, kRouterExperts>(xs, hidden, nt, g, quarter, lane, q[quarter]);
+    if (lane == 0) {
 #pragma unroll
-                for (int j = 0; j < kRouterTokens; ++j)
-                    if (j < nt) acc[j] = fmaf(xs[j * hidden + i], gv, acc[j]);
-            }
-        }
+        for (int j = 0; j < kRouterTokens; ++j)
 #pragma unroll
-        for (int j = 0; j < kRouterTokens; ++j) {
-            if (j < nt) {
-                const float v = warp_sum(acc[j]);
-                if (lane == 0) logits[(size_t)(t0 + j) * experts + e] = v;
-            }
-        }
+            for (int e = 0; e < kRouterExperts; ++e)
+                if (j < nt && e0 + e < experts)
+                    logits[(size_t)(t0 + j) * experts + e0 + e] = (q[0][j][e] + q[1][j][e]) + (q[2][j][e] + q[3][j][e]);
     }
 }
 
 // Few tokens (decode): the latency of one warp walking a whole gate row dominates, so a
-// block of 8 warps takes 2 experts, 4 warps each on a quarter of the row; partial sums
-// meet in shared memory.  Same 32-bit arithmetic, another order of the sum.
+// block of 8 warps takes 2 experts, 4 warps each on one quarter of the row.
 template <typename T>
 __global__ void router_logits_small_kernel(const T* __restrict__ x, const float* __restrict__ gate,
                                            float* __restrict__ logits, int tokens, int hidden, int experts) {
     extern __shared__ __align__(16) float xs[];              // [tokens <= kRouterTokens][hidden]
     __shared__ float part[kRouterWarps][kRouterTokens];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if ((hidden & 7) == 0 && aligned8(x)) {
-        for (int i = threadIdx.x * 8; i < tokens * hidden; i += blockDim.x * 8) load8(x + i, xs + i);
-    } else {
-        for (int i = threadIdx.x; i < tokens * hidden; i += blockDim.x) xs[i] = to_float(x[i]);
-    }
+    load_tokens(x, xs, tokens * hidden);
     __syncthreads();
     const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3;
-    float acc[kRouterTokens];
+    const float* g[1] = {gate + (size_t)min(e, experts - 1) * hidden};
+    float acc[kRouterTokens][1];
+    quarter_dot<kRouterTokens, 1>(xs, hidden, tokens, g, quarter, lane, acc);
+    if (lane == 0)
 #pragma unroll
-    for (int j = 0; j < kRouterTokens; ++j) acc[j] = 0.f;
-    if (e < experts) {
-        const float* g = gate + (size_t)e * hidden;
-        const int n4 = hidden >> 2;                           // hidden % 4 == 0 (checked by the launcher)
-        const int per = (n4 + 3) / 4, a = quarter * per, b = min(n4, a + per);
-        const float4* g4 = reinterpret_cast<const float4*>(g);
-#pragma unroll 8
-        for (int i = a + lane; i < b; i += 32) {
-            const float4 gv = __ldg(g4 + i);
-#pragma unroll
-            for (int j = 0; j < kRouterTokens; ++j) {
-                if (j < tokens) {
-                    const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
-                    acc[j] = fmaf(xv.x, gv.x, acc[j]);
-                    acc[j] = fmaf(xv.y, gv.y, acc[j]);
-                    acc[j] = fmaf(xv.z, gv.z, acc[j]);
-                    acc[j] = fmaf(xv.w, gv.w, acc[j]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < kRouterTokens; ++j) {
-        const float v = warp_sum(acc[j]);
-        if (lane == 0) part[warp][j] = v;
-    }
+        for (int j = 0; j < kRouterTokens; ++j) part[warp][j] = acc[j][0];
     __syncthreads();
     if (threadIdx.x < 2 * kRouterTokens) {
         const int which = threadIdx.x / kRouterTokens, j = threadIdx.x % kRouterTokens;
@@ -229,42 +233,35 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
 }  // namespace se
 
 // logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
-// With skip_logits != 0 the caller has already filled `logits` (a library 32-bit product for
-// large batches) and only the selection runs.
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
                          float* logits, int tokens, int hidden, int experts, int top_k, int score_fn,
-                         int renormalize, float routed_scale, int skip_logits, int dtype, cudaStream_t stream) {
+                         int renormalize, float routed_scale, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
-    const size_t smem = (size_t)se::kRouterTokens * hidden * sizeof(float);
+    const int tile_tokens = tokens < se::kRouterTokens ? tokens : se::kRouterTokens;
+    const size_t smem = (size_t)tile_tokens * hidden * sizeof(float);
     const size_t smem_sel = (size_t)((experts + 3) & ~3) * 3 * sizeof(float);
     if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
-    // few tokens: one gate row per warp (many blocks); many tokens: several rows per warp so
-    // that the token tile in shared memory is reused
-    const int token_blocks = se::ceil_div(tokens, se::kRouterTokens);
-    int epw = 1;
-    while (epw < 8 && token_blocks * se::ceil_div(experts, se::kRouterWarps * epw) > 4 * 148) epw *= 2;
-    dim3 grid(token_blocks, se::ceil_div(experts, se::kRouterWarps * epw));
-    if (skip_logits) {
-    } else if (tokens <= se::kRouterTokens && (hidden & 3) == 0) {
-        const size_t small_smem = (size_t)tokens * hidden * sizeof(float);
-        SE_DISPATCH_DTYPE(dtype, T, {
-            if (small_smem > 48 * 1024) {
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (tokens <= se::kRouterTokens) {
+            if (smem > 48 * 1024) {
                 cudaError_t e = cudaFuncSetAttribute(se::router_logits_small_kernel<T>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_smem);
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
             }
-            se::router_logits_small_kernel<T><<<se::ceil_div(experts, 2), 32 * se::kRouterWarps, small_smem, stream>>>(
+            se::router_logits_small_kernel<T><<<se::ceil_div(experts, 2), 32 * se::kRouterWarps, smem, stream>>>(
                 (const T*)x, gate, logits, tokens, hidden, experts);
-        });
-    } else
-    SE_DISPATCH_DTYPE(dtype, T, {
-        if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
+        } else {
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return (int)e;
+            }
+            dim3 grid(se::ceil_div(tokens, se::kRouterTokens),
+                      se::ceil_div(experts, se::kRouterWarps * se::kRouterExperts));
+            se::router_logits_kernel<T><<<grid, 32 * se::kRouterWarps, smem, stream>>>((const T*)x, gate, logits, tokens,
+                                                                                        hidden, experts);
         }
-        se::router_logits_kernel<T><<<grid, 32 * se::kRouterWarps, smem, stream>>>((const T*)x, gate, logits, tokens, hidden,
-                                                                                    experts, epw);
     });
     if (smem_sel > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);

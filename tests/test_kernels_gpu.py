@@ -207,6 +207,26 @@ def test_router(dtype, tokens, hidden, experts, top_k, bias):
     torch.testing.assert_close(w.cpu()[clear], ref_w[clear], atol=1e-5, rtol=1e-5)
 
 
+def test_router_logits_do_not_depend_on_the_batch():
+    """A token's router logits are bit-equal whether it is routed alone, with seven others
+    or with hundreds (the decode and the many-token kernels sum in the same order)."""
+    from sparseengine_b200.csrc import ops
+    for hidden, experts in ((3072, 256), (200, 37), (77, 5)):
+        x = rnd(300, hidden, dtype=torch.bfloat16, seed=1)
+        gate = rnd(experts, hidden, scale=0.2, seed=2)
+        outs = []
+        for sl in (slice(0, 300), slice(0, 8), slice(0, 1), slice(5, 13), slice(7, 8)):
+            xs = x[sl].contiguous()
+            n = xs.shape[0]
+            logits = torch.empty(n, experts, dtype=torch.float32, device=DEV)
+            ops.router(xs, gate, None, torch.empty(n, 2, dtype=torch.int32, device=DEV),
+                       torch.empty(n, 2, dtype=torch.float32, device=DEV), top_k=2, logits_out=logits)
+            outs.append((sl, logits))
+        full = outs[0][1]
+        for sl, lg in outs[1:]:
+            assert torch.equal(lg, full[sl]), (hidden, experts, sl)
+
+
 def test_router_tie_order_nan_and_softmax():
     from sparseengine_b200.csrc import ops
     x = torch.zeros(2, 8, device=DEV)
