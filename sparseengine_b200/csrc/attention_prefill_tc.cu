@@ -1,0 +1,392 @@
+// Prompt-portion attention on 5th-generation tensor cores (bfloat16, head size 128).
+//
+// One CTA per (batch entry, KV head, tile of 128 query rows); a row is one (query token,
+// query head of the GQA group) pair, token-major, so a tile spans ~21 tokens of M2 and all
+// six heads that share the KV head.  Per 64-key tile:
+//
+//   S = Q·Kᵀ        tcgen05.mma, M 128 x N 64 x K 128, Q and K K-major in shared memory
+//                   (128-byte swizzle), S in tensor memory (two buffers);
+//   softmax         four warps, one thread per row: tcgen05.ld of its row of S, mask
+//                   (causal, window, end of keys), running maximum and sum in 32-bit, P
+//                   rounded to bfloat16 and written to shared memory as the next A operand;
+//   O += P·V        tcgen05.mma, M 128 x N 128 x K 64, V straight from its pages (dims
+//                   contiguous: the MN-major B operand), O in tensor memory.
+//
+// The running maximum only moves when a row's maximum grows by more than 2^8 (then O and
+// the sum are rescaled), so O is read back from tensor memory rarely; the final division by
+// the sum is exact for whatever reference maximum was used.  Warp roles: warp 0 loads K/V
+// tiles (cp.async, three stages), warp 1 owns tensor memory and issues the MMAs, warps 2-5
+// are the softmax/epilogue warps.  Every mbarrier wait is bounded and reports through the
+// error word.  Arithmetic as the reference's prefill kernel
+// (src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127).
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace se {
+namespace fa {
+
+constexpr int D = 128;
+constexpr int kRows = 128;
+constexpr int kKeys = 64;
+constexpr int kStages = 3;
+constexpr int kThreads = 192;
+constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
+constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
+constexpr int kKVStageBytes = 4 * kHalfBytes;        // K halves, V halves
+constexpr int kPBytes = kRows * 128;                 // [128 rows][64 keys] bf16
+constexpr uint32_t kSpin = 1u << 24;
+constexpr float kRescaleThreshold = 8.f;             // log2 units
+
+using se::mma::smem_u32;
+using se::mma::cp_async16;
+using se::mma::cp_async_commit;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+// rows of 128 bytes, 16-byte chunks XOR-swizzled by (row % 8): the canonical 128-byte-swizzle image
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+// K-major operand (rows = M or N index, 64 contiguous K elements per 128-byte row)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand: 64 contiguous N elements per 128-byte row, rows = K index; 8-row groups
+// 1024 bytes apart (stride offset), 64-element N groups `lbo` bytes apart (leading offset)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+struct Bars {
+    uint64_t kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], p_empty[2];
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                       const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
+                       const int* __restrict__ cu_q, const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out,
+                       int* error, int hq, int hkv, int page_size, float scale_log2, int window) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;                               // [2 halves][128 rows][128 B]
+    uint8_t* kv_s = q_s + kQBytes;                     // [stages][K half0, K half1, V half0, V half1]
+    uint8_t* p_s = kv_s + kStages * kKVStageBytes;     // [2][128 rows][128 B]
+    __shared__ __align__(8) Bars bars;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+
+    const int entry = blockIdx.z, kvh = blockIdx.y;
+    const int group = hq / hkv;
+    const int tok0 = cu_q[entry];
+    const int q_len = cu_q[entry + 1] - tok0;
+    const int total_rows = q_len * group;
+    const int row_base = blockIdx.x * kRows;
+    if (row_base >= total_rows) return;
+    const int kv_end = kv_len[entry];
+    const int q_start = kv_end - q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int last_row = min(row_base + kRows, total_rows) - 1;
+    const int max_pos = q_start + last_row / group;
+    const int first_pos = q_start + row_base / group;
+    const int k_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int k_begin = (k_lo / kKeys) * kKeys;
+    const int k_end = max_pos + 1;
+    const int num_tiles = (k_end - k_begin + kKeys - 1) / kKeys;
+
+    auto bar = [&](uint64_t* b) { return smem_u32(b); };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(&bars.kv_full[s]), 1); mbar_init(bar(&bars.kv_empty[s]), 1); }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(&bars.s_full[b]), 1);
+            mbar_init(bar(&bars.s_empty[b]), 128);
+            mbar_init(bar(&bars.p_full[b]), 128);
+            mbar_init(bar(&bars.p_empty[b]), 1);
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q tile: every thread copies chunks; rows beyond the tile's rows are zero-filled
+    for (int i = threadIdx.x; i < kRows * 16; i += kThreads) {
+        const int r = i >> 4, c = i & 15;
+        const int row = row_base + r;
+        const bool ok = row < total_rows;
+        const int rr = ok ? row : total_rows - 1;
+        const __nv_bfloat16* src = q + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D + c * 8;
+        cp_async16(smem_u32(q_s) + (c >> 3) * (kRows * 128) + sw128(r, c & 7), src, ok);
+    }
+    cp_async_commit();
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base_s;
+    const uint32_t tmem_o = tmem, tmem_s0 = tmem + 128;          // O: columns 0..127, S buffers: 128.., 192..
+
+    const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
+    const size_t page_elems = (size_t)2 * hkv * page_size * D;
+    const size_t head_off = (size_t)kvh * page_size * D;
+    const size_t v_off = (size_t)hkv * page_size * D;
+
+    if (warp == 0) {
+        // ---- loader: K/V tiles from their pages ------------------------------------------
+        auto issue = [&](int tile) {
+            uint8_t* st = kv_s + (size_t)(tile % kStages) * kKVStageBytes;
+            const int base = k_begin + tile * kKeys;
+            for (int i = lane; i < kKeys * 16; i += 32) {
+                const int r = i >> 4, c = i & 15;
+                const int j = base + r;
+                const bool ok = j < k_end;
+                const int jj = ok ? j : k_end - 1;
+                const int page = row_table[jj / page_size];
+                const __nv_bfloat16* src = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+                const uint32_t off = (c >> 3) * kHalfBytes + sw128(r, c & 7);
+                cp_async16(smem_u32(st) + off, src, ok);
+                cp_async16(smem_u32(st) + 2 * kHalfBytes + off, src + v_off, ok);
+            }
+        };
+        bool ok = true;
+        for (int tile = 0; tile < num_tiles + 1 && ok; ++tile) {
+            if (tile < num_tiles) {
+                if (tile >= kStages) ok = mbar_wait(bar(&bars.kv_empty[tile % kStages]), ((tile / kStages) - 1) & 1, &abort_s);
+                if (ok) issue(tile);
+            }
+            cp_async_commit();
+            if (tile >= 1) {           // the previous tile's copies have landed
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(&bars.kv_full[(tile - 1) % kStages]));
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) { abort_s = 1; if (lane == 0) atomicCAS(error, 0, 11); }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t id_s = idesc(kKeys, 0), id_o = idesc(D, 1);
+            bool ok = true;
+            auto issue_pv = [&](int i) {
+                const int b = i & 1;
+                if (!mbar_wait(bar(&bars.p_full[b]), (i >> 1) & 1, &abort_s)) { ok = false; return; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t pa = smem_u32(p_s) + b * kPBytes;
+                const uint32_t va = smem_u32(kv_s) + (i % kStages) * kKVStageBytes + 2 * kHalfBytes;
+#pragma unroll
+                for (int kk = 0; kk < kKeys / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+                    umma(tmem_o, desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
+                         (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(&bars.kv_empty[i % kStages]));
+                umma_commit(bar(&bars.p_empty[b]));
+            };
+            for (int j = 0; j < num_tiles && ok; ++j) {
+                const int b = j & 1;
+                if (!mbar_wait(bar(&bars.kv_full[j % kStages]), (j / kStages) & 1, &abort_s)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(bar(&bars.s_empty[b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ka = smem_u32(kv_s) + (j % kStages) * kKVStageBytes;
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(tmem_s0 + b * 64, desc_kmajor(smem_u32(q_s) + kb * (kRows * 128)) + (uint64_t)(kk * 2),
+                             desc_kmajor(ka + kb * kHalfBytes) + (uint64_t)(kk * 2), id_s, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(&bars.s_full[b]));
+                if (j >= 1) issue_pv(j - 1);
+            }
+            if (ok) issue_pv(num_tiles - 1);
+            if (!ok) { abort_s = 1; atomicCAS(error, 0, 12); }
+        }
+    } else {
+        // ---- softmax and epilogue: one thread per row ------------------------------------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+        const int row = row_base + r;
+        const bool valid = row < total_rows;
+        const int rr = valid ? row : total_rows - 1;
+        const int pos = q_start + rr / group;
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float m_ref = -INFINITY, l = 0.f;                  // reference maximum (log2 units), running sum
+        bool ok = true;
+        for (int j = 0; j < num_tiles && ok; ++j) {
+            const int b = j & 1;
+            if (!mbar_wait(bar(&bars.s_full[b]), (j >> 1) & 1, &abort_s)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sv[64];
+            tmem_ld32(tmem_s0 + b * 64 + lane_addr, sv);
+            tmem_ld32(tmem_s0 + b * 64 + 32 + lane_addr, sv + 32);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar(&bars.s_empty[b]));
+            const int key0 = k_begin + j * kKeys;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                const int key = key0 + c;
+                float s = __uint_as_float(sv[c]) * scale_log2;
+                if (key > pos || key < lo) s = -INFINITY;
+                sv[c] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            // move the reference maximum only on the first visible keys or a large jump
+            float factor = 1.f;
+            bool need = false;
+            if (mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx != -INFINITY)) {
+                factor = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                need = m_ref != -INFINITY;
+                m_ref = mx;
+                l *= factor;
+            }
+            if (__any_sync(0xffffffffu, need)) {
+                // O must be at rest: the P·V of the previous tile has finished
+                if (!mbar_wait(bar(&bars.p_empty[(j - 1) & 1]), ((j - 1) >> 1) & 1, &abort_s)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_o + c0 + lane_addr, ov);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * (need ? factor : 1.f));
+                    tmem_st32(tmem_o + c0 + lane_addr, ov);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // the P buffer is free once the P·V two tiles back has finished
+            if (j >= 2 && !mbar_wait(bar(&bars.p_empty[b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
+            uint8_t* prow = p_s + b * kPBytes;
+            float sum = 0.f;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_use);
+                    const float p1 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_use);
+                    sum += p0 + p1;
+                    packed[i] = se::mma::pack_bf16(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(prow + sw128(r, c8)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l += sum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar(&bars.p_full[b]));
+        }
+        if (ok && mbar_wait(bar(&bars.p_empty[(num_tiles - 1) & 1]), ((num_tiles - 1) >> 1) & 1, &abort_s)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = 1.f / l;
+            __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + c0 + lane_addr, ov);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (valid) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = se::mma::pack_bf16(__uint_as_float(ov[c + 2 * i]) * inv, __uint_as_float(ov[c + 2 * i + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        } else {
+            abort_s = 1;
+            atomicCAS(error, 0, 13);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+
+}  // namespace fa
+}  // namespace se
+
+extern "C" int se_attn_prefill_tc_supported(int head_dim, int hq, int hkv) {
+    return (head_dim == 128 && hkv > 0 && hq % hkv == 0) ? 1 : 0;
+}
+
+extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* table, int table_stride,
+                                  const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int* error,
+                                  int entries, int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale,
+                                  int window, cudaStream_t stream) {
+    using namespace se::fa;
+    if (entries <= 0 || max_q_len <= 0) return 0;
+    if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)kQBytes + kStages * kKVStageBytes + 2 * kPBytes + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int group = hq / hkv;
+    dim3 grid(se::ceil_div(max_q_len * group, kRows), hkv, entries);
+    attn_prefill_tc_kernel<<<grid, kThreads, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
+        (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window);
+    return (int)cudaGetLastError();
+}

@@ -340,3 +340,22 @@ def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), entries, max_q_len, num_heads,
         num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()), "attn_prefill")
     return out
+
+
+def attn_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
+    f = library().se_attn_prefill_tc_supported
+    f.restype = _I
+    f.argtypes = [_I, _I, _I]
+    return bool(f(head_dim, num_heads, num_kv_heads))
+
+
+def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
+                    head_dim, page_size, scale, window=None):
+    """Prompt-portion attention on tcgen05 (head size 128)."""
+    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ip")(
+        _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
+        table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
+        _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), _ptr(tc_error_flag(q.device)),
+        entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()),
+        "attn_prefill_tc")
+    return out

@@ -425,12 +425,17 @@ def test_decode_attention_tensor_cores(hq, hkv, d, page, window):
     torch.testing.assert_close(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("impl", ["mma_sync", "tcgen05"])
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(12, 2, 128, 16, None), (48, 8, 128, 16, None), (6, 6, 64, 8, None),
                                                   (20, 4, 64, 5, None), (8, 2, 128, 32, 100), (5, 1, 128, 1, 33)])
-def test_prefill_attention_tensor_cores(hq, hkv, d, page, window):
-    """The prompt-portion kernel: whole prompts, portions that continue a cached prefix,
-    single tokens beside them, row tiles that straddle tokens and requests' ends."""
+def test_prefill_attention_tensor_cores(hq, hkv, d, page, window, impl):
+    """The prompt-portion kernels (m16n8k16 tiles, and tcgen05 with tensor memory): whole
+    prompts, portions that continue a cached prefix, single tokens beside them, row tiles
+    that straddle tokens and requests' ends."""
     from sparseengine_b200.csrc import ops
+    if impl == "tcgen05" and not ops.attn_prefill_tc_supported(d, hq, hkv):
+        pytest.skip("the tcgen05 kernel takes head size 128")
+    fn = ops.attn_prefill_tc if impl == "tcgen05" else ops.attn_prefill
     kv_lens, q_lens = [300, 70, 1, 700, 129, 64], [300, 3, 1, 257, 129, 1]
     starts = [kv - ql for kv, ql in zip(kv_lens, q_lens)]
     dtype = torch.bfloat16
@@ -447,9 +452,9 @@ def test_prefill_attention_tensor_cores(hq, hkv, d, page, window):
     cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
     kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
     out = torch.zeros_like(q)
-    ops.attn_prefill(q.view(t, hq * d), cache, table, rows, cu_q, kv_len, out.view(t, hq * d), entries=len(q_lens),
-                     max_q_len=max(q_lens), num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
-                     scale=d ** -0.5, window=window)
+    fn(q.view(t, hq * d), cache, table, rows, cu_q, kv_len, out.view(t, hq * d), entries=len(q_lens),
+       max_q_len=max(q_lens), num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
+    ops.tc_check(DEV)
     ref = _attention_reference(q.float().cpu(), [k.float().cpu() for k in ks], [v.float().cpu() for v in vs], q_lens,
                                starts, dtype, window)
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
