@@ -125,14 +125,17 @@ def bench_attention_prefill(a, dev):
     cu = torch.tensor([0, t], dtype=torch.int32, device=dev)
     kvl = torch.tensor([a.context_prefix + t], dtype=torch.int32, device=dev)
 
+    fn = ops.attn_prefill_tc if a.impl == "tcgen05" else ops.attn_prefill
+
     def run():
-        ops.attn_prefill(q, cache, table, rows, cu, kvl, out, entries=1, max_q_len=t, num_heads=a.heads,
-                         num_kv_heads=a.kv_heads, head_dim=a.head_dim, page_size=a.page_size, scale=a.head_dim ** -0.5)
+        fn(q, cache, table, rows, cu, kvl, out, entries=1, max_q_len=t, num_heads=a.heads,
+           num_kv_heads=a.kv_heads, head_dim=a.head_dim, page_size=a.page_size, scale=a.head_dim ** -0.5)
     ms = timed(run, a.iters)
+    ops.tc_check(dev)
     keys = a.context_prefix * t + t * (t + 1) / 2
     fl = 4 * a.heads * a.head_dim * keys
     by = (a.context_prefix + t) * 2 * a.kv_heads * a.head_dim * 2 + 2 * t * a.heads * a.head_dim * 2
-    return ms, by, fl, {}
+    return ms, by, fl, {"impl": a.impl}
 
 
 def bench_router(a, dev):
@@ -187,6 +190,8 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma_sync"],
+                    help="attention_prefill: which of the two tensor-core kernels")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")

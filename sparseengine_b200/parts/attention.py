@@ -72,10 +72,12 @@ class PagedAttention(Mixer):
                                 num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
                                 page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys)
             else:
-                ops.attn_prefill(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out,
-                                 entries=step.num_seqs, max_q_len=step.max_q_len, num_heads=s.num_heads,
-                                 num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, page_size=slot.page_size,
-                                 scale=s.scale, window=s.window)
+                # prompt portions: tcgen05 + tensor memory for head size 128, m16n8k16 tiles otherwise
+                fn = (ops.attn_prefill_tc if ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads)
+                      else ops.attn_prefill)
+                fn(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out, entries=step.num_seqs,
+                   max_q_len=step.max_q_len, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
+                   head_dim=s.head_dim, page_size=slot.page_size, scale=s.scale, window=s.window)
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
