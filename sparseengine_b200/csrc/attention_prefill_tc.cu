@@ -15,7 +15,7 @@
 // The running maximum only moves when a row's maximum grows by more than 2^8 (then O and
 // the sum are rescaled), so O is read back from tensor memory rarely; the final division by
 // the sum is exact for whatever reference maximum was used.  Warp roles: warp 0 loads K/V
-// tiles (cp.async, three stages), warp 1 owns tensor memory and issues the MMAs, warps 2-5
+// tiles (cp.async, five stages), warp 1 owns tensor memory and issues the MMAs, warps 2-5
 // are the softmax/epilogue warps.  Every mbarrier wait is bounded and reports through the
 // error word.  Arithmetic as the reference's prefill kernel
 // (src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127).
@@ -28,7 +28,7 @@ namespace fa {
 constexpr int D = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;
-constexpr int kStages = 3;
+constexpr int kStages = 5;
 constexpr int kThreads = 192;
 constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
 constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
@@ -184,16 +184,27 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     if (warp == 0) {
         // ---- loader: K/V tiles from their pages ------------------------------------------
+        // Lane l looks up where keys base+l and base+32+l live (two independent table loads per
+        // lane and tile); the copy loop gets each row's address by shuffle, so no load sits
+        // between the asynchronous copies.
         auto issue = [&](int tile) {
             uint8_t* st = kv_s + (size_t)(tile % kStages) * kKVStageBytes;
             const int base = k_begin + tile * kKeys;
-            for (int i = lane; i < kKeys * 16; i += 32) {
-                const int r = i >> 4, c = i & 15;
-                const int j = base + r;
-                const bool ok = j < k_end;
-                const int jj = ok ? j : k_end - 1;
-                const int page = row_table[jj / page_size];
-                const __nv_bfloat16* src = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            unsigned long long src_row[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int j = min(base + 32 * h + lane, k_end - 1);
+                const int page = row_table[j / page_size];
+                src_row[h] = (unsigned long long)(cache + (size_t)page * page_elems + head_off + (size_t)(j % page_size) * D);
+            }
+            const int c = lane & 15;
+#pragma unroll 4
+            for (int k = 0; k < kKeys / 2; ++k) {
+                const int r = 2 * k + (lane >> 4);
+                const unsigned long long a = __shfl_sync(0xffffffffu, src_row[0], r & 31);
+                const unsigned long long b = __shfl_sync(0xffffffffu, src_row[1], r & 31);
+                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(r < 32 ? a : b) + c * 8;
+                const bool ok = base + r < k_end;
                 const uint32_t off = (c >> 3) * kHalfBytes + sw128(r, c & 7);
                 cp_async16(smem_u32(st) + off, src, ok);
                 cp_async16(smem_u32(st) + 2 * kHalfBytes + off, src + v_off, ok);
