@@ -15,7 +15,7 @@
 // The running maximum only moves when a row's maximum grows by more than 2^8 (then O and
 // the sum are rescaled), so O is read back from tensor memory rarely; the final division by
 // the sum is exact for whatever reference maximum was used.  Warp roles: warp 0 loads K/V
-// tiles (cp.async, five stages), warp 1 owns tensor memory and issues the MMAs, warps 2-5
+// tiles (cp.async, five stages; warps 0 and 6), warp 1 owns tensor memory and issues the MMAs, warps 2-5
 // are the softmax/epilogue warps.  Every mbarrier wait is bounded and reports through the
 // error word.  Arithmetic as the reference's prefill kernel
 // (src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127).
@@ -29,7 +29,7 @@ constexpr int D = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;
 constexpr int kStages = 5;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
 constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
 constexpr int kKVStageBytes = 4 * kHalfBytes;        // K halves, V halves
@@ -104,6 +104,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
           "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 struct Bars {
@@ -182,8 +188,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const size_t head_off = (size_t)kvh * page_size * D;
     const size_t v_off = (size_t)hkv * page_size * D;
 
-    if (warp == 0) {
-        // ---- loader: K/V tiles from their pages ------------------------------------------
+    if (warp == 0 || warp == 6) {
+        // ---- loaders: K/V tiles from their pages ------------------------------------------
         // Lane l looks up where keys base+l and base+32+l live (two independent table loads per
         // lane and tile); the copy loop gets each row's address by shuffle, so no load sits
         // between the asynchronous copies.
@@ -210,19 +216,26 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 cp_async16(smem_u32(st) + 2 * kHalfBytes + off, src + v_off, ok);
             }
         };
+        // Two loader warps take alternate tiles; each announces a tile once its next one has
+        // been issued and `cp.async.wait_group 1` says the earlier copies have landed, so up
+        // to four tiles are in flight.
+        const int first = warp == 0 ? 0 : 1;
         bool ok = true;
-        for (int tile = 0; tile < num_tiles + 1 && ok; ++tile) {
+        int prev = -1;
+        for (int tile = first; ok; tile += 2) {
             if (tile < num_tiles) {
                 if (tile >= kStages) ok = mbar_wait(bar(&bars.kv_empty[tile % kStages]), ((tile / kStages) - 1) & 1, &abort_s);
                 if (ok) issue(tile);
             }
             cp_async_commit();
-            if (tile >= 1) {           // the previous tile's copies have landed
+            if (prev >= 0) {
                 asm volatile("cp.async.wait_group 1;" ::: "memory");
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(&bars.kv_full[(tile - 1) % kStages]));
+                if (lane == 0) mbar_arrive(bar(&bars.kv_full[prev % kStages]));
             }
+            if (tile >= num_tiles) break;
+            prev = tile;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!ok) { abort_s = 1; if (lane == 0) atomicCAS(error, 0, 11); }
@@ -285,15 +298,27 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(&bars.s_empty[b]));
             const int key0 = k_begin + j * kKeys;
-            float mx = -INFINITY;
+            // A tile every row of the warp sees in full needs no masking (rows ascend with the
+            // lane: lane 0 has the smallest position, lane 31 the largest window start).
+            const bool full = key0 + kKeys - 1 <= __shfl_sync(0xffffffffu, pos, 0) &&
+                              key0 >= __shfl_sync(0xffffffffu, lo, 31);
+            if (!full) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const int key = key0 + c;
-                float s = __uint_as_float(sv[c]) * scale_log2;
-                if (key > pos || key < lo) s = -INFINITY;
-                sv[c] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int c = 0; c < 64; ++c) {
+                    const int key = key0 + c;
+                    if (key > pos || key < lo) sv[c] = 0xff800000u;      // -inf
+                }
             }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                m4[0] = fmaxf(m4[0], __uint_as_float(sv[c]));
+                m4[1] = fmaxf(m4[1], __uint_as_float(sv[c + 1]));
+                m4[2] = fmaxf(m4[2], __uint_as_float(sv[c + 2]));
+                m4[3] = fmaxf(m4[3], __uint_as_float(sv[c + 3]));
+            }
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            mx *= scale_log2;                                            // log2 units (scale > 0)
             // move the reference maximum only on the first visible keys or a large jump
             float factor = 1.f;
             bool need = false;
@@ -322,20 +347,22 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             // the P buffer is free once the P·V two tiles back has finished
             if (j >= 2 && !mbar_wait(bar(&bars.p_empty[b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
             uint8_t* prow = p_s + b * kPBytes;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const float neg_m = -m_use;
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float p0 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_use);
-                    const float p1 = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_use);
-                    sum += p0 + p1;
+                    // p = 2^(s * scale - m): one fused multiply-add and one ex2 per element
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), scale_log2, neg_m));
+                    sum4[i] += p0 + p1;
                     packed[i] = se::mma::pack_bf16(p0, p1);
                 }
                 *reinterpret_cast<uint4*>(prow + sw128(r, c8)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar(&bars.p_full[b]));
