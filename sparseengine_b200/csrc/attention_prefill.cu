@@ -99,15 +99,26 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         uint8_t* kbase = smem + (size_t)stage * 2 * kTileBytes;
         uint8_t* vbase = kbase + kTileBytes;
         const int base = k_begin + tile * kTileKeys;
-        for (int i = threadIdx.x; i < kTileKeys * kChunks; i += kThreads) {
-            const int r = i / kChunks, c = i % kChunks;
-            const int j = base + r;
-            const bool ok = j < k_end;
-            const int jj = ok ? j : k_end - 1;
+        // A thread copies chunk (tid % kChunks) of rows tid / kChunks + k * (kThreads / kChunks).  The
+        // rows' addresses are looked up first (independent loads), so that no table load sits
+        // between the asynchronous copies.
+        constexpr int kRowStep = kThreads / kChunks, kIters = kTileKeys / kRowStep;
+        static_assert(kThreads % kChunks == 0 && kTileKeys % kRowStep == 0, "tile copy mapping");
+        const int c = threadIdx.x % kChunks, r0t = threadIdx.x / kChunks;
+        const __nv_bfloat16* srcs[kIters];
+#pragma unroll
+        for (int k = 0; k < kIters; ++k) {
+            const int j = base + r0t + k * kRowStep;
+            const int jj = j < k_end ? j : k_end - 1;      // any valid key: the copy is zero-filled when out of range
             const int page = row_table[jj / page_size];
-            const __nv_bfloat16* src = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
-            cp_async16(smem_u32(kbase) + tile_off<D>(r, c), src, ok);
-            cp_async16(smem_u32(vbase) + tile_off<D>(r, c), src + v_off, ok);
+            srcs[k] = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+        }
+#pragma unroll
+        for (int k = 0; k < kIters; ++k) {
+            const int r = r0t + k * kRowStep;
+            const bool ok = base + r < k_end;
+            cp_async16(smem_u32(kbase) + tile_off<D>(r, c), srcs[k], ok);
+            cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
         }
     };
 
