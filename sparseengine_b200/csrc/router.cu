@@ -76,7 +76,7 @@ __device__ __forceinline__ void load_tokens(const T* __restrict__ xt, float* xs,
     }
 }
 
-// Many tokens: block (bx, by) takes tokens bx*8 .. +7 (converted to 32-bit in shared memory)
+// Many tokens, a width that is no multiple of 4: block (bx, by) takes tokens bx*8 .. +7 (converted to 32-bit in shared memory)
 // and experts by*32 .. +31; each warp walks 4 gate rows at once for the 8 tokens.
 template <typename T>
 __global__ void router_logits_kernel(const T* __restrict__ x, const float* __restrict__ gate,
@@ -102,6 +102,113 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
             for (int e = 0; e < kRouterExperts; ++e)
                 if (j < nt && e0 + e < experts)
                     logits[(size_t)(t0 + j) * experts + e0 + e] = (q[0][j][e] + q[1][j][e]) + (q[2][j][e] + q[3][j][e]);
+    }
+}
+
+// Many tokens: a block of 8 warps takes 32 tokens x 16 experts; warp w owns the 8 x 8
+// sub-tile (tokens 8*(w/2).., experts 8*(w%2)..) with 64 accumulators per lane.  The token
+// and gate rows are staged through shared memory in chunks of 32 16-byte groups, which are
+// exactly the groups the 32 lanes take in one step of the fixed summation order (see
+// quarter_dot), so every (token, expert, quarter, lane) partial sum is accumulated in the
+// same order as in the other kernels; quarters are reduced by the same butterfly and
+// combined as (q0 + q1) + (q2 + q3).  Needs hidden % 4 == 0.
+constexpr int kBigTokens = 32, kBigExperts = 16;
+
+// four consecutive elements as 32-bit values (the address is 4-element aligned)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256, 2)
+router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ gate, float* __restrict__ logits,
+                           int tokens, int hidden, int experts) {
+    extern __shared__ __align__(16) float tiled_smem[];
+    float (*xs)[kBigTokens][128] = reinterpret_cast<float (*)[kBigTokens][128]>(tiled_smem);
+    float (*gs)[kBigExperts][128] = reinterpret_cast<float (*)[kBigExperts][128]>(tiled_smem + 2 * kBigTokens * 128);
+    float (*qsum)[4][64] = reinterpret_cast<float (*)[4][64]>(tiled_smem + 2 * (kBigTokens + kBigExperts) * 128);
+    const int t0 = blockIdx.x * kBigTokens, e0 = blockIdx.y * kBigExperts;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wt = (warp >> 1) * 8, we = (warp & 1) * 8;
+    const int n4 = hidden >> 2;
+    const int per = (n4 + 3) / 4;
+
+    // staging: thread -> 4 token groups (token tid/32 + 8*i, group tid%32) and 2 gate groups
+    float4 xr[4], gr[2];
+    auto fetch = [&](int first, int last) {     // groups first + lane .. (< last) of every row
+        const int i = first + lane;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int t = t0 + warp + 8 * k;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < last && t < tokens) v = load4(x + (size_t)t * hidden + 4 * i);
+            xr[k] = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int e = min(e0 + warp + 8 * k, experts - 1);
+            gr[k] = i < last ? __ldg(reinterpret_cast<const float4*>(gate + (size_t)e * hidden) + i)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<float4*>(&xs[buf][warp + 8 * k][4 * lane]) = xr[k];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) *reinterpret_cast<float4*>(&gs[buf][warp + 8 * k][4 * lane]) = gr[k];
+    };
+
+    for (int quarter = 0; quarter < 4; ++quarter) {
+        const int a = quarter * per, b = min(n4, a + per);
+        const int chunks = a < b ? (b - a + 31) / 32 : 0;
+        float acc[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        if (chunks > 0) fetch(a, b);
+        for (int c = 0; c < chunks; ++c) {
+            const int buf = c & 1;
+            stash(buf);
+            __syncthreads();
+            if (c + 1 < chunks) fetch(a + 32 * (c + 1), b);
+            if (a + 32 * c + lane < b) {         // lanes past the quarter's end add nothing (as in quarter_dot)
+                float4 gv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) gv[j] = *reinterpret_cast<const float4*>(&gs[buf][we + j][4 * lane]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][wt + i][4 * lane]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        acc[i][j] = fmaf(xv.x, gv[j].x, acc[i][j]);
+                        acc[i][j] = fmaf(xv.y, gv[j].y, acc[i][j]);
+                        acc[i][j] = fmaf(xv.z, gv[j].z, acc[i][j]);
+                        acc[i][j] = fmaf(xv.w, gv[j].w, acc[i][j]);
+                    }
+                }
+            }
+            // the buffer written two chunks ahead is this one: everyone must be done reading it
+            if (c + 2 < chunks) __syncthreads();
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float v = warp_sum(acc[i][j]);
+                if (lane == 0) qsum[warp][quarter][i * 8 + j] = v;
+            }
+    }
+    __syncwarp();
+    for (int o = lane; o < 64; o += 32) {
+        const int t = t0 + wt + o / 8, e = e0 + we + o % 8;
+        if (t < tokens && e < experts)
+            logits[(size_t)t * experts + e] = (qsum[warp][0][o] + qsum[warp][1][o]) + (qsum[warp][2][o] + qsum[warp][3][o]);
     }
 }
 
@@ -251,6 +358,14 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
             }
             se::router_logits_small_kernel<T><<<se::ceil_div(experts, 2), 32 * se::kRouterWarps, smem, stream>>>(
                 (const T*)x, gate, logits, tokens, hidden, experts);
+        } else if ((hidden & 3) == 0) {
+            dim3 grid(se::ceil_div(tokens, se::kBigTokens), se::ceil_div(experts, se::kBigExperts));
+            const int tiled_smem = (2 * (se::kBigTokens + se::kBigExperts) * 128 + 8 * 4 * 64) * (int)sizeof(float);
+            cudaError_t e = cudaFuncSetAttribute(se::router_logits_tiled_kernel<T>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, tiled_smem);
+            if (e != cudaSuccess) return (int)e;
+            se::router_logits_tiled_kernel<T><<<grid, 256, tiled_smem, stream>>>((const T*)x, gate, logits, tokens, hidden,
+                                                                                  experts);
         } else {
             if (smem > 48 * 1024) {
                 cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>,
