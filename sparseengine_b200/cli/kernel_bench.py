@@ -157,8 +157,14 @@ def bench_dense(a, dev):
     out = torch.empty(a.tokens, a.n, dtype=torch.bfloat16, device=dev)
     i = [0]
 
+    from ..parts import linear as linear_mod
+
     def run_lib():
-        linear(x, ws[i[0] % len(ws)], out)
+        torch.matmul(x, ws[i[0] % len(ws)].t(), out=out)
+        i[0] += 1
+
+    def run_gemv():
+        ops.gemv(x, ws[i[0] % len(ws)], out)
         i[0] += 1
 
     def run_tc():
@@ -166,7 +172,11 @@ def bench_dense(a, dev):
         i[0] += 1
     ms = timed(run_lib, a.iters)
     ms_tc = timed(run_tc, a.iters)
-    return ms, a.n * a.k * 2, 2 * a.tokens * a.n * a.k, {"library_ms": round(ms, 4), "own_tcgen05_ms": round(ms_tc, 4)}
+    extra = {"library_ms": round(ms, 4), "own_tcgen05_ms": round(ms_tc, 4)}
+    if ops.gemv_supported(a.tokens, a.n, a.k):
+        ms = timed(run_gemv, a.iters)          # what the engine runs for this shape
+        extra["own_gemv_ms"] = round(ms, 4)
+    return ms, a.n * a.k * 2, 2 * a.tokens * a.n * a.k, extra
 
 
 def main(argv=None) -> int:

@@ -1,0 +1,94 @@
+// Dense projection for a handful of rows (decode): out[t, n] = sum_k x[t, k] w[n, k], bf16
+// in, fp32 accumulate, bf16 out, for up to 16 rows of x.
+//
+// With so few rows the projection is a stream over the weight matrix.  A warp owns 16
+// weight rows and walks K in 32-element chunks: every lane loads 16 contiguous bytes of two
+// weight rows (and of one x row) straight from global memory into the registers of
+// m16n8k16 tensor-core fragments.  The fragment's k slots are filled in a permuted order
+// (slot pairs {2t, 2t+1} and {2t+8, 2t+9} of lane t take 4 consecutive elements), which is
+// harmless because A and B use the same permutation and the sum over k does not care.  No
+// shared memory on the way in; the four warps of a block split K and add their partial
+// sums through shared memory at the end.  The weights are read exactly once.
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace se {
+namespace gemv {
+
+constexpr int kWarps = 4;
+constexpr int kRowsPerBlock = 16;
+
+template <int NT>   // 8-row tiles of x: 1 (up to 8 rows) or 2 (up to 16)
+__global__ void __launch_bounds__(32 * kWarps)
+gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+            int rows, int n_out, int k_dim) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int n0 = blockIdx.x * kRowsPerBlock;
+    const int chunks = k_dim / 32;
+    const int c_begin = warp * chunks / kWarps, c_end = (warp + 1) * chunks / kWarps;
+    const __nv_bfloat16* w_lo = w + (size_t)min(n0 + g, n_out - 1) * k_dim + 8 * t4;
+    const __nv_bfloat16* w_hi = w + (size_t)min(n0 + g + 8, n_out - 1) * k_dim + 8 * t4;
+    const __nv_bfloat16* x_row[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        x_ok[nt] = nt * 8 + g < rows;
+        x_row[nt] = x + (size_t)min(nt * 8 + g, rows - 1) * k_dim + 8 * t4;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+#pragma unroll 4
+    for (int c = c_begin; c < c_end; ++c) {
+        const uint4 a_lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + c * 32));     // streamed once
+        const uint4 a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint4 b = make_uint4(0u, 0u, 0u, 0u);
+            if (x_ok[nt]) b = __ldg(reinterpret_cast<const uint4*>(x_row[nt] + c * 32));
+            const uint32_t a0[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
+            const uint32_t a1[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
+            se::mma::mma_bf16(acc[nt], a0, b.x, b.y);
+            se::mma::mma_bf16(acc[nt], a1, b.z, b.w);
+        }
+    }
+    __shared__ float part[kWarps][kRowsPerBlock][8 * NT + 1];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        part[warp][g][nt * 8 + 2 * t4] = acc[nt][0];
+        part[warp][g][nt * 8 + 2 * t4 + 1] = acc[nt][1];
+        part[warp][g + 8][nt * 8 + 2 * t4] = acc[nt][2];
+        part[warp][g + 8][nt * 8 + 2 * t4 + 1] = acc[nt][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kRowsPerBlock * 8 * NT; i += blockDim.x) {
+        const int r = i % kRowsPerBlock, t = i / kRowsPerBlock;      // consecutive threads -> consecutive n
+        if (t < rows && n0 + r < n_out) {
+            const float v = (part[0][r][t] + part[1][r][t]) + (part[2][r][t] + part[3][r][t]);
+            out[(size_t)t * n_out + n0 + r] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+}  // namespace gemv
+}  // namespace se
+
+extern "C" int se_gemv_supported(int rows, int n_out, int k_dim) {
+    return (rows >= 1 && rows <= 16 && n_out >= 1 && k_dim >= 32 && k_dim % 32 == 0) ? 1 : 0;
+}
+
+// x [rows <= 16, k_dim], w [n_out, k_dim], out [rows, n_out]; bf16; k_dim a multiple of 32.
+extern "C" int se_gemv(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!se_gemv_supported(rows, n_out, k_dim)) return SE_ERR_UNSUPPORTED;
+    const int blocks = se::ceil_div(n_out, se::gemv::kRowsPerBlock);
+    if (rows <= 8)
+        se::gemv::gemv_kernel<1><<<blocks, 32 * se::gemv::kWarps, 0, stream>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
+    else
+        se::gemv::gemv_kernel<2><<<blocks, 32 * se::gemv::kWarps, 0, stream>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
+    SE_LAUNCH_CHECK();
+}

@@ -359,3 +359,19 @@ def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, ma
         entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()),
         "attn_prefill_tc")
     return out
+
+
+# ---- dense projection for a handful of rows (bf16; csrc/gemv.cu) --------------------------------
+
+def gemv_supported(rows: int, n_out: int, k_dim: int) -> bool:
+    return 1 <= rows <= 16 and n_out >= 1 and k_dim >= 32 and k_dim % 32 == 0
+
+
+def gemv(x, w, out):
+    """out[rows <= 16, n] = x · wᵀ, weights streamed once through tensor-core fragments."""
+    rows, k_dim = x.shape
+    n_out = w.shape[0]
+    _check(_fn("se_gemv", "pppiiip")(
+        _ptr(x, torch.bfloat16, "x"), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"), rows, n_out,
+        k_dim, _stream()), "gemv")
+    return out

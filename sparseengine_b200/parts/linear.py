@@ -2,7 +2,9 @@
 
 The reference runs these through a library GEMM (``F.linear``:
 src/sparseengine/layers/linear.py:174-191, src/sparseengine/layers/embed_head.py:80), and so
-does this module (cuBLAS through ``torch.matmul``).  In float32 the reduced-precision
+does this module (cuBLAS through ``torch.matmul``), except for up to 16 rows in bfloat16
+(decode), where the product is a stream over the weights and this library's own kernel
+(csrc/gemv.cu) reads them once at memory speed.  In float32 the reduced-precision
 matrix modes are switched off for the whole process, so a float32 product is a true
 32-bit product.
 """
@@ -10,9 +12,14 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
+
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+
+USE_GEMV = True     # False: the library product for every shape
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -21,6 +28,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
         raise ValueError("linear needs CUDA tensors (there is no CPU path)")
     if x.dtype != w.dtype:
         raise TypeError(f"linear: activation {x.dtype} and weight {w.dtype} differ")
+    if (USE_GEMV and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous() and w.is_contiguous()
+            and ops.gemv_supported(x.shape[0], w.shape[0], x.shape[1])):
+        # a handful of rows (decode): this library's weight-streaming kernel
+        if out is None:
+            out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+        return ops.gemv(x, w, out)
     if out is None:
         return torch.matmul(x, w.t())
     return torch.matmul(x, w.t(), out=out)

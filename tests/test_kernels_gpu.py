@@ -458,3 +458,16 @@ def test_prefill_attention_tensor_cores(hq, hkv, d, page, window, impl):
     ref = _attention_reference(q.float().cpu(), [k.float().cpu() for k in ks], [v.float().cpu() for v in vs], q_lens,
                                starts, dtype, window)
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("rows,n_out,k_dim", [(1, 16, 32), (8, 8192, 3072), (3, 3072, 6144), (16, 1000, 96), (11, 37, 160),
+                                             (5, 200064, 3072)])
+def test_gemv_for_a_handful_of_rows(rows, n_out, k_dim):
+    from sparseengine_b200.csrc import ops
+    x = rnd(rows, k_dim, dtype=torch.bfloat16, scale=0.5, seed=1)
+    w = rnd(n_out, k_dim, dtype=torch.bfloat16, scale=0.1, seed=2)
+    out = torch.full((rows, n_out), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemv(x, w, out)
+    ref = (x.float() @ w.float().t())
+    torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), atol=2e-2, rtol=2e-2)
+    assert not ops.gemv_supported(17, n_out, k_dim) and not ops.gemv_supported(4, n_out, 40)
