@@ -7,7 +7,7 @@
 // m16n8k16 tensor-core fragments.  The fragment's k slots are filled in a permuted order
 // (slot pairs {2t, 2t+1} and {2t+8, 2t+9} of lane t take 4 consecutive elements), which is
 // harmless because A and B use the same permutation and the sum over k does not care.  No
-// shared memory on the way in; the four warps of a block split K and add their partial
+// shared memory on the way in; the eight warps of a block split K and add their partial
 // sums through shared memory at the end.  The weights are read exactly once.
 #include "common.cuh"
 #include "mma_util.cuh"
@@ -15,7 +15,7 @@
 namespace se {
 namespace gemv {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kRowsPerBlock = 16;
 
 template <int NT>   // 8-row tiles of x: 1 (up to 8 rows) or 2 (up to 16)
@@ -40,7 +40,7 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-#pragma unroll 4
+#pragma unroll 8
     for (int c = c_begin; c < c_end; ++c) {
         const uint4 a_lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + c * 32));     // streamed once
         const uint4 a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
@@ -66,7 +66,9 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     for (int i = threadIdx.x; i < kRowsPerBlock * 8 * NT; i += blockDim.x) {
         const int r = i % kRowsPerBlock, t = i / kRowsPerBlock;      // consecutive threads -> consecutive n
         if (t < rows && n0 + r < n_out) {
-            const float v = (part[0][r][t] + part[1][r][t]) + (part[2][r][t] + part[3][r][t]);
+            float v = 0.f;
+#pragma unroll
+            for (int wq = 0; wq < kWarps; ++wq) v += part[wq][r][t];
             out[(size_t)t * n_out + n0 + r] = __float2bfloat16_rn(v);
         }
     }

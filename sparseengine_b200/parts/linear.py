@@ -20,6 +20,7 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 
 USE_GEMV = True     # False: the library product for every shape
+GEMV_MAX_OUT = 16384   # measured: beyond this many output features (the LM head) the library product is ahead
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -29,7 +30,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
     if x.dtype != w.dtype:
         raise TypeError(f"linear: activation {x.dtype} and weight {w.dtype} differ")
     if (USE_GEMV and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous() and w.is_contiguous()
-            and ops.gemv_supported(x.shape[0], w.shape[0], x.shape[1])):
+            and w.shape[0] <= GEMV_MAX_OUT and ops.gemv_supported(x.shape[0], w.shape[0], x.shape[1])):
         # a handful of rows (decode): this library's weight-streaming kernel
         if out is None:
             out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
