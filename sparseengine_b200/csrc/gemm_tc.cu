@@ -34,7 +34,7 @@ namespace tc {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;          // bf16 elements: 128 bytes, one swizzle span
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;     // the ring's depth is a launch parameter (2..8)
 constexpr int kThreads = 192;
 constexpr int kTileABytes = kBlockM * kBlockK * 2;
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -126,6 +126,7 @@ struct Params {
     int up_offset;              // row offset of the "up" half (MODE_GATE_UP)
     int total_rows;             // dense: number of activation rows
     int nt;                     // activation rows per tile: 16, 32, 64 or 128
+    int stages;                 // depth of the shared-memory ring
 };
 
 template <int MODE>
@@ -151,11 +152,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t stage_bytes = NA * kTileABytes + nt * kBlockK * 2;
-    __shared__ __align__(8) uint64_t bars[2 * kStages + 1];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
+    const int kStages = p.stages;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ float route_s[128];
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]), accum = smem_u32(&bars[2 * kStages]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]), accum = smem_u32(&bars[2 * kMaxStages]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     uint32_t cols = 32;
@@ -352,11 +354,11 @@ static int make_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t c
 template <int MODE>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
     constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
-    const size_t smem = (size_t)kStages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
+    const size_t smem = (size_t)p.stages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kStages * (NA * kTileABytes + 128 * kBlockK * 2) + 1024);
+                                             226 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -369,6 +371,24 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 }  // namespace se
 
 using namespace se::tc;
+
+#include <cstdlib>
+
+// Depth of the shared-memory ring.  Small token tiles make small stages: several CTAs then
+// fit on an SM (their prologues and epilogues overlap) and each still has several stages in
+// flight.  SE_TC_STAGES_GATE_UP / SE_TC_STAGES_OTHER override the choice (tuning aid).
+static int pick_stages(int na, int nt) {
+    const char* env = std::getenv(na == 2 ? "SE_TC_STAGES_GATE_UP" : "SE_TC_STAGES_OTHER");
+    if (env != nullptr) {
+        const int v = std::atoi(env);
+        if (v >= 2 && v <= kMaxStages) return v;
+    }
+    const int stage_bytes = na * kTileABytes + nt * kBlockK * 2;
+    int stages = na == 2 && nt <= 32 ? 3 : 4;      // measured: three 34 KB stages x two CTAs per SM stream a little faster
+    while (stages < kMaxStages && (stages + 1) * stage_bytes + 1024 <= 100 * 1024) ++stages;   // two CTAs per SM
+    while (stages > 2 && stages * stage_bytes + 1024 > 226 * 1024) --stages;
+    return stages;
+}
 
 // 1 if the tensor-core path takes these sizes (bf16 only; row pitches must be 16-byte
 // multiples for TMA), else 0.
@@ -401,7 +421,7 @@ extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, co
     rc = make_map(&mx, a, assignments, k_dim, nt);
     if (rc) return rc;
     Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
-             n_out,  k_dim,   w_rows,      n_out,     assignments, nt};
+             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(mode == 0 ? 2 : 1, nt)};
     return mode == 0 ? launch<MODE_GATE_UP>(mw, mx, p, max_tiles, stream) : launch<MODE_DOWN>(mw, mx, p, max_tiles, stream);
 }
 
@@ -416,6 +436,6 @@ extern "C" int se_gemm_tc_dense(const void* x, const void* w, void* out, int* er
     rc = make_map(&mx, x, rows, k_dim, nt);
     if (rc) return rc;
     Params p{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (__nv_bfloat16*)out, error,
-             n_out,   k_dim,   n_out,   0,       rows,    nt};
+             n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt)};
     return launch<MODE_DENSE>(mw, mx, p, se::ceil_div(rows, nt), stream);
 }
