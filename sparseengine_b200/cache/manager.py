@@ -68,9 +68,12 @@ class CacheGroup:
 
 class CacheManager:
     def __init__(self, layout, *, page_size: int, num_pages, max_rows: int, max_seq_len: int,
-                 dtype=torch.float32, device="cpu", allocate: bool = True):
+                 dtype=torch.float32, device="cpu", allocate: bool = True, reserved_state_bytes: int = 0):
         """``layout`` is a model's :class:`CacheLayout`; ``num_pages`` an int (every group)
-        or a list with one entry per group."""
+        or a list with one entry per group.  ``reserved_state_bytes`` adds one more slot of
+        that many bytes per request (``reserved_state[row]``, zeroed at admission) that no
+        part of the dense-cache path uses: it is the room a sparse cache method would keep
+        its per-request metadata in."""
         if page_size <= 0 or max_rows <= 0 or max_seq_len <= 0:
             raise ValueError("page_size, max_rows and max_seq_len must be positive")
         self.layout = layout
@@ -88,6 +91,9 @@ class CacheManager:
         for st in layout.states:
             self.states.append(torch.zeros((self.max_rows, *st.shape), dtype=st.dtype, device=device)
                                if allocate else None)
+        self.reserved_state = None
+        if reserved_state_bytes > 0 and allocate:
+            self.reserved_state = torch.zeros(self.max_rows, int(reserved_state_bytes), dtype=torch.uint8, device=device)
         self._free_rows = list(range(self.max_rows - 1, -1, -1))
         self._requests: dict = {}
 
@@ -149,6 +155,8 @@ class CacheManager:
         for st in self.states:
             if st is not None:
                 st[row].zero_()
+        if self.reserved_state is not None:
+            self.reserved_state[row].zero_()
         return row
 
     def reserve(self, seq_id, n_tokens: int) -> None:

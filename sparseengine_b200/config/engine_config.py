@@ -28,7 +28,11 @@ class Config:
     expert_parallel_size: int = 1
     data_parallel_size: int = 1
     sparse_method: str = ""                        # "" or "vanilla": the dense cache
+    mlp_chunk_size: int = 16384                    # most rows the feed-forward takes at once
     decode_graph: bool = True                      # replay decode steps as CUDA graphs
+    enable_profiler: bool = False                  # CUDA-event timing of every part (forces launch-by-launch steps)
+    validate_runtime_invariants: bool = False      # host-side checks of every step's index tensors
+    throughput_log_interval_s: float = 10.0        # generate() logs tokens/s this often (0 = never)
     tiny_random: bool = False                      # random weights instead of a checkpoint
     tiny_random_seed: int = 0
     eos: int = -1
@@ -62,6 +66,10 @@ class Config:
             self.engine_prefill_chunk_size = self.max_num_batched_tokens
         if self.engine_prefill_chunk_size <= 0:
             raise ValueError("engine_prefill_chunk_size must be positive")
+        if self.mlp_chunk_size <= 0:
+            raise ValueError("mlp_chunk_size must be positive")
+        if self.state_slot_bytes < 0:
+            raise ValueError("state_slot_bytes must not be negative")
         self.eos_token_ids = tuple(int(t) for t in self.eos_token_ids)
 
     @classmethod

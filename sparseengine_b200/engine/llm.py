@@ -75,8 +75,13 @@ class LLM:
             num_pages = self._num_pages(m, dt, device)
             cache = CacheManager(m.layout, page_size=cfg.page_size, num_pages=num_pages,
                                  max_rows=cfg.max_num_seqs_in_gpu, max_seq_len=self.max_model_len,
-                                 dtype=dt, device=device)
-        self.runner = ModelRunner(m, cache, device, decode_graphs=cfg.decode_graph)
+                                 dtype=dt, device=device, reserved_state_bytes=cfg.state_slot_bytes)
+        for b in m.blocks:
+            if hasattr(b.feed_forward, "chunk_rows"):
+                b.feed_forward.chunk_rows = cfg.mlp_chunk_size
+        self.runner = ModelRunner(m, cache, device, decode_graphs=cfg.decode_graph and not cfg.enable_profiler)
+        self.runner.validate = cfg.validate_runtime_invariants
+        m.profile = {} if cfg.enable_profiler else None
         eos = tuple(cfg.eos_token_ids) or ((cfg.eos,) if cfg.eos >= 0 else ())
         if not eos and not isinstance(model, dict):
             eos = _eos_from_folder(model, raw)
@@ -184,15 +189,43 @@ class LLM:
         if use_tqdm:
             from tqdm import tqdm
             bar = tqdm(total=len(ids), desc="generate", file=sys.stderr)
+        import time
+        interval = self.config.throughput_log_interval_s
+        t_last, pre, dec = time.perf_counter(), 0, 0
         while not self.is_finished():
-            outs, _ = self.step()
+            outs, n = self.step()
+            pre += max(n, 0)
+            dec += max(-n, 0)
             for o in outs:
                 done[o["seq_id"]] = o
                 if bar is not None:
                     bar.update(1)
+            now = time.perf_counter()
+            if interval and now - t_last >= interval:
+                print(f"[sparseengine_b200] prefill {pre / (now - t_last):.0f} tok/s, decode {dec / (now - t_last):.0f} tok/s, "
+                      f"running {len(self.scheduler.running)}, waiting {len(self.scheduler.waiting)}, "
+                      f"free pages {self.runner.cache.free_pages()}", file=sys.stderr, flush=True)
+                t_last, pre, dec = now, 0, 0
         if bar is not None:
             bar.close()
         return [{k: v for k, v in done[i].items() if k != "seq_id"} for i in ids]
+
+    def stats(self) -> dict:
+        """Counters of the engine: steps, tokens, preemptions, cache occupancy, graph replays
+        and, with ``enable_profiler``, milliseconds per part (CUDA events)."""
+        c = self.runner.cache
+        out = {"steps": self.runner.steps, "tokens": self.runner.tokens,
+               "preemptions": self.scheduler.num_preemptions, "graph_replays": self.runner.graph_replays,
+               "waiting": len(self.scheduler.waiting), "running": len(self.scheduler.running),
+               "free_rows": c.free_rows,
+               "pages": [{"free": g.pool.free, "total": g.pool.num_pages, "taken": g.pool.taken_total,
+                          "reused": g.pool.reused_total} for g in c.groups],
+               "gpu_memory_allocated_bytes": torch.cuda.memory_allocated(self.runner.device)}
+        prof = self.runner.model.profile
+        if prof is not None:
+            torch.cuda.synchronize(self.runner.device)
+            out["part_ms"] = {k: round(sum(a.elapsed_time(b) for a, b in v), 3) for k, v in prof.items()}
+        return out
 
     def exit(self) -> None:
         self.runner = None

@@ -57,6 +57,7 @@ class Model:
         self.final_norm = make_norm(spec.final_norm, dtype)
         self.embed = None
         self.head = None
+        self.profile = None     # a dict: CUDA-event pairs per part are collected in it (a debugging aid)
         for i, e in enumerate(spec.order):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
@@ -134,6 +135,23 @@ class Model:
             entries.append(EntryCache(group, layer, write if kv is not None else False, state))
         return CacheLayout(tuple((g[0], g[1]) for g in groups), tuple(states), tuple(entries))
 
+    def _timed_block(self, block, hidden, residual, step, slot):
+        """The pre-norm block part by part with a CUDA event pair around each part."""
+        def timed(name, fn, *a):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a)
+            e1.record()
+            self.profile.setdefault(name, []).append((e0, e1))
+            return out
+        if not hasattr(block, "mixer_norm"):
+            return timed("block", block.forward, hidden, residual, step, slot)
+        x, residual = timed("mixer_norm", block.mixer_norm.forward, hidden, residual)
+        hidden = timed("mixer", block.mixer.forward, x, step, slot)
+        x, residual = timed("feed_forward_norm", block.feed_forward_norm.forward, hidden, residual)
+        hidden = timed("feed_forward", block.feed_forward.forward, x, step)
+        return hidden, residual
+
     # ---- forward -----------------------------------------------------------------------
     def forward(self, step: StepContext, slots: list, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every schedule entry; return logits
@@ -143,7 +161,11 @@ class Model:
         ops.embed_gather(self.embed, step.token_ids, hidden)
         residual = None
         for entry, slot in zip(s.order, slots):
-            hidden, residual = self.blocks[entry.layer].forward(hidden, residual, step, slot)
+            block = self.blocks[entry.layer]
+            if self.profile is None:
+                hidden, residual = block.forward(hidden, residual, step, slot)
+            else:
+                hidden, residual = self._timed_block(block, hidden, residual, step, slot)
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

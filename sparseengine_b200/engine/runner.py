@@ -89,6 +89,7 @@ class ModelRunner:
         self._graphs: dict = {}
         self._graph_pool = None
         self.graph_replays = 0
+        self.validate = False          # host-side checks of every step's indices (a debugging aid)
 
     # ---- life cycle of a request -------------------------------------------------------
     def admit(self, seq_id) -> None:
@@ -129,22 +130,49 @@ class ModelRunner:
                 self.cache.cancel(s)
             raise
 
-        if self.decode_graphs and all(len(e.tokens) == 1 for e in entries):
-            logits = self._step_graph(entries)
-        else:
-            logits = None
-        if logits is None:
-            step, want_rows, updates = self._pack(entries)
-            with torch.cuda.device(self.device):
-                for g, (upd, n) in zip(self.cache.groups, updates):
-                    if n:
-                        ops.table_update(g.table, upd, n)
-                logits = self.model.forward(step, self.slots, want_rows)
+        try:
+            if self.validate:
+                self._check_invariants(entries)
+            if self.decode_graphs and all(len(e.tokens) == 1 for e in entries):
+                logits = self._step_graph(entries)
+            else:
+                logits = None
+            if logits is None:
+                step, want_rows, updates = self._pack(entries)
+                with torch.cuda.device(self.device):
+                    for g, (upd, n) in zip(self.cache.groups, updates):
+                        if n:
+                            ops.table_update(g.table, upd, n)
+                    logits = self.model.forward(step, self.slots, want_rows)
+        except BaseException:
+            # the step did not happen: give back what was reserved for it
+            # (cf. src/sparseengine/engine/llm_engine.py:1826-1857)
+            for e in entries:
+                self.cache.cancel(e.seq_id)
+            raise
         for e in entries:
             self.cache.commit(e.seq_id, len(e.tokens))
         self.steps += 1
         self.tokens += sum(len(e.tokens) for e in entries)
         return logits
+
+    def _check_invariants(self, entries) -> None:
+        """Host-side validation of what the kernels will index with: every position a step
+        reads or writes has a page, pages are inside their pool, no page belongs to two
+        requests, lengths stay under the limit (the reference's debug bounds checks,
+        src/sparseengine/layers/attention_backend.py:155-215)."""
+        self.cache.check()
+        for e in entries:
+            row, start = self.cache.row(e.seq_id), self.cache.length(e.seq_id)
+            end = start + len(e.tokens)
+            if end > self.cache.max_seq_len:
+                raise AssertionError(f"request {e.seq_id!r} would exceed the maximum length")
+            for g in self.cache.groups:
+                lo = 0 if g.window is None else max(0, start - g.window + 1)
+                idx = np.arange(lo // g.page_size, -(-end // g.page_size))
+                pages = g.table_host[row, idx]
+                if (pages < 0).any() or (pages >= g.pool.num_pages).any():
+                    raise AssertionError(f"request {e.seq_id!r}: block table has no valid page for positions {lo}..{end - 1}")
 
     # ---- decode steps as replayed CUDA graphs ------------------------------------------
     def _step_graph(self, entries):

@@ -102,9 +102,20 @@ class SparseMoE(_RoutedSwiGLU):
             self.capture.append(ids.cpu())
         return ids, weights
 
+    # Most rows routed and run at once (the reference's mlp_chunk_size,
+    # src/sparseengine/models/minimax_m2.py:254-268); the engine sets it from its options.
+    chunk_rows = 16384
+
     def forward(self, x, step):
-        ids, weights = self.route(x)
-        return self.run_experts(x, ids, weights)
+        if x.shape[0] <= self.chunk_rows:
+            ids, weights = self.route(x)
+            return self.run_experts(x, ids, weights)
+        outs = []
+        for a in range(0, x.shape[0], self.chunk_rows):
+            xc = x[a:a + self.chunk_rows]
+            ids, weights = self.route(xc)
+            outs.append(self.run_experts(xc, ids, weights))
+        return torch.cat(outs, 0)
 
 
 class DenseMLP(_RoutedSwiGLU):

@@ -95,7 +95,10 @@ def load_weights(model, model_dir: str, device) -> LoadReport:
     duplicates = []
     handles = []
     for path in files:
-        f = safe_open(path, framework="pt", device="cpu")
+        try:
+            f = safe_open(path, framework="pt", device="cpu")
+        except Exception as e:      # a truncated or damaged file: say which one
+            raise WeightLoadError([], [], [], [f"{path} cannot be read as safetensors ({type(e).__name__}: {e})"]) from e
         handles.append(f)
         for name in f.keys():
             if name in where:

@@ -156,3 +156,15 @@ def test_random_orders_never_lose_or_double_book_a_page(seed):
         cm.release(sid)
     assert all(g.pool.free == g.pool.num_pages for g in cm.groups) and cm.free_rows == 3
     cm.check()
+
+
+def test_reserved_state_slot_is_zeroed_at_admission():
+    """The per-request slot that no part of the dense-cache path uses: fixed size, one per
+    row, clean for every new request."""
+    m = CacheManager(layout(), page_size=4, num_pages=8, max_rows=2, max_seq_len=32, reserved_state_bytes=24)
+    assert m.reserved_state.shape == (2, 24) and m.reserved_state.dtype == torch.uint8
+    row = m.admit("a")
+    m.reserved_state[row].fill_(7)
+    m.release("a")
+    assert m.admit("b") == row and int(m.reserved_state[row].sum()) == 0
+    assert CacheManager(layout(), page_size=4, num_pages=8, max_rows=2, max_seq_len=32).reserved_state is None

@@ -94,3 +94,54 @@ def test_entry_point_refuses_what_it_cannot_do(folder_a):
     first = llm.generate([[1, 2, 3]], SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))[0]["token_ids"]
     out = llm.generate([[1, 2, 3]], SamplingParams(temperature=0, max_tokens=4, eos_token_ids=[first[1]]))[0]
     assert out["token_ids"] == first[:2] and out["finish_reason"] == "stop"
+
+
+def test_a_failed_step_gives_its_pages_back(folder_a):
+    """Host-side failure injection: the forward pass raises in the middle of a step.  The
+    reservation is undone, no page is lost, and the same step then gives the usual logits."""
+    from sparseengine_b200.engine.factory import build_runner
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, _ = folder_a
+    runner = build_runner(folder, dtype="float32", page_size=4, num_pages=16, max_rows=2, max_seq_len=64)
+    runner.validate = True
+    a, b = tu.random_prompt(256, 9, 1), tu.random_prompt(256, 6, 2)
+    runner.cache.admit("a")
+    runner.cache.admit("b")
+    runner.step([StepEntry("a", a[:5], [])])
+    free = runner.cache.free_pages()
+    real = runner.model.forward
+
+    def broken(*args, **kw):
+        raise RuntimeError("injected")
+    runner.model.forward = broken
+    with pytest.raises(RuntimeError, match="injected"):
+        runner.step([StepEntry("a", a[5:], [3]), StepEntry("b", b, [5])])
+    runner.model.forward = real
+    runner.cache.check()
+    assert runner.cache.free_pages() == free and runner.cache.length("a") == 5 and runner.cache.length("b") == 0
+    got = runner.step([StepEntry("a", a[5:], [3]), StepEntry("b", b, [5])]).float().cpu()
+    fresh = build_runner(folder, dtype="float32", page_size=4, num_pages=16, max_rows=2, max_seq_len=64)
+    fresh.cache.admit("a")
+    fresh.cache.admit("b")
+    want = torch.cat([fresh.step([StepEntry("a", a, [8])]), fresh.step([StepEntry("b", b, [5])])]).float().cpu()
+    assert (got - want).abs().max() < 2e-4 * max(1.0, want.abs().max())
+
+
+def test_options_for_debugging_and_long_rows(folder_a):
+    """mlp_chunk_size cuts the feed-forward's rows without changing the result; the
+    profiler and the invariant checks run; stats() reports the engine's counters."""
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, _ = folder_a
+    prompts = [tu.random_prompt(256, n, 20 + n) for n in (11, 17)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    base = LLM(folder, dtype="float32", page_size=4, num_kvcache_slots=256, max_num_batched_tokens=32, max_model_len=64)
+    want = [o["token_ids"] for o in base.generate(prompts, sp)]
+    llm = LLM(folder, dtype="float32", page_size=4, num_kvcache_slots=256, max_num_batched_tokens=32, max_model_len=64,
+              mlp_chunk_size=5, enable_profiler=True, validate_runtime_invariants=True, state_slot_bytes=32)
+    assert [o["token_ids"] for o in llm.generate(prompts, sp)] == want
+    st = llm.stats()
+    assert st["steps"] > 0 and st["tokens"] == sum(len(p) for p in prompts) + 2 * 5
+    assert st["pages"][0]["free"] == st["pages"][0]["total"] and st["running"] == 0
+    assert set(st["part_ms"]) == {"mixer_norm", "mixer", "feed_forward_norm", "feed_forward"}
+    assert all(v > 0 for v in st["part_ms"].values())
+    assert llm.runner.cache.reserved_state.shape[1] == 32

@@ -129,3 +129,15 @@ def test_random_weights_folder_is_seeded_and_loadable(tmp_path):
     # the plain implementation runs on such a folder
     out = plain_m2.forward(cfg, ta, [1, 2, 3])
     assert out.shape == (3, cfg["vocab_size"]) and torch.isfinite(out).all()
+
+
+def test_truncated_file_is_named(tmp_path):
+    cfg = tu.TINY["A"][0]
+    tu.make_model_folder(str(tmp_path), "A")
+    path = os.path.join(str(tmp_path), "model.safetensors")
+    size = os.path.getsize(path)
+    with open(path, "r+b") as f:
+        f.truncate(size // 2)
+    with pytest.raises(WeightLoadError) as e:
+        load_weights(_model(cfg), str(tmp_path), "cpu")
+    assert "model.safetensors" in str(e.value) and "cannot be read" in str(e.value)
