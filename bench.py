@@ -289,9 +289,10 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference's MiniMax M2 path is FP8-only and its fused expert kernel requires SM90 "
-                          "(src/sparseengine/models/spec.py:161-173, src/sparseengine/operators/moe.py:777); "
-                          "it has no bfloat16 M2 path to time on a B200"}))
+                          "the reference installs offline only with --no-deps and then refuses to start its CUDA engine: "
+                          "it requires flashinfer-python>=0.6.18.post1 (0.6.11.post2 is installed) and sglang-kernel "
+                          "(absent, not in the wheelhouse); its MiniMax M2 path is also FP8-only with SM90-only fused "
+                          "expert kernels (src/sparseengine/models/spec.py:161-173, src/sparseengine/operators/moe.py:777)"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
