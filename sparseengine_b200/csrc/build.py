@@ -25,6 +25,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
                            "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+NVCC_FLAGS += os.environ.get("SPARSEENGINE_NVCC_FLAGS", "").split()     # e.g. -D switches for experiments
 LIB_NAME = "libsparseengine_b200.so"
 
 _lock = threading.Lock()

@@ -25,6 +25,8 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -285,6 +287,312 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+
+// ---- the persistent form ---------------------------------------------------------------------
+// The same roles and the same arithmetic, but a CTA does not end with its item (one 128-row
+// block of one tile = one block index of the grid).  When it starts an item it asks the
+// hardware for another block of this grid that has not started yet
+// (clusterlaunchcontrol.try_cancel): that block then never launches and this CTA does its
+// work next.  So the SMs that stream faster take more items, as with one CTA per item, but
+// without a prologue and an epilogue per item: the loader keeps the shared-memory ring full
+// across items, and the accumulator lives in one of two tensor-memory buffers, so that the
+// MMAs of item j + 1 fill buffer b ^ 1 while the epilogue warps drain buffer b of item j.
+//
+// The answer to a request is 16 bytes that land in a shared-memory slot (ring of kSchedSlots)
+// and complete an mbarrier; the loader thread, the MMA thread and the four epilogue warps
+// each read it (sched_full), the last five arrive on sched_empty before the slot is used
+// again.  After the first answer "nothing left" no further request is made.
+constexpr int kSchedSlots = 4;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void clc_try_cancel(uint32_t response, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], 16;" ::"r"(bar) : "memory");
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 ::"r"(response), "r"(bar)
+                 : "memory");
+}
+// The block index in the answer at `response`; false if no block was left to take.
+__device__ __forceinline__ bool clc_read(uint32_t response, int* x, int* y) {
+    uint32_t got, bx, by;
+    asm volatile(
+        "{\n\t.reg .b128 r;\n\t.reg .pred p;\n\t.reg .b32 z, w;\n\t"
+        "ld.shared.b128 r, [%3];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, r;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "mov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\t"
+        "@p clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%1, %2, z, w}, r;\n\t}"
+        : "=r"(got), "=r"(bx), "=r"(by)
+        : "r"(response)
+        : "memory");
+    *x = (int)bx;
+    *y = (int)by;
+    return got != 0;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          const Params p) {
+    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+    const int nt = p.nt;
+    const int tiles = p.tile_expert != nullptr ? p.num_tiles[0] : (p.total_rows + nt - 1) / nt;
+    const int num_kb = (p.k_dim + kBlockK - 1) / kBlockK;
+    const int kStages = p.stages;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t stage_bytes = NA * kTileABytes + nt * kBlockK * 2;
+    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4 + 2 * kSchedSlots];
+    __shared__ __align__(16) uint4 sched_s[kSchedSlots];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+    __shared__ float route_s[2][128];
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * kMaxStages]), acc_empty0 = smem_u32(&bars[2 * kMaxStages + 2]);
+    const uint32_t sched_full0 = smem_u32(&bars[2 * kMaxStages + 4]);
+    const uint32_t sched_empty0 = smem_u32(&bars[2 * kMaxStages + 4 + kSchedSlots]);
+    const uint32_t sched0 = smem_u32(&sched_s[0]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    uint32_t cols = 32;
+    while ((int)cols < 2 * NA * nt) cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);       // one arrival per epilogue warp
+        }
+        for (int q = 0; q < kSchedSlots; ++q) {
+            mbar_init(sched_full0 + 8 * q, 1);
+            mbar_init(sched_empty0 + 8 * q, 5);     // the MMA thread and the four epilogue warps
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                     "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    // Every role walks the same list of items: its own block index first, then the answers in
+    // the scheduling ring.  `next_item` waits for answer j (the item after item j).
+    int bx = blockIdx.x, by = blockIdx.y;
+    // role: 0 the loader (it frees nothing), 1 a single thread, 2 a whole warp
+    auto next_item = [&](int j, int role) -> bool {
+        const int q = j % kSchedSlots;
+        if (!mbar_wait(sched_full0 + 8 * q, (j / kSchedSlots) & 1, &abort_s)) {
+            abort_s = 1;
+            atomicCAS(p.error, 0, 5);
+            return false;
+        }
+        const bool more = clc_read(sched0 + 16 * q, &bx, &by);
+        if (role == 2) __syncwarp();          // every lane has read the slot
+        if (role != 0 && lane == 0) mbar_arrive(sched_empty0 + 8 * q);
+        return more;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            int asked = 0;          // requests made so far
+            int expert = 0, row0 = by * nt;
+            if (p.tile_expert != nullptr && by < tiles) {
+                expert = p.tile_expert[by];
+                row0 = p.tile_row0[by];
+            }
+            for (int j = 0; ok; ++j) {
+                // ask for the item after this one; the answer comes while this item streams
+                {
+                    const int q = j % kSchedSlots;
+                    if (!mbar_wait(sched_empty0 + 8 * q, ((j / kSchedSlots) & 1) ^ 1, &abort_s)) {
+                        abort_s = 1;
+                        atomicCAS(p.error, 0, 6);
+                        break;
+                    }
+                    clc_try_cancel(sched0 + 16 * q, sched_full0 + 8 * q);
+                    asked = j + 1;
+                }
+                const int tile = by, n0 = bx * kBlockM;
+                // The answer is read half-way through this item (it has had time to arrive, and
+                // the ring is full), and the next tile's expert and first row are fetched then,
+                // so the first copies of the next item do not wait for them.
+                bool answered = false, more = false;
+                int expert_next = 0, row0_next = 0;
+                auto read_answer = [&]() {
+                    answered = true;
+                    more = next_item(j, 0);
+                    row0_next = by * nt;
+                    if (more && p.tile_expert != nullptr && by < tiles) {
+                        expert_next = p.tile_expert[by];
+                        row0_next = p.tile_row0[by];
+                    }
+                };
+                if (tile < tiles) {
+                    const int wy = expert * p.w_rows_per_expert + n0;
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        if (kb == num_kb / 2) {
+                            read_answer();
+                            if (abort_s) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                        const int s = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) {
+                            abort_s = 1;
+                            atomicCAS(p.error, 0, 1);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+                        mbar_expect_tx(full0 + 8 * s, stage_bytes);
+                        tma_load_2d(a, &map_w, full0 + 8 * s, kb * kBlockK, wy);
+                        if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * s, kb * kBlockK, wy + p.up_offset);
+                        tma_load_2d(a + NA * kTileABytes, &map_x, full0 + 8 * s, kb * kBlockK, row0);
+                    }
+                }
+                if (ok && !answered) read_answer();
+                if (!ok || !more) break;
+                expert = expert_next;
+                row0 = row0_next;
+            }
+            if (abort_s) {
+                // let what is still in flight land before the CTA's shared memory goes away:
+                // the copies of the ring and the answer to the last request
+                for (int k = max(0, it - kStages); k < it; ++k) {
+                    const uint32_t bar = full0 + 8 * (k % kStages);
+                    const uint32_t ph = (k / kStages) & 1;
+                    for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(bar, ph); ++i) {}
+                }
+                if (asked > 0) {
+                    const int j = asked - 1;
+                    const uint32_t bar = sched_full0 + 8 * (j % kSchedSlots);
+                    for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(bar, (j / kSchedSlots) & 1); ++i) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(nt);
+            int it = 0, used = 0;       // used: items that took an accumulator buffer
+            bool ok = true;
+            for (int j = 0; ok; ++j) {
+                if (by < tiles) {
+                    const int b = used & 1;
+                    if (!mbar_wait(acc_empty0 + 8 * b, ((used >> 1) & 1) ^ 1, &abort_s)) {   // the epilogue has drained buffer b
+                        abort_s = 1;
+                        atomicCAS(p.error, 0, 4);
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t acc_col = tmem_base + (uint32_t)(b * NA * nt);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) {
+                            abort_s = 1;
+                            atomicCAS(p.error, 0, 2);
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+                        const uint64_t da = smem_desc(a), db = smem_desc(a + NA * kTileABytes);
+#pragma unroll
+                        for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                            const uint64_t adv = (uint64_t)((kk * kUmmaK * 2) >> 4);      // 32 bytes per K step
+                            const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                            umma(acc_col, da + adv, db + adv, idesc, acc);
+                            if (NA == 2) umma(acc_col + (uint32_t)nt, smem_desc(a + kTileABytes) + adv, db + adv, idesc, acc);
+                        }
+                        umma_commit(empty0 + 8 * s);     // frees the stage when these MMAs have read it
+                    }
+                    if (!ok) break;
+                    umma_commit(acc_full0 + 8 * b);      // arrives when every MMA of this item has finished
+                    ++used;
+                }
+                if (!next_item(j, 1)) break;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
+        const int et = threadIdx.x - 64;         // 0..127 among the epilogue threads
+        int used = 0;
+        for (int j = 0;; ++j) {
+            if (by < tiles) {
+                const int b = used & 1;
+                const int tile = by, n0 = bx * kBlockM;
+                int row0 = tile * nt, row_end = p.total_rows;
+                if (p.tile_expert != nullptr) {
+                    row0 = p.tile_row0[tile];
+                    row_end = p.offsets[p.tile_expert[tile] + 1];
+                }
+                const int valid = min(nt, row_end - row0);
+                if (MODE == MODE_DOWN) {
+                    if (et < nt) route_s[b][et] = et < valid ? p.route_w[p.sorted[row0 + et]] : 0.f;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                if (!mbar_wait(acc_full0 + 8 * b, (used >> 1) & 1, &abort_s)) {
+                    abort_s = 1;
+                    atomicCAS(p.error, 0, 3);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int n = n0 + quarter * 32 + lane;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NA * nt);
+                for (int c0 = 0; c0 < nt; c0 += 16) {
+                    if (c0 >= valid) break;          // warp-uniform
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + c0, g);
+                    if (NA == 2) tmem_ld16(taddr + nt + c0, u);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < p.n_out) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            if (c0 + jj >= valid) break;
+                            float v = __uint_as_float(g[jj]);
+                            if (MODE == MODE_GATE_UP) {
+                                const float gate = round_act<__nv_bfloat16>(v);
+                                const float up = round_act<__nv_bfloat16>(__uint_as_float(u[jj]));
+                                v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
+                            } else if (MODE == MODE_DOWN) {
+                                v *= route_s[b][c0 + jj];
+                            }
+                            p.out[(size_t)(row0 + c0 + jj) * p.n_out + n] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+                // this warp has read its lanes of buffer b: hand it back to the MMA thread
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * b);
+                ++used;
+            }
+            if (!next_item(j, 2)) break;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(cols) : "memory");
+    }
+}
+
 // out[p, :] = x[sorted[p] / top_k, :]  (activation rows gathered into expert order)
 __global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted,
                                     __nv_bfloat16* __restrict__ out, int width, int top_k) {
@@ -351,8 +659,50 @@ static int make_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t c
     return 0;
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+static bool persistent_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("SE_TC_PERSISTENT");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
+template <int MODE>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
+    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+    size_t smem = (size_t)p.stages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             224 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    // A CTA takes 2 * NA * nt columns of tensor memory (512 per SM).  Where two CTAs would
+    // fit by shared memory but not by columns, ask for more than half of the shared memory, so
+    // that no CTA waits for columns behind a persistent neighbour.
+    int cols = 32;
+    while (cols < 2 * NA * p.nt) cols <<= 1;
+    if (2 * cols > 512) smem = std::max<size_t>(smem, 116 * 1024);
+    dim3 grid(ceil_div(p.n_out, kBlockM), tiles);
+    gemm_tc_persistent_kernel<MODE><<<grid, kThreads, smem, stream>>>(mw, mx, p);
+    return (int)cudaGetLastError();
+}
+
 template <int MODE>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
+    if (persistent_enabled()) return launch_persistent<MODE>(mw, mx, p, tiles, stream);
     constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
     const size_t smem = (size_t)p.stages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
     static bool configured = false;
@@ -386,7 +736,7 @@ static int pick_stages(int na, int nt) {
     const int stage_bytes = na * kTileABytes + nt * kBlockK * 2;
     int stages = na == 2 && nt <= 32 ? 3 : 4;      // measured: three 34 KB stages x two CTAs per SM stream a little faster
     while (stages < kMaxStages && (stages + 1) * stage_bytes + 1024 <= 100 * 1024) ++stages;   // two CTAs per SM
-    while (stages > 2 && stages * stage_bytes + 1024 > 226 * 1024) --stages;
+    while (stages > 2 && stages * stage_bytes + 1024 > 224 * 1024) --stages;
     return stages;
 }
 

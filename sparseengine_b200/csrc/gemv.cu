@@ -7,18 +7,20 @@
 // m16n8k16 tensor-core fragments.  The fragment's k slots are filled in a permuted order
 // (slot pairs {2t, 2t+1} and {2t+8, 2t+9} of lane t take 4 consecutive elements), which is
 // harmless because A and B use the same permutation and the sum over k does not care.  No
-// shared memory on the way in; the eight warps of a block split K and add their partial
+// shared memory on the way in; the 8 or 16 warps of a block split K and add their partial
 // sums through shared memory at the end.  The weights are read exactly once.
 #include "common.cuh"
 #include "mma_util.cuh"
+#include <cstdlib>
 
 namespace se {
 namespace gemv {
 
-constexpr int kWarps = 8;
-constexpr int kRowsPerBlock = 16;
-
-template <int NT>   // 8-row tiles of x: 1 (up to 8 rows) or 2 (up to 16)
+// NT: 8-row tiles of x, 1 (up to 8 rows) or 2 (up to 16).  kWarps: warps of a block, which
+// split K.  kRowsPerBlock: weight rows of a block, 16 (a full fragment) or 8 (the fragment's
+// upper half stays zero): fewer rows make more blocks, which a matrix with few rows needs to
+// keep every SM loading.
+template <int NT, int kWarps, int kRowsPerBlock>
 __global__ void __launch_bounds__(32 * kWarps)
 gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
             int rows, int n_out, int k_dim) {
@@ -43,7 +45,8 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll 8
     for (int c = c_begin; c < c_end; ++c) {
         const uint4 a_lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + c * 32));     // streamed once
-        const uint4 a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
+        uint4 a_hi = make_uint4(0u, 0u, 0u, 0u);
+        if (kRowsPerBlock == 16) a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             uint4 b = make_uint4(0u, 0u, 0u, 0u);
@@ -59,8 +62,10 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     for (int nt = 0; nt < NT; ++nt) {
         part[warp][g][nt * 8 + 2 * t4] = acc[nt][0];
         part[warp][g][nt * 8 + 2 * t4 + 1] = acc[nt][1];
-        part[warp][g + 8][nt * 8 + 2 * t4] = acc[nt][2];
-        part[warp][g + 8][nt * 8 + 2 * t4 + 1] = acc[nt][3];
+        if (kRowsPerBlock == 16) {
+            part[warp][g + 8][nt * 8 + 2 * t4] = acc[nt][2];
+            part[warp][g + 8][nt * 8 + 2 * t4 + 1] = acc[nt][3];
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < kRowsPerBlock * 8 * NT; i += blockDim.x) {
@@ -81,16 +86,31 @@ extern "C" int se_gemv_supported(int rows, int n_out, int k_dim) {
     return (rows >= 1 && rows <= 16 && n_out >= 1 && k_dim >= 32 && k_dim % 32 == 0) ? 1 : 0;
 }
 
+template <int NT, int W, int R>
+static void launch_gemv(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, cudaStream_t stream) {
+    se::gemv::gemv_kernel<NT, W, R><<<se::ceil_div(n_out, R), 32 * W, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
+}
+
 // x [rows <= 16, k_dim], w [n_out, k_dim], out [rows, n_out]; bf16; k_dim a multiple of 32.
 extern "C" int se_gemv(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!se_gemv_supported(rows, n_out, k_dim)) return SE_ERR_UNSUPPORTED;
-    const int blocks = se::ceil_div(n_out, se::gemv::kRowsPerBlock);
-    if (rows <= 8)
-        se::gemv::gemv_kernel<1><<<blocks, 32 * se::gemv::kWarps, 0, stream>>>(
-            (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
-    else
-        se::gemv::gemv_kernel<2><<<blocks, 32 * se::gemv::kWarps, 0, stream>>>(
-            (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
+    // Shape = 100 * (warps that split K) + (weight rows per block).  A warp's walk over its
+    // share of K is one chain of dependent loads, so a long K takes more warps (measured:
+    // K = 6144 runs in 9.4 us with 16 warps, 14.4 us with 8).  SE_GEMV_SHAPE overrides (tuning aid).
+    static const int force = [] { const char* v = std::getenv("SE_GEMV_SHAPE"); return v ? atoi(v) : 0; }();
+    const int shape = force ? force : (k_dim >= 4096 ? 1616 : 816);
+    const int nt = rows <= 8 ? 1 : 2;
+#define SE_GEMV_CASE(W, R)                                                       \
+    case W * 100 + R:                                                            \
+        if (nt == 1) launch_gemv<1, W, R>(x, w, out, rows, n_out, k_dim, stream); \
+        else launch_gemv<2, W, R>(x, w, out, rows, n_out, k_dim, stream);         \
+        break;
+    switch (shape) {
+        SE_GEMV_CASE(4, 8) SE_GEMV_CASE(4, 16) SE_GEMV_CASE(8, 8) SE_GEMV_CASE(8, 16) SE_GEMV_CASE(16, 8) SE_GEMV_CASE(16, 16)
+        default: return SE_ERR_ARGUMENT;
+    }
+#undef SE_GEMV_CASE
     SE_LAUNCH_CHECK();
 }
