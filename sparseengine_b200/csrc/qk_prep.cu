@@ -107,6 +107,107 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     }
 }
 
+// Many tokens: one block per token, every thread moves groups of 8 consecutive dims with
+// 16-byte accesses.  A work item is (head, group): a group below rot/2 is rotated together
+// with its partner group rot/2 dims further on, groups from rot on pass through, and the
+// value heads are copied.  Same arithmetic per element as qk_prep_kernel; the block first takes
+// the statistics of the token's whole q and k projections.  Needs d, rot/2 and the row pitch to
+// be multiples of 8 elements.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
+                   const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                   const int* __restrict__ token_seq, const int* __restrict__ seq_rows,
+                   const int* __restrict__ table, int table_stride, T* __restrict__ cache, T* __restrict__ q_out,
+                   int hq, int hkv, int d, int rot, float eps, float rope_scale, int page_size, int write_cache) {
+    extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
+    const int t = blockIdx.x;
+    const int qn = hq * d, kn = hkv * d;
+    const T* row = qkv + (size_t)t * (qn + 2 * kn);
+    const int pos = positions[t];
+    const int half = rot / 2;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[j], &s, &c);
+        cs[j] = c * rope_scale;
+        cs[half + j] = s * rope_scale;
+    }
+    __syncthreads();
+    // statistics of the whole q and k projections of this token (the row is re-read from L1/L2 below)
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_w != nullptr) {
+        __shared__ float scratch[33];
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const T* part = row + (which ? qn : 0);
+            const int n = which ? kn : qn;
+            float ss = 0.f;
+            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+                float v[8];
+                load8(part + i, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            }
+            ss = block_sum(ss, scratch);
+            (which ? inv_k : inv_q) = 1.0f / sqrtf(ss / (float)n + eps);
+        }
+    }
+    T* kv_base = nullptr;
+    if (write_cache) {
+        const int page = table[(size_t)seq_rows[token_seq[t]] * table_stride + pos / page_size];
+        kv_base = cache + (size_t)page * 2 * hkv * page_size * d + (size_t)(pos % page_size) * d;
+    }
+    const int groups = d / 8, rot_groups = half / 8;
+    const int live = groups - rot_groups;                  // items per head: rotated pairs, then pass-through groups
+    const int qk_heads = hq + (write_cache ? hkv : 0);
+    const int qk_items = qk_heads * live;
+    const int v_items = write_cache ? hkv * groups : 0;
+    for (int item = threadIdx.x; item < qk_items + v_items; item += blockDim.x) {
+        if (item >= qk_items) {                            // value head: copy
+            const int h = (item - qk_items) / groups, g = (item - qk_items) % groups;
+            const T* src = row + qn + kn + h * d + 8 * g;
+            T* dst = kv_base + (size_t)(hkv + h) * page_size * d + 8 * g;
+            float v[8];
+            load8(src, v);
+            store8(dst, v);
+            continue;
+        }
+        const int hh = item / live, i = item % live;
+        const bool is_q = hh < hq;
+        const int h = is_q ? hh : hh - hq;
+        const T* w = is_q ? q_w : k_w;
+        const float inv = is_q ? inv_q : inv_k;
+        const T* src = row + (is_q ? 0 : qn) + h * d;
+        T* dst = is_q ? q_out + (size_t)t * qn + h * d : kv_base + (size_t)h * page_size * d;
+        auto normed8 = [&](int dim0, float* out) {
+            load8(src + dim0, out);
+            if (w != nullptr) {
+                float wv[8];
+                load8(w + h * d + dim0, wv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) out[j] = round_act<T>(round_act<T>(out[j] * inv) * wv[j]);
+            }
+        };
+        if (i < rot_groups) {
+            float x1[8], x2[8], o1[8], o2[8];
+            normed8(8 * i, x1);
+            normed8(8 * i + half, x2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float c = cs[8 * i + j], sn = cs[half + 8 * i + j];
+                o1[j] = x1[j] * c - x2[j] * sn;
+                o2[j] = x2[j] * c + x1[j] * sn;
+            }
+            store8(dst + 8 * i, o1);
+            store8(dst + 8 * i + half, o2);
+        } else {
+            float x[8];
+            normed8(8 * (i + rot_groups), x);
+            store8(dst + 8 * (i + rot_groups), x);
+        }
+    }
+}
+
 // inv_rms[t] = (1/sqrt(mean(q^2)+eps), 1/sqrt(mean(k^2)+eps)) of token t's whole projections:
 // for many tokens the statistics are taken once here instead of once per head.
 template <typename T>
@@ -143,6 +244,18 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
     if (rot < 0 || rot > d || (rot & 1)) return SE_ERR_ARGUMENT;
     if (inv_freq == nullptr) rot = 0;
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    // many tokens and sizes that allow 16-byte groups: one block per token does everything
+    const int elem = dtype == SE_DTYPE_BF16 ? 2 : 4;
+    const bool vec = tokens > 64 && (q_w == nullptr) == (k_w == nullptr) && d % 8 == 0 && (rot / 2) % 8 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0 &&
+                     ((size_t)page_size * d * elem) % 16 == 0;
+    if (vec) {
+        SE_DISPATCH_DTYPE(dtype, T,
+            se::qk_prep_vec_kernel<T><<<tokens, 256, smem, stream>>>(
+                (const T*)qkv, (const T*)q_w, (const T*)k_w, inv_freq, positions, token_seq, seq_rows, table,
+                table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size, write_cache));
+        SE_LAUNCH_CHECK();
+    }
     // inv_rms: optional float [tokens, 2] workspace; when given (many tokens) the statistics
     // are computed once per token by a first kernel
     const bool two_pass = inv_rms != nullptr && q_w != nullptr;

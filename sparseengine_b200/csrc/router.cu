@@ -123,6 +123,17 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
     return make_float4(a.x, a.y, b.x, b.y);
 }
 
+template <int N, int M>
+__device__ __forceinline__ void halve_over_lanes(float* v, int lane) {
+    const bool upper = (lane & M) != 0;
+#pragma unroll
+    for (int k = 0; k < N / 2; ++k) {
+        const float send = upper ? v[k] : v[k + N / 2];
+        const float keep = upper ? v[k + N / 2] : v[k];
+        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, M);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256, 2)
 router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ gate, float* __restrict__ logits,
@@ -196,13 +207,18 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
             if (c + 2 < chunks) __syncthreads();
         }
         __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float v = warp_sum(acc[i][j]);
-                if (lane == 0) qsum[warp][quarter][i * 8 + j] = v;
-            }
+        // 64 sums over the lanes at once: each step halves the values a lane holds and adds
+        // the partner's copy of the half it keeps.  The pairs are those of warp_sum (lanes
+        // l and l ^ 16, then ^ 8, 4, 2, 1) and a + b = b + a, so every total has warp_sum's
+        // bits; lane l ends with the totals of values 2l and 2l + 1.
+        float* v = &acc[0][0];
+        halve_over_lanes<64, 16>(v, lane);
+        halve_over_lanes<32, 8>(v, lane);
+        halve_over_lanes<16, 4>(v, lane);
+        halve_over_lanes<8, 2>(v, lane);
+        halve_over_lanes<4, 1>(v, lane);
+        qsum[warp][quarter][2 * lane] = v[0];
+        qsum[warp][quarter][2 * lane + 1] = v[1];
     }
     __syncwarp();
     for (int o = lane; o < 64; o += 32) {

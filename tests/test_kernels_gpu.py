@@ -82,9 +82,11 @@ def _cache_setup(tokens_per_seq, hkv, d, page, dtype, firsts=None):
 @pytest.mark.parametrize("hq,hkv,d,rot,page,theta,norm", [
     (4, 2, 16, 8, 4, 1e4, True), (6, 3, 32, 32, 8, 1e6, True), (5, 1, 48, 16, 16, 5e4, True),
     (7, 7, 80, 0, 3, 1e4, False), (3, 1, 32, 16, 8, 1e4, False), (48, 8, 128, 64, 16, 5e6, True)])
-def test_qk_prep_norm_rotary_and_cache_write(dtype, hq, hkv, d, rot, page, theta, norm):
+@pytest.mark.parametrize("lens", [[5, 1, 19], [70, 1, 40]], ids=["few_tokens", "many_tokens"])
+def test_qk_prep_norm_rotary_and_cache_write(dtype, hq, hkv, d, rot, page, theta, norm, lens):
+    """Few tokens take the kernel with a block per head, many tokens the two-pass kernels
+    (16-byte groups where the sizes allow it, element by element otherwise)."""
     from sparseengine_b200.csrc import ops
-    lens = [5, 1, 19]
     t = sum(lens)
     # one request sits at large positions (large rotation angles, a far table index)
     table, rows, positions, token_seq, cache = _cache_setup(lens, hkv, d, page, dtype, firsts=[0, 3, 1000])
