@@ -21,6 +21,11 @@
 // issues the MMAs (one elected lane), warps 2-5 run the epilogue (one TMEM lane quarter
 // each).  Every wait on an mbarrier is bounded; on a timeout the CTA records an error code,
 // drains its outstanding copies, frees its tensor memory and returns.
+//
+// A work item is one block index of the grid: NA blocks of 128 weight rows (the gate and the
+// up block of MODE_GATE_UP, one block in the other modes; two neighbouring blocks per item
+// were measured there and gained nothing) times one tile of activation rows, which the NA
+// accumulators share.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -131,163 +136,6 @@ struct Params {
     int stages;                 // depth of the shared-memory ring
 };
 
-template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
-    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
-    int tile = blockIdx.y, expert = 0, row0, row_end;
-    if (p.tile_expert != nullptr) {
-        if (tile >= p.num_tiles[0]) return;
-        expert = p.tile_expert[tile];
-        row0 = p.tile_row0[tile];
-        row_end = p.offsets[expert + 1];
-    } else {
-        row0 = tile * p.nt;
-        row_end = p.total_rows;
-        if (row0 >= row_end) return;
-    }
-    const int n0 = blockIdx.x * kBlockM;
-    const int nt = p.nt;
-    const int valid = min(nt, row_end - row0);
-    const int num_kb = (p.k_dim + kBlockK - 1) / kBlockK;
-
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const uint32_t stage_bytes = NA * kTileABytes + nt * kBlockK * 2;
-    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
-    const int kStages = p.stages;
-    __shared__ uint32_t tmem_base_s;
-    __shared__ volatile int abort_s;
-    __shared__ float route_s[128];
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]), accum = smem_u32(&bars[2 * kMaxStages]);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    uint32_t cols = 32;
-    while ((int)cols < NA * nt) cols <<= 1;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
-        }
-        mbar_init(accum, 1);
-        abort_s = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
-                     "r"(cols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = tmem_base_s;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            int issued = 0;
-            const int wy = expert * p.w_rows_per_expert + n0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t ph = (kb / kStages) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) {
-                    abort_s = 1;
-                    atomicCAS(p.error, 0, 1);
-                    break;
-                }
-                const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
-                mbar_expect_tx(full0 + 8 * s, stage_bytes);
-                tma_load_2d(a, &map_w, full0 + 8 * s, kb * kBlockK, wy);
-                if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * s, kb * kBlockK, wy + p.up_offset);
-                tma_load_2d(a + NA * kTileABytes, &map_x, full0 + 8 * s, kb * kBlockK, row0);
-                issued = kb + 1;
-            }
-            if (abort_s) {
-                // let copies already in flight land before the CTA's shared memory goes away
-                for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
-                    const uint32_t bar = full0 + 8 * (kb % kStages);
-                    const uint32_t ph = (kb / kStages) & 1;
-                    for (uint32_t i = 0; i < kSpinLimit && !mbar_try_wait(bar, ph); ++i) {}
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = instr_desc(nt);
-            bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t ph = (kb / kStages) & 1;
-                if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) {
-                    abort_s = 1;
-                    atomicCAS(p.error, 0, 2);
-                    ok = false;
-                    break;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
-                const uint64_t da = smem_desc(a), db = smem_desc(a + NA * kTileABytes);
-#pragma unroll
-                for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-                    const uint64_t adv = (uint64_t)((kk * kUmmaK * 2) >> 4);      // 32 bytes per K step
-                    const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-                    umma(tmem_base, da + adv, db + adv, idesc, acc);
-                    if (NA == 2) umma(tmem_base + (uint32_t)nt, smem_desc(a + kTileABytes) + adv, db + adv, idesc, acc);
-                }
-                umma_commit(empty0 + 8 * s);     // frees the stage when these MMAs have read it
-            }
-            umma_commit(accum);                  // arrives when every MMA above has finished
-        }
-    } else {
-        const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
-        const int et = threadIdx.x - 64;         // 0..127 among the epilogue threads
-        if (MODE == MODE_DOWN) {
-            if (et < nt) route_s[et] = et < valid ? p.route_w[p.sorted[row0 + et]] : 0.f;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        const bool ready = mbar_wait(accum, 0, &abort_s);
-        if (!ready) {
-            abort_s = 1;
-            atomicCAS(p.error, 0, 3);
-        } else {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int n = n0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            for (int c0 = 0; c0 < nt; c0 += 16) {
-                if (c0 >= valid) break;          // warp-uniform
-                uint32_t g[16], u[16];
-                tmem_ld16(taddr + c0, g);
-                if (NA == 2) tmem_ld16(taddr + nt + c0, u);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.n_out) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j >= valid) break;
-                        float v = __uint_as_float(g[j]);
-                        if (MODE == MODE_GATE_UP) {
-                            const float gate = round_act<__nv_bfloat16>(v);
-                            const float up = round_act<__nv_bfloat16>(__uint_as_float(u[j]));
-                            v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
-                        } else if (MODE == MODE_DOWN) {
-                            v *= route_s[c0 + j];
-                        }
-                        p.out[(size_t)(row0 + c0 + j) * p.n_out + n] = __float2bfloat16_rn(v);
-                    }
-                }
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(cols) : "memory");
-    }
-}
-
-
 // ---- the persistent form ---------------------------------------------------------------------
 // The same roles and the same arithmetic, but a CTA does not end with its item (one 128-row
 // block of one tile = one block index of the grid).  When it starts an item it asks the
@@ -331,11 +179,14 @@ __device__ __forceinline__ bool clc_read(uint32_t response, int* x, int* y) {
     return got != 0;
 }
 
-template <int MODE>
+template <int MODE, int NA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const Params p) {
-    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+    static_assert(MODE != MODE_GATE_UP || NA == 2, "gate and up are the two blocks of an item");
+    // rows of the weight view between the item's blocks, and weight rows (= outputs) per item
+    const int second = MODE == MODE_GATE_UP ? p.up_offset : kBlockM;
+    constexpr int kItemM = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
     const int nt = p.nt;
     const int tiles = p.tile_expert != nullptr ? p.num_tiles[0] : (p.total_rows + nt - 1) / nt;
     const int num_kb = (p.k_dim + kBlockK - 1) / kBlockK;
@@ -425,7 +276,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     clc_try_cancel(sched0 + 16 * q, sched_full0 + 8 * q);
                     asked = j + 1;
                 }
-                const int tile = by, n0 = bx * kBlockM;
+                const int tile = by, n0 = bx * kItemM;
                 // The answer is read half-way through this item (it has had time to arrive, and
                 // the ring is full), and the next tile's expert and first row are fetched then,
                 // so the first copies of the next item do not wait for them.
@@ -461,7 +312,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                         const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
                         mbar_expect_tx(full0 + 8 * s, stage_bytes);
                         tma_load_2d(a, &map_w, full0 + 8 * s, kb * kBlockK, wy);
-                        if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * s, kb * kBlockK, wy + p.up_offset);
+                        if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * s, kb * kBlockK, wy + second);
                         tma_load_2d(a + NA * kTileABytes, &map_x, full0 + 8 * s, kb * kBlockK, row0);
                     }
                 }
@@ -535,7 +386,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         for (int j = 0;; ++j) {
             if (by < tiles) {
                 const int b = used & 1;
-                const int tile = by, n0 = bx * kBlockM;
+                const int tile = by, n0 = bx * kItemM;
                 int row0 = tile * nt, row_end = p.total_rows;
                 if (p.tile_expert != nullptr) {
                     row0 = p.tile_row0[tile];
@@ -552,27 +403,45 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int n = n0 + quarter * 32 + lane;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NA * nt);
-                for (int c0 = 0; c0 < nt; c0 += 16) {
-                    if (c0 >= valid) break;          // warp-uniform
-                    uint32_t g[16], u[16];
-                    tmem_ld16(taddr + c0, g);
-                    if (NA == 2) tmem_ld16(taddr + nt + c0, u);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (n < p.n_out) {
+                if (MODE == MODE_GATE_UP) {
+                    const int n = n0 + quarter * 32 + lane;
+                    for (int c0 = 0; c0 < nt; c0 += 16) {
+                        if (c0 >= valid) break;          // warp-uniform
+                        uint32_t g[16], u[16];
+                        tmem_ld16(taddr + c0, g);
+                        tmem_ld16(taddr + nt + c0, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (n < p.n_out) {
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) {
-                            if (c0 + jj >= valid) break;
-                            float v = __uint_as_float(g[jj]);
-                            if (MODE == MODE_GATE_UP) {
-                                const float gate = round_act<__nv_bfloat16>(v);
+                            for (int jj = 0; jj < 16; ++jj) {
+                                if (c0 + jj >= valid) break;
+                                const float gate = round_act<__nv_bfloat16>(__uint_as_float(g[jj]));
                                 const float up = round_act<__nv_bfloat16>(__uint_as_float(u[jj]));
-                                v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
-                            } else if (MODE == MODE_DOWN) {
-                                v *= route_s[b][c0 + jj];
+                                const float v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
+                                p.out[(size_t)(row0 + c0 + jj) * p.n_out + n] = __float2bfloat16_rn(v);
                             }
-                            p.out[(size_t)(row0 + c0 + jj) * p.n_out + n] = __float2bfloat16_rn(v);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int blk = 0; blk < NA; ++blk) {
+                        const int n = n0 + blk * kBlockM + quarter * 32 + lane;
+                        if (n0 + blk * kBlockM >= p.n_out) break;       // warp-uniform: no such block
+                        for (int c0 = 0; c0 < nt; c0 += 16) {
+                            if (c0 >= valid) break;      // warp-uniform
+                            uint32_t g[16];
+                            tmem_ld16(taddr + blk * nt + c0, g);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (n < p.n_out) {
+#pragma unroll
+                                for (int jj = 0; jj < 16; ++jj) {
+                                    if (c0 + jj >= valid) break;
+                                    float v = __uint_as_float(g[jj]);
+                                    if (MODE == MODE_DOWN) v *= route_s[b][c0 + jj];
+                                    p.out[(size_t)(row0 + c0 + jj) * p.n_out + n] = __float2bfloat16_rn(v);
+                                }
+                            }
                         }
                     }
                 }
@@ -659,33 +528,14 @@ static int make_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t c
     return 0;
 }
 
-static int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            n <= 0)
-            n = 148;
-    }
-    return n;
-}
-
-static bool persistent_enabled() {
-    static const bool on = [] {
-        const char* v = std::getenv("SE_TC_PERSISTENT");
-        return !(v && v[0] == '0');
-    }();
-    return on;
-}
-
-template <int MODE>
-static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
-    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
+// NA: blocks of 128 weight rows per work item (2 for gate/up, else 1).
+template <int MODE, int NA>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
     size_t smem = (size_t)p.stages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             224 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<MODE, NA>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -695,25 +545,9 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const
     int cols = 32;
     while (cols < 2 * NA * p.nt) cols <<= 1;
     if (2 * cols > 512) smem = std::max<size_t>(smem, 116 * 1024);
-    dim3 grid(ceil_div(p.n_out, kBlockM), tiles);
-    gemm_tc_persistent_kernel<MODE><<<grid, kThreads, smem, stream>>>(mw, mx, p);
-    return (int)cudaGetLastError();
-}
-
-template <int MODE>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int tiles, cudaStream_t stream) {
-    if (persistent_enabled()) return launch_persistent<MODE>(mw, mx, p, tiles, stream);
-    constexpr int NA = MODE == MODE_GATE_UP ? 2 : 1;
-    const size_t smem = (size_t)p.stages * (NA * kTileABytes + p.nt * kBlockK * 2) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             226 * 1024);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    dim3 grid(ceil_div(p.n_out, kBlockM), tiles);
-    gemm_tc_kernel<MODE><<<grid, kThreads, smem, stream>>>(mw, mx, p);
+    const int item_m = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
+    dim3 grid(ceil_div(p.n_out, item_m), tiles);
+    gemm_tc_persistent_kernel<MODE, NA><<<grid, kThreads, smem, stream>>>(mw, mx, p);
     return (int)cudaGetLastError();
 }
 
@@ -770,9 +604,11 @@ extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, co
     if (rc) return rc;
     rc = make_map(&mx, a, assignments, k_dim, nt);
     if (rc) return rc;
+    const int na = mode == 0 ? 2 : 1;
     Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
-             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(mode == 0 ? 2 : 1, nt)};
-    return mode == 0 ? launch<MODE_GATE_UP>(mw, mx, p, max_tiles, stream) : launch<MODE_DOWN>(mw, mx, p, max_tiles, stream);
+             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(na, nt)};
+    if (mode == 0) return launch<MODE_GATE_UP, 2>(mw, mx, p, max_tiles, stream);
+    return launch<MODE_DOWN, 1>(mw, mx, p, max_tiles, stream);
 }
 
 // Dense projection on tensor cores: out[rows, n_out] = x[rows, k_dim] · w[n_out, k_dim]ᵀ (bf16, fp32 accumulate).
@@ -787,5 +623,5 @@ extern "C" int se_gemm_tc_dense(const void* x, const void* w, void* out, int* er
     if (rc) return rc;
     Params p{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (__nv_bfloat16*)out, error,
              n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt)};
-    return launch<MODE_DENSE>(mw, mx, p, se::ceil_div(rows, nt), stream);
+    return launch<MODE_DENSE, 1>(mw, mx, p, se::ceil_div(rows, nt), stream);
 }
