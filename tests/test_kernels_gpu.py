@@ -462,6 +462,58 @@ def test_prefill_attention_tensor_cores(hq, hkv, d, page, window, impl):
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kernel", ["decode", "prefill_mma_sync", "prefill_tcgen05"])
+@pytest.mark.parametrize("window", [None, 1000])
+def test_tensor_core_attention_far_key_and_window_edge(kernel, window):
+    """Random keys would hide a key that is skipped or seen wrongly, so one key is made to
+    dominate the last query's scores: wherever it lies (first or last slot of a page, the
+    first page, a split's or a tile's edge) the output must be its value.  With a window,
+    the key just outside it must not be seen at all and the key just inside it must be."""
+    from sparseengine_b200.csrc import ops
+    hq, hkv, d, page, n = 8, 2, 128, 16, 3000
+    dtype = torch.bfloat16
+    q_len = 1 if kernel == "decode" else 130          # the last query is the one that is checked
+    last = n - 1
+    first_seen = 0 if window is None else last - window + 1
+    places = [first_seen, first_seen + 1, last, last - 1, 2047, 2048, first_seen + 15, first_seen + 16]
+    if window is None:
+        places += [15, 16, 1023]
+    else:
+        places += [first_seen - 1, 0]                 # outside the window: must be invisible
+    table, rows, _, _, cache = _cache_setup([n], hkv, d, page, dtype)
+    k = rnd(n, hkv, d, dtype=dtype, scale=0.1, seed=1)
+    v = rnd(n, hkv, d, dtype=dtype, seed=2)
+    q = rnd(q_len, hq, d, dtype=dtype, scale=0.1, seed=3)
+    pos = torch.arange(n, device=DEV)
+    pg = table[int(rows[0]), (pos // page).long()].long()
+    group = hq // hkv
+    for far in places:
+        kk = k.clone()
+        kk[far] = (q[-1, ::group].float() * 300.0).to(dtype)       # KV head g gets the direction of its first query head
+        cache[pg, 0, :, (pos % page).long()] = kk
+        cache[pg, 1, :, (pos % page).long()] = v
+        out = torch.zeros_like(q)
+        if kernel == "decode":
+            ops.attn_decode(q.view(q_len, hq * d), cache, table, rows, torch.zeros(q_len, dtype=torch.int32, device=DEV),
+                            torch.tensor([last], dtype=torch.int32, device=DEV), out.view(q_len, hq * d), num_heads=hq,
+                            num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window, max_keys=n)
+        else:
+            fn = ops.attn_prefill_tc if kernel == "prefill_tcgen05" else ops.attn_prefill
+            fn(q.view(q_len, hq * d), cache, table, rows, torch.tensor([0, q_len], dtype=torch.int32, device=DEV),
+               torch.tensor([n], dtype=torch.int32, device=DEV), out.view(q_len, hq * d), entries=1, max_q_len=q_len,
+               num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
+            ops.tc_check(DEV)
+        got = out[-1].float().cpu()
+        visible = far >= first_seen
+        for g in range(hkv):
+            hit = torch.allclose(got[g * group], v[far, g].float().cpu(), atol=2e-2)
+            assert hit == visible, (kernel, window, far, g)
+        qs = torch.zeros(n, hq, d)
+        qs[n - q_len:] = q.float().cpu()
+        ref = plain_m2.causal_attention(qs, kk.float().cpu(), v.float().cpu(), dtype, window)[n - q_len:]
+        torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("rows,n_out,k_dim", [(1, 16, 32), (8, 8192, 3072), (3, 3072, 6144), (16, 1000, 96), (11, 37, 160),
                                              (5, 200064, 3072)])
 def test_gemv_for_a_handful_of_rows(rows, n_out, k_dim):
