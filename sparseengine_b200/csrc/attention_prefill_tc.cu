@@ -28,8 +28,10 @@ namespace fa {
 constexpr int D = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;
-constexpr int kStages = 5;
-constexpr int kThreads = 224;
+constexpr int kTiles = 2;                            // query tiles per CTA
+constexpr int kStages = 4;
+constexpr int kLoaderWarp2 = 2 + 4 * kTiles;         // the second loader warp
+constexpr int kThreads = 32 * (kLoaderWarp2 + 1);    // loader, MMA, 4 softmax warps per query tile, loader
 constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
 constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
 constexpr int kKVStageBytes = 4 * kHalfBytes;        // K halves, V halves
@@ -113,7 +115,9 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 struct Bars {
-    uint64_t kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t kv_full[kStages], kv_empty[kStages];
+    uint64_t s_full[kTiles][2], s_empty[kTiles][2];      // per query tile: two S buffers
+    uint64_t p_full[kTiles], p_empty[kTiles];            // per query tile: one P buffer
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -123,9 +127,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        int* error, int hq, int hkv, int page_size, float scale_log2, int window) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_s = smem;                               // [2 halves][128 rows][128 B]
-    uint8_t* kv_s = q_s + kQBytes;                     // [stages][K half0, K half1, V half0, V half1]
-    uint8_t* p_s = kv_s + kStages * kKVStageBytes;     // [2][128 rows][128 B]
+    uint8_t* q_s = smem;                               // [2 tiles][2 halves][128 rows][128 B]
+    uint8_t* kv_s = q_s + kTiles * kQBytes;            // [stages][K half0, K half1, V half0, V half1]
+    uint8_t* p_s = kv_s + kStages * kKVStageBytes;     // [2 tiles][128 rows][128 B]
     __shared__ __align__(8) Bars bars;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
@@ -135,13 +139,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int tok0 = cu_q[entry];
     const int q_len = cu_q[entry + 1] - tok0;
     const int total_rows = q_len * group;
-    const int row_base = blockIdx.x * kRows;
+    const int row_base = blockIdx.x * (kTiles * kRows);
     if (row_base >= total_rows) return;
     const int kv_end = kv_len[entry];
     const int q_start = kv_end - q_len;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int last_row = min(row_base + kRows, total_rows) - 1;
+    const int last_row = min(row_base + kTiles * kRows, total_rows) - 1;
     const int max_pos = q_start + last_row / group;
     const int first_pos = q_start + row_base / group;
     const int k_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
@@ -151,28 +155,30 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     auto bar = [&](uint64_t* b) { return smem_u32(b); };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar(&bars.kv_full[s]), 1); mbar_init(bar(&bars.kv_empty[s]), 1); }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar(&bars.s_full[b]), 1);
-            mbar_init(bar(&bars.s_empty[b]), 128);
-            mbar_init(bar(&bars.p_full[b]), 128);
-            mbar_init(bar(&bars.p_empty[b]), 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(&bars.kv_full[s]), 32); mbar_init(bar(&bars.kv_empty[s]), 1); }   // full: every lane of the tile's loader warp
+        for (int x = 0; x < kTiles; ++x) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(bar(&bars.s_full[x][b]), 1);
+                mbar_init(bar(&bars.s_empty[x][b]), 4);      // one arrival per softmax warp
+            }
+            mbar_init(bar(&bars.p_full[x]), 4);
+            mbar_init(bar(&bars.p_empty[x]), 1);
         }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(256) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q tile: every thread copies chunks; rows beyond the tile's rows are zero-filled
-    for (int i = threadIdx.x; i < kRows * 16; i += kThreads) {
-        const int r = i >> 4, c = i & 15;
+    // Q tiles: every thread copies chunks; rows beyond the portion's rows are zero-filled
+    for (int i = threadIdx.x; i < kTiles * kRows * 16; i += kThreads) {
+        const int r = i >> 4, c = i & 15;                  // r: 0..255 over both tiles
         const int row = row_base + r;
         const bool ok = row < total_rows;
         const int rr = ok ? row : total_rows - 1;
         const __nv_bfloat16* src = q + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D + c * 8;
-        cp_async16(smem_u32(q_s) + (c >> 3) * (kRows * 128) + sw128(r, c & 7), src, ok);
+        cp_async16(smem_u32(q_s) + (r >> 7) * kQBytes + (c >> 3) * (kRows * 128) + sw128(r & 127, c & 7), src, ok);
     }
     cp_async_commit();
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -181,14 +187,16 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_s;
-    const uint32_t tmem_o = tmem, tmem_s0 = tmem + 128;          // O: columns 0..127, S buffers: 128.., 192..
+    // tensor memory: O of tile x in columns 128 x .. 128 x + 127; S buffer b of tile x in 256 + 128 x + 64 b ..
+    auto tmem_o = [&](int x) { return tmem + (uint32_t)(128 * x); };
+    auto tmem_s = [&](int x, int b) { return tmem + (uint32_t)(256 + 128 * x + 64 * b); };
 
     const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
     const size_t page_elems = (size_t)2 * hkv * page_size * D;
     const size_t head_off = (size_t)kvh * page_size * D;
     const size_t v_off = (size_t)hkv * page_size * D;
 
-    if (warp == 0 || warp == 6) {
+    if (warp == 0 || warp == kLoaderWarp2) {
         // ---- loaders: K/V tiles from their pages ------------------------------------------
         // Lane l looks up where keys base+l and base+32+l live (two independent table loads per
         // lane and tile); the copy loop gets each row's address by shuffle, so no load sits
@@ -216,87 +224,91 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 cp_async16(smem_u32(st) + 2 * kHalfBytes + off, src + v_off, ok);
             }
         };
-        // Two loader warps take alternate tiles; each announces a tile once its next one has
-        // been issued and `cp.async.wait_group 1` says the earlier copies have landed, so up
-        // to four tiles are in flight.
+        // Two loader warps take alternate tiles and run ahead as far as stages are free.  Each
+        // lane ties the tile's barrier to its own copies (cp.async.mbarrier.arrive.noinc: the
+        // arrival happens when the lane's earlier copies have landed), so the warp never waits
+        // for data and a tile is announced the moment it is complete.
         const int first = warp == 0 ? 0 : 1;
         bool ok = true;
-        int prev = -1;
-        for (int tile = first; ok; tile += 2) {
-            if (tile < num_tiles) {
-                if (tile >= kStages) ok = mbar_wait(bar(&bars.kv_empty[tile % kStages]), ((tile / kStages) - 1) & 1, &abort_s);
-                if (ok) issue(tile);
-            }
-            cp_async_commit();
-            if (prev >= 0) {
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(&bars.kv_full[prev % kStages]));
-            }
-            if (tile >= num_tiles) break;
-            prev = tile;
+        for (int tile = first; tile < num_tiles && ok; tile += 2) {
+            if (tile >= kStages) ok = mbar_wait(bar(&bars.kv_empty[tile % kStages]), ((tile / kStages) - 1) & 1, &abort_s);
+            if (!ok) break;
+            issue(tile);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(&bars.kv_full[tile % kStages])) : "memory");
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.wait_all;" ::: "memory");
         if (!ok) { abort_s = 1; if (lane == 0) atomicCAS(error, 0, 11); }
     } else if (warp == 1) {
         // ---- MMA issuer ----------------------------------------------------------------------
+        // Order in the tensor pipe per K/V tile j: S_0(j), S_1(j), then P·V of tile j-1 for both
+        // query tiles as their P arrives.  S(j+1) is thus issued before the softmax of tile j has
+        // finished, and the two query tiles' softmax warps keep the pipe fed alternately.
         if (lane == 0) {
             const uint32_t id_s = idesc(kKeys, 0), id_o = idesc(D, 1);
             bool ok = true;
             auto issue_pv = [&](int i) {
-                const int b = i & 1;
-                if (!mbar_wait(bar(&bars.p_full[b]), (i >> 1) & 1, &abort_s)) { ok = false; return; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t pa = smem_u32(p_s) + b * kPBytes;
                 const uint32_t va = smem_u32(kv_s) + (i % kStages) * kKVStageBytes + 2 * kHalfBytes;
 #pragma unroll
-                for (int kk = 0; kk < kKeys / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-                    umma(tmem_o, desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
-                         (i > 0 || kk > 0) ? 1u : 0u);
+                for (int x = 0; x < kTiles; ++x) {
+                    if (!ok) return;
+                    if (!mbar_wait(bar(&bars.p_full[x]), i & 1, &abort_s)) { ok = false; return; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t pa = smem_u32(p_s) + x * kPBytes;
+#pragma unroll
+                    for (int kk = 0; kk < kKeys / 16; ++kk)  // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+                        umma(tmem_o(x), desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
+                             (i > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(bar(&bars.p_empty[x]));
+                }
                 umma_commit(bar(&bars.kv_empty[i % kStages]));
-                umma_commit(bar(&bars.p_empty[b]));
             };
             for (int j = 0; j < num_tiles && ok; ++j) {
                 const int b = j & 1;
                 if (!mbar_wait(bar(&bars.kv_full[j % kStages]), (j / kStages) & 1, &abort_s)) { ok = false; break; }
-                if (j >= 2 && !mbar_wait(bar(&bars.s_empty[b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copies were generic-proxy writes
                 const uint32_t ka = smem_u32(kv_s) + (j % kStages) * kKVStageBytes;
 #pragma unroll
-                for (int kb = 0; kb < 2; ++kb)
+                for (int x = 0; x < kTiles; ++x) {
+                    if (j >= 2 && !mbar_wait(bar(&bars.s_empty[x][b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma(tmem_s0 + b * 64, desc_kmajor(smem_u32(q_s) + kb * (kRows * 128)) + (uint64_t)(kk * 2),
-                             desc_kmajor(ka + kb * kHalfBytes) + (uint64_t)(kk * 2), id_s, (kb > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(bar(&bars.s_full[b]));
-                if (j >= 1) issue_pv(j - 1);
+                    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma(tmem_s(x, b), desc_kmajor(smem_u32(q_s) + x * kQBytes + kb * (kRows * 128)) + (uint64_t)(kk * 2),
+                                 desc_kmajor(ka + kb * kHalfBytes) + (uint64_t)(kk * 2), id_s, (kb > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(bar(&bars.s_full[x][b]));
+                }
+                if (ok && j >= 1) issue_pv(j - 1);
             }
             if (ok) issue_pv(num_tiles - 1);
             if (!ok) { abort_s = 1; atomicCAS(error, 0, 12); }
         }
-    } else {
-        // ---- softmax and epilogue: one thread per row ------------------------------------------
+    } else if (warp < 2 + 4 * kTiles) {
+        // ---- softmax and epilogue: warps 2-5 own query tile 0, warps 6-9 tile 1; one thread per row ----
+        const int x = (warp - 2) >> 2;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
-        const int row = row_base + r;
+        const int row = row_base + x * kRows + r;
         const bool valid = row < total_rows;
         const int rr = valid ? row : total_rows - 1;
         const int pos = q_start + rr / group;
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint8_t* prow = p_s + x * kPBytes;
         float m_ref = -INFINITY, l = 0.f;                  // reference maximum (log2 units), running sum
         bool ok = true;
         for (int j = 0; j < num_tiles && ok; ++j) {
             const int b = j & 1;
-            if (!mbar_wait(bar(&bars.s_full[b]), (j >> 1) & 1, &abort_s)) { ok = false; break; }
+            if (!mbar_wait(bar(&bars.s_full[x][b]), (j >> 1) & 1, &abort_s)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[64];
-            tmem_ld32(tmem_s0 + b * 64 + lane_addr, sv);
-            tmem_ld32(tmem_s0 + b * 64 + 32 + lane_addr, sv + 32);
+            tmem_ld32(tmem_s(x, b) + lane_addr, sv);
+            tmem_ld32(tmem_s(x, b) + 32 + lane_addr, sv + 32);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar(&bars.s_empty[b]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(&bars.s_empty[x][b]));
             const int key0 = k_begin + j * kKeys;
             // A tile every row of the warp sees in full needs no masking (rows ascend with the
             // lane: lane 0 has the smallest position, lane 31 the largest window start).
@@ -328,25 +340,22 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 m_ref = mx;
                 l *= factor;
             }
+            // P·V of the previous tile has finished: O is at rest and the P buffer is free
+            if (j >= 1 && !mbar_wait(bar(&bars.p_empty[x]), (j - 1) & 1, &abort_s)) { ok = false; break; }
             if (__any_sync(0xffffffffu, need)) {
-                // O must be at rest: the P·V of the previous tile has finished
-                if (!mbar_wait(bar(&bars.p_empty[(j - 1) & 1]), ((j - 1) >> 1) & 1, &abort_s)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t ov[32];
-                    tmem_ld32(tmem_o + c0 + lane_addr, ov);
+                    tmem_ld32(tmem_o(x) + c0 + lane_addr, ov);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * (need ? factor : 1.f));
-                    tmem_st32(tmem_o + c0 + lane_addr, ov);
+                    tmem_st32(tmem_o(x) + c0 + lane_addr, ov);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // the P buffer is free once the P·V two tiles back has finished
-            if (j >= 2 && !mbar_wait(bar(&bars.p_empty[b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
-            uint8_t* prow = p_s + b * kPBytes;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_use;
 #pragma unroll
@@ -365,16 +374,17 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar(&bars.p_full[b]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(&bars.p_full[x]));
         }
-        if (ok && mbar_wait(bar(&bars.p_empty[(num_tiles - 1) & 1]), ((num_tiles - 1) >> 1) & 1, &abort_s)) {
+        if (ok && mbar_wait(bar(&bars.p_empty[x]), (num_tiles - 1) & 1, &abort_s)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t ov[32];
-                tmem_ld32(tmem_o + c0 + lane_addr, ov);
+                tmem_ld32(tmem_o(x) + c0 + lane_addr, ov);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (valid) {
 #pragma unroll
@@ -396,7 +406,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
 
@@ -414,7 +424,7 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
     using namespace se::fa;
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)kQBytes + kStages * kKVStageBytes + 2 * kPBytes + 1024;
+    const size_t smem = (size_t)kTiles * kQBytes + kStages * kKVStageBytes + kTiles * kPBytes + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -422,7 +432,7 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
         configured = true;
     }
     const int group = hq / hkv;
-    dim3 grid(se::ceil_div(max_q_len * group, kRows), hkv, entries);
+    dim3 grid(se::ceil_div(max_q_len * group, kTiles * kRows), hkv, entries);
     attn_prefill_tc_kernel<<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
         (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window);
