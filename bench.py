@@ -231,8 +231,15 @@ def run_ours(args) -> dict:
         runner.release(f"p{i}")
     pms = min(pre_ms[1:])
     flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
+    # With 2,048 tokens over top-k of many experts, every expert's weights are still read once
+    # per layer, which bounds this prefill by HBM rather than by the tensor cores: hbm_frac is
+    # the bytes it has to read (all weights once, the prompt's K/V once) over time and peak.
+    experts = cfg.get("num_local_experts", 0)
+    pre_bytes = (args.layers * (mb["dense_layer"] + experts * mb["expert"] + PROMPT_LEN * mb["kv_token_layer"])
+                 + mb["lm_head"])
     prefill = {"value": round(PROMPT_LEN * 1000.0 / pms, 1), "tokens": PROMPT_LEN, "ms": round(pms, 3),
-               "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
+               "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
+               "hbm_frac": round(pre_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
 
     # ---- end to end through the public API -----------------------------------------------
     sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 16, ignore_eos=True)

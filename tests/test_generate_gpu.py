@@ -145,3 +145,51 @@ def test_options_for_debugging_and_long_rows(folder_a):
     assert set(st["part_ms"]) == {"mixer_norm", "mixer", "feed_forward_norm", "feed_forward"}
     assert all(v > 0 for v in st["part_ms"].values())
     assert llm.runner.cache.reserved_state.shape[1] == 32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_requests_under_memory_pressure(folder_b, dtype):
+    """Forty requests of mixed lengths through a cache that holds a handful of them: requests
+    wait, are admitted as pages come back, some are preempted and recomputed, requests arrive
+    while others run, one is aborted.  Every request ends with exactly the tokens it gets when
+    it has the engine to itself (sampling noise is keyed by request and step), the page books
+    balance at every step, and all pages are free at the end."""
+    import random
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, _ = folder_b
+    rng = random.Random(5)
+    reqs = [(tu.random_prompt(384, rng.randint(1, 40), 100 + i), rng.randint(1, 24)) for i in range(40)]
+    kw = dict(dtype=dtype, page_size=8, max_model_len=128, seed=11, max_num_batched_tokens=48)
+
+    def params(n):
+        return SamplingParams(temperature=0.9, top_k=50, max_tokens=n, ignore_eos=True)
+    alone = LLM(folder, num_kvcache_slots=1024, **kw)
+    want = {}
+    for i, (p, n) in enumerate(reqs):
+        assert alone.add_request(p, params(n)) == i      # ids count up in arrival order in both engines
+        while not alone.is_finished():
+            for o in alone.step()[0]:
+                want[o["seq_id"]] = o["token_ids"]
+    tight = LLM(folder, num_kvcache_slots=200, decode_reservation_tokens=0, max_num_seqs_in_batch=6, **kw)   # 25 pages
+    got, pending, aborted = {}, list(enumerate(reqs)), None
+    steps = 0
+    while pending or not tight.is_finished():
+        for _ in range(rng.randint(0, 3)):               # requests trickle in
+            if pending:
+                i, (p, n) = pending.pop(0)
+                assert tight.add_request(p, params(n)) == i
+        if steps == 30 and aborted is None and tight.scheduler.running:
+            aborted = tight.scheduler.running[-1].seq_id
+            tight.abort_request(aborted)
+        for o in tight.step()[0]:
+            got[o["seq_id"]] = o["token_ids"]
+        tight.runner.cache.check()
+        steps += 1
+        assert steps < 5000
+    assert aborted is not None and aborted not in got
+    assert tight.scheduler.num_preemptions > 0
+    for i in range(len(reqs)):
+        if i != aborted:
+            assert got[i] == want[i], i
+    c = tight.runner.cache
+    assert c.free_pages() == c.groups[0].pool.num_pages and c.groups[0].pool.reused_total > 0
