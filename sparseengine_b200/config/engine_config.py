@@ -34,6 +34,7 @@ class Config:
     validate_runtime_invariants: bool = False      # host-side checks of every step's index tensors
     throughput_log_interval_s: float = 10.0        # generate() logs tokens/s this often (0 = never)
     tiny_random: bool = False                      # random weights instead of a checkpoint
+    tiny_random_config: Optional[str] = None       # JSON file of size overrides for the model's config.json
     tiny_random_seed: int = 0
     eos: int = -1
     eos_token_ids: tuple = field(default_factory=tuple)
@@ -71,6 +72,37 @@ class Config:
         if self.state_slot_bytes < 0:
             raise ValueError("state_slot_bytes must not be negative")
         self.eos_token_ids = tuple(int(t) for t in self.eos_token_ids)
+
+    # Keys a tiny-random override file may shrink (src/sparseengine/debug/tiny_random.py:15-26).
+    TINY_RANDOM_KEYS = ("head_dim", "hidden_size", "intermediate_size", "max_position_embeddings", "num_attention_heads",
+                        "num_hidden_layers", "num_key_value_heads", "vocab_size")
+
+    def apply_tiny_random_overrides(self, raw: dict) -> dict:
+        """The model's config.json with the sizes of ``tiny_random_config`` put in, as the
+        reference's tiny random mode does (src/sparseengine/debug/tiny_random.py:66-120): one
+        JSON object of positive integers, only the keys above, present in the model's config,
+        and the three main sizes never larger than the model's own."""
+        if not self.tiny_random_config:
+            return raw
+        if not self.tiny_random:
+            raise ValueError("tiny_random_config needs tiny_random=True")
+        with open(self.tiny_random_config) as f:
+            over = json.load(f)
+        if not isinstance(over, dict):
+            raise TypeError("the tiny random config must contain one JSON object")
+        unknown = sorted(set(over) - set(self.TINY_RANDOM_KEYS))
+        if unknown:
+            raise ValueError(f"unsupported tiny random config keys: {unknown}; allowed: {sorted(self.TINY_RANDOM_KEYS)}")
+        out = dict(raw)
+        for k, v in over.items():
+            if isinstance(v, bool) or not isinstance(v, int) or v <= 0:
+                raise ValueError(f"tiny random override {k} must be a positive integer, got {v!r}")
+            if k not in raw:
+                raise ValueError(f"tiny random override {k!r} is not a key of the model's config.json")
+            if k in ("num_hidden_layers", "hidden_size", "intermediate_size") and v > int(raw[k]):
+                raise ValueError(f"tiny random override {k} must not enlarge the model: {v} > {raw[k]}")
+            out[k] = v
+        return out
 
     @classmethod
     def field_names(cls) -> set:

@@ -54,6 +54,7 @@ class LLM:
         from ..csrc import ops
         ops.library()       # compile/load the kernels now; there is no other path
         raw = model if isinstance(model, dict) else read_config_json(model)
+        raw = cfg.apply_tiny_random_overrides(raw)
         self._raw = raw
         dt = resolve_dtype(cfg.dtype)
         from ..config.registry import load_model_spec

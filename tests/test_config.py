@@ -79,3 +79,23 @@ def test_engine_options(tmp_path):
     c = Config.from_json("m", "@" + str(p))
     assert c.page_size == 8 and c.dtype == "float32"
     assert Config.from_json("m", '{"seed": 3}').seed == 3
+
+
+def test_tiny_random_override_file(tmp_path):
+    """The reference's tiny random mode: a JSON file that shrinks sizes of the model's config."""
+    import json
+    from sparseengine_b200.config.engine_config import Config
+    raw = dict(plain_m2.TINY_A)
+    path = tmp_path / "tiny.json"
+    path.write_text(json.dumps({"num_hidden_layers": 1, "vocab_size": 99}))
+    cfg = Config.from_kwargs("m", tiny_random=True, tiny_random_config=str(path))
+    out = cfg.apply_tiny_random_overrides(raw)
+    assert out["num_hidden_layers"] == 1 and out["vocab_size"] == 99 and raw["num_hidden_layers"] != 1
+    assert Config.from_kwargs("m").apply_tiny_random_overrides(raw) is raw
+    with pytest.raises(ValueError, match="tiny_random=True"):
+        Config.from_kwargs("m", tiny_random_config=str(path)).apply_tiny_random_overrides(raw)
+    for bad, msg in (({"num_experts_per_tok": 1}, "unsupported"), ({"hidden_size": 0}, "positive"),
+                     ({"hidden_size": 10 ** 6}, "enlarge"), ({"num_hidden_layers": True}, "positive")):
+        path.write_text(json.dumps(bad))
+        with pytest.raises(ValueError, match=msg):
+            cfg.apply_tiny_random_overrides(raw)
