@@ -176,6 +176,18 @@ def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormaliz
     return ids, weights
 
 
+def router_select(logits, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
+                  impl="auto"):
+    """Selection alone from given 32-bit logits.  ``impl``: "auto", "block" (a block per token, any
+    size and score function) or "warp" (a warp per token: sigmoid scores, up to 256 experts)."""
+    tokens, experts = logits.shape
+    _check(_fn("se_router_select", "pppp" "iiiii" "f" "ip")(
+        _ptr(logits, torch.float32, "logits"), _ptr(bias, torch.float32, "bias"), _ptr(ids, torch.int32, "ids"),
+        _ptr(weights, torch.float32, "weights"), tokens, experts, top_k, SCORE_FN[score_fn], int(renormalize),
+        float(routed_scale), {"auto": 0, "block": 1, "warp": 2}[impl], _stream()), "router_select")
+    return ids, weights
+
+
 def moe_plain_tile_rows() -> int:
     f = library().se_moe_plain_tile_rows
     f.restype = _I

@@ -353,7 +353,123 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     }
 }
 
+// The same selection by one warp per token, for sigmoid scores and up to 256 experts (what
+// MiniMax M2 has): lane l holds experts l, l + 32, ... in registers; top_k rounds of "best
+// remaining" find the chosen set (the warp's best key by one redux.max, the lowest expert
+// that has it by one redux.min), then slots and weights as above.  Same values, slot for slot.
+constexpr int kSelPer = 8;             // experts per lane
+
+__global__ void __launch_bounds__(256)
+router_select_warp_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                          float* __restrict__ weights, int tokens, int experts, int top_k, int renormalize,
+                          float routed_scale) {
+    extern __shared__ float sel_w[];                 // [warps][top_k] probabilities of the chosen, in slot order
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    float* w_s = sel_w + warp * top_k;
+    const unsigned below = (1u << lane) - 1u;
+    float pj[kSelPer], sj[kSelPer];
+    unsigned key[kSelPer];                           // the score as an unsigned key in the same order; 0 = none or taken
+#pragma unroll
+    for (int i = 0; i < kSelPer; ++i) {
+        const int e = 32 * i + lane;
+        pj[i] = 0.f;
+        sj[i] = 0.f;
+        key[i] = 0u;
+        if (e < experts) {
+            pj[i] = 1.f / (1.f + expf(-logits[(size_t)t * experts + e]));
+            const float sc = pj[i] + (bias ? bias[e] : 0.f);
+            sj[i] = (sc == sc) ? sc : INFINITY;      // a NaN score counts as +inf
+            const unsigned u = __float_as_uint(sj[i]);
+            key[i] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+            if (key[i] == 0u) key[i] = 1u;
+        }
+    }
+    unsigned chosen = 0;                             // bit i: expert 32 i + lane
+    float thr = 0.f;
+    for (int r = 0; r < top_k; ++r) {
+        unsigned bk = 0u;
+        int bi = 0;
+#pragma unroll
+        for (int i = 0; i < kSelPer; ++i)
+            if (key[i] > bk) {                       // ascending i: the lowest index among equals stays
+                bk = key[i];
+                bi = i;
+            }
+        const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+        const unsigned mine = (bk == top && bk != 0u) ? (unsigned)(32 * bi + lane) : 0xffffffffu;
+        const unsigned win = __reduce_min_sync(0xffffffffu, mine);
+        if (mine == win) {
+            chosen |= 1u << bi;
+#pragma unroll
+            for (int i = 0; i < kSelPer; ++i)
+                if (i == bi) {
+                    thr = sj[i];
+                    key[i] = 0u;
+                }
+        }
+        thr = __shfl_sync(0xffffffffu, thr, win & 31u);
+    }
+    // slots: strictly above the threshold by ascending index, then the ties with it
+    int n_greater = 0;
+#pragma unroll
+    for (int i = 0; i < kSelPer; ++i) n_greater += (((chosen >> i) & 1u) && sj[i] > thr) ? 1 : 0;
+    n_greater = __reduce_add_sync(0xffffffffu, n_greater);
+    int run_g = 0, run_t = 0;
+#pragma unroll
+    for (int i = 0; i < kSelPer; ++i) {
+        const bool c = (chosen >> i) & 1u;
+        const bool gr = c && sj[i] > thr, tie = c && !gr;
+        const unsigned bg = __ballot_sync(0xffffffffu, gr), bt = __ballot_sync(0xffffffffu, tie);
+        if (c) {
+            const int slot = gr ? run_g + __popc(bg & below) : n_greater + run_t + __popc(bt & below);
+            ids[(size_t)t * top_k + slot] = 32 * i + lane;
+            w_s[slot] = pj[i];
+        }
+        run_g += __popc(bg);
+        run_t += __popc(bt);
+    }
+    __syncwarp();
+    float sum = 0.f;
+    for (int k = 0; k < top_k; ++k) sum += w_s[k];                  // slot order, as one thread adds them
+    for (int k = lane; k < top_k; k += 32)
+        weights[(size_t)t * top_k + k] = (renormalize ? w_s[k] / sum : w_s[k]) * routed_scale;
+}
+
 }  // namespace se
+
+// impl: 0 = by sizes, 1 = the block-per-token kernel, 2 = the warp-per-token kernel
+static int launch_select(const float* logits, const float* bias, int* ids, float* weights, int tokens, int experts,
+                         int top_k, int score_fn, int renormalize, float routed_scale, int impl, cudaStream_t stream) {
+    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 3 * sizeof(float);
+    const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256;
+    if (impl == 2 && !warp_ok) return SE_ERR_UNSUPPORTED;
+    if (smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    // A warp's selection is one long chain of dependent steps (8 us for a token, against 6.6 us
+    // for the block kernel), so it pays when there are tokens enough to fill the SMs with warps.
+    if (impl == 2 || (impl == 0 && warp_ok && tokens >= 128)) {
+        se::router_select_warp_kernel<<<se::ceil_div(tokens, 8), 256, 8 * top_k * sizeof(float), stream>>>(
+            logits, bias, ids, weights, tokens, experts, top_k, renormalize, routed_scale);
+        SE_LAUNCH_CHECK();
+    }
+    if (smem_sel > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);
+        if (e != cudaSuccess) return (int)e;
+    }
+    se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(logits, bias, ids, weights, experts, top_k, score_fn,
+                                                                renormalize, routed_scale);
+    SE_LAUNCH_CHECK();
+}
+
+// Selection alone, from given logits (float [tokens, experts]).
+extern "C" int se_router_select(const float* logits, const float* bias, int* ids, float* weights, int tokens, int experts,
+                                int top_k, int score_fn, int renormalize, float routed_scale, int impl,
+                                cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (top_k <= 0 || top_k > experts || impl < 0 || impl > 2) return SE_ERR_ARGUMENT;
+    return launch_select(logits, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, impl, stream);
+}
 
 // logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
@@ -394,11 +510,5 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                                                                                         hidden, experts);
         }
     });
-    if (smem_sel > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);
-        if (e != cudaSuccess) return (int)e;
-    }
-    se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(logits, bias, ids, weights, experts, top_k, score_fn,
-                                                                renormalize, routed_scale);
-    SE_LAUNCH_CHECK();
+    return launch_select(logits, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, 0, stream);
 }

@@ -229,6 +229,42 @@ def test_router_logits_do_not_depend_on_the_batch():
             assert torch.equal(lg, full[sl]), (hidden, experts, sl)
 
 
+@pytest.mark.parametrize("tokens,experts,top_k,kind", [
+    (1, 256, 8, "random"), (70, 256, 8, "random"), (9, 37, 5, "random"), (13, 5, 5, "random"), (300, 200, 1, "random"),
+    (6, 64, 6, "ties"), (5, 256, 8, "coarse"), (4, 40, 7, "nan")])
+def test_router_selection_by_a_warp_equals_selection_by_a_block(tokens, experts, top_k, kind):
+    """The two selection kernels give the same experts in the same slots with the same
+    weights, bit for bit: on random logits, on logits with many exact ties (where only the tie
+    order decides), on coarse logits with ties at the threshold, and with NaN scores."""
+    from sparseengine_b200.csrc import ops
+    g = torch.Generator().manual_seed(tokens * 1000 + experts)
+    logits = torch.randn(tokens, experts, generator=g)
+    bias = torch.randn(experts, generator=g) * 0.3
+    if kind == "ties":
+        logits.zero_()
+        bias = torch.tensor([0.0, 0.25, 0.5, 0.25] * (experts // 4))
+    elif kind == "coarse":
+        logits = (logits * 2).round() / 2
+        bias = (bias * 4).round() / 4
+    elif kind == "nan":
+        bias[3] = float("nan")
+        logits[1, 7] = float("nan")
+    logits, bias = logits.to(DEV), bias.to(DEV)
+    out = {}
+    for impl in ("block", "warp", "auto"):
+        ids = torch.full((tokens, top_k), -1, dtype=torch.int32, device=DEV)
+        w = torch.full((tokens, top_k), -1.0, dtype=torch.float32, device=DEV)
+        ops.router_select(logits, bias, ids, w, top_k=top_k, routed_scale=1.25, impl=impl)
+        out[impl] = (ids.cpu(), w.cpu())
+    assert torch.equal(out["warp"][0], out["block"][0]) and torch.equal(out["auto"][0], out["block"][0])
+    same = (out["warp"][1] == out["block"][1]) | (out["warp"][1].isnan() & out["block"][1].isnan())
+    assert bool(same.all())
+    assert int(out["block"][0].min()) >= 0 and all(len(set(r)) == top_k for r in out["block"][0].tolist())
+    with pytest.raises(ValueError, match="does not support"):
+        ops.router_select(torch.zeros(2, 300, device=DEV), None, torch.empty(2, 2, dtype=torch.int32, device=DEV),
+                          torch.empty(2, 2, device=DEV), top_k=2, impl="warp")       # more than 256 experts
+
+
 def test_router_tie_order_nan_and_softmax():
     from sparseengine_b200.csrc import ops
     x = torch.zeros(2, 8, device=DEV)
