@@ -112,7 +112,30 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
 // quarter_dot), so every (token, expert, quarter, lane) partial sum is accumulated in the
 // same order as in the other kernels; quarters are reduced by the same butterfly and
 // combined as (q0 + q1) + (q2 + q3).  Needs hidden % 4 == 0.
+//
+// The multiply-adds are the packed ones of this architecture (fma.rn.f32x2: two independent
+// IEEE fp32 fused multiply-adds per instruction): an accumulator pair holds one token's sums
+// for two neighbouring experts, the token's value is duplicated into both halves, and the gate
+// rows are staged pair-interleaved -- (g0.x, g1.x, g0.y, g1.y) and (g0.z, g1.z, g0.w, g1.w) per
+// 16-byte group -- so that one 16-byte shared-memory load yields two packed operands.  Every
+// accumulator still sees its four products per group in the order x, y, z, w.
 constexpr int kBigTokens = 32, kBigExperts = 16;
+
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long dup2(float v) {
+    unsigned long long d;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "f"(v));
+    return d;
+}
+__device__ __forceinline__ unsigned long long pair2(float lo, float hi) {
+    unsigned long long d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
 
 // four consecutive elements as 32-bit values (the address is 4-element aligned)
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -160,8 +183,8 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
             xr[k] = v;
         }
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int e = min(e0 + warp + 8 * k, experts - 1);
+        for (int k = 0; k < 2; ++k) {            // the two experts of pair `warp`
+            const int e = min(e0 + 2 * warp + k, experts - 1);
             gr[k] = i < last ? __ldg(reinterpret_cast<const float4*>(gate + (size_t)e * hidden) + i)
                              : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -169,18 +192,19 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
     auto stash = [&](int buf) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) *reinterpret_cast<float4*>(&xs[buf][warp + 8 * k][4 * lane]) = xr[k];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) *reinterpret_cast<float4*>(&gs[buf][warp + 8 * k][4 * lane]) = gr[k];
+        // pair `warp` of the block's experts: rows 2 warp (x and y halves) and 2 warp + 1 (z and w halves)
+        *reinterpret_cast<float4*>(&gs[buf][2 * warp][4 * lane]) = make_float4(gr[0].x, gr[1].x, gr[0].y, gr[1].y);
+        *reinterpret_cast<float4*>(&gs[buf][2 * warp + 1][4 * lane]) = make_float4(gr[0].z, gr[1].z, gr[0].w, gr[1].w);
     };
 
     for (int quarter = 0; quarter < 4; ++quarter) {
         const int a = quarter * per, b = min(n4, a + per);
         const int chunks = a < b ? (b - a + 31) / 32 : 0;
-        float acc[8][8];
+        unsigned long long acc2[8][4];           // [token][expert pair]: the sums for experts we + 2p and we + 2p + 1
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+            for (int p = 0; p < 4; ++p) acc2[i][p] = 0ull;
         if (chunks > 0) fetch(a, b);
         for (int c = 0; c < chunks; ++c) {
             const int buf = c & 1;
@@ -188,24 +212,40 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
             __syncthreads();
             if (c + 1 < chunks) fetch(a + 32 * (c + 1), b);
             if (a + 32 * c + lane < b) {         // lanes past the quarter's end add nothing (as in quarter_dot)
-                float4 gv[8];
+                unsigned long long gxy[4][2], gzw[4][2];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) gv[j] = *reinterpret_cast<const float4*>(&gs[buf][we + j][4 * lane]);
+                for (int p = 0; p < 4; ++p) {
+                    const float4 ga = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p][4 * lane]);
+                    const float4 gb = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p + 1][4 * lane]);
+                    gxy[p][0] = pair2(ga.x, ga.y);
+                    gxy[p][1] = pair2(ga.z, ga.w);
+                    gzw[p][0] = pair2(gb.x, gb.y);
+                    gzw[p][1] = pair2(gb.z, gb.w);
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][wt + i][4 * lane]);
+                    const unsigned long long xx = dup2(xv.x), xy = dup2(xv.y), xz = dup2(xv.z), xw = dup2(xv.w);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        acc[i][j] = fmaf(xv.x, gv[j].x, acc[i][j]);
-                        acc[i][j] = fmaf(xv.y, gv[j].y, acc[i][j]);
-                        acc[i][j] = fmaf(xv.z, gv[j].z, acc[i][j]);
-                        acc[i][j] = fmaf(xv.w, gv[j].w, acc[i][j]);
+                    for (int p = 0; p < 4; ++p) {
+                        acc2[i][p] = fma2(xx, gxy[p][0], acc2[i][p]);
+                        acc2[i][p] = fma2(xy, gxy[p][1], acc2[i][p]);
+                        acc2[i][p] = fma2(xz, gzw[p][0], acc2[i][p]);
+                        acc2[i][p] = fma2(xw, gzw[p][1], acc2[i][p]);
                     }
                 }
             }
             // the buffer written two chunks ahead is this one: everyone must be done reading it
             if (c + 2 < chunks) __syncthreads();
         }
+        float acc[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                acc[i][2 * p] = __uint_as_float((unsigned)(acc2[i][p] & 0xffffffffull));
+                acc[i][2 * p + 1] = __uint_as_float((unsigned)(acc2[i][p] >> 32));
+            }
         __syncthreads();
         // 64 sums over the lanes at once: each step halves the values a lane holds and adds
         // the partner's copy of the half it keeps.  The pairs are those of warp_sum (lanes
