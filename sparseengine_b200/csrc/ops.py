@@ -27,6 +27,7 @@ _fns: dict = {}
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
 KERNELS_PER_CALL = {"se_moe_route_build": 2, "se_attn_decode": 2, "se_router": 2}   # upper bounds per call
 launch_count = 0
+calls: dict = {}     # launcher name -> times called (tests check which kernels a path took)
 
 
 def library():
@@ -36,6 +37,7 @@ def library():
 def _fn(name: str, sig: str):
     global launch_count
     launch_count += KERNELS_PER_CALL.get(name, 1)
+    calls[name] = calls.get(name, 0) + 1
     f = _fns.get(name)
     if f is None:
         f = getattr(library(), name)

@@ -356,3 +356,28 @@ TINY_C = {
     "scoring_func": "sigmoid", "use_routing_bias": True, "use_mtp": True,
     "shared_intermediate_size": 0, "torch_dtype": "float32",
 }
+
+# Head sizes 128 and 64, which the engine's tensor-core attention kernels take (the shapes
+# above all go through its plain attention kernel): 6 query heads on 2 KV heads of 128 with
+# half of the dims rotated, as MiniMax M2 has them; and 4 on 4 heads of 64, fully rotated.
+TINY_D = {
+    "architectures": ["MiniMaxM2ForCausalLM"], "model_type": "minimax_m2",
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 128, "rotary_dim": 64, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6,
+    "num_local_experts": 8, "num_experts_per_tok": 2, "intermediate_size": 64,
+    "vocab_size": 320, "max_position_embeddings": 4096, "tie_word_embeddings": False,
+    "hidden_act": "silu", "qk_norm_type": "per_layer", "use_qk_norm": True,
+    "scoring_func": "sigmoid", "use_routing_bias": True, "use_mtp": True,
+    "shared_intermediate_size": 0, "torch_dtype": "float32",
+}
+
+TINY_E = {
+    "architectures": ["MiniMaxM2ForCausalLM"], "model_type": "minimax_m2",
+    "num_hidden_layers": 1, "hidden_size": 192, "num_attention_heads": 4, "num_key_value_heads": 4,
+    "head_dim": 64, "rotary_dim": 64, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+    "num_local_experts": 5, "num_experts_per_tok": 3, "intermediate_size": 96,
+    "vocab_size": 150, "max_position_embeddings": 4096, "tie_word_embeddings": False,
+    "hidden_act": "silu", "qk_norm_type": "per_layer", "use_qk_norm": True,
+    "scoring_func": "sigmoid", "use_routing_bias": True, "use_mtp": True,
+    "shared_intermediate_size": 0, "torch_dtype": "float32",
+}

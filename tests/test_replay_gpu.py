@@ -117,6 +117,49 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", list(ACT))
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_portions_through_the_tensor_core_attention(folders, name, dtype):
+    """Portions of more than 512 tokens take the prompt-portion attention kernels (tcgen05 for
+    head size 128, m16n8k16 tiles for 64; in 32-bit the plain kernel), shorter ones and single
+    tokens the split-key kernel: a 1,500-token request in portions of 700, 600 and 200, a
+    second request whose 650-token portion shares a step with a decoded token of the first,
+    then both decode side by side."""
+    folder, tensors = folders[name, dtype]
+    vocab = tu.TINY[name][0]["vocab_size"]
+    a, b = tu.random_prompt(vocab, 1510, 71), tu.random_prompt(vocab, 659, 72)
+    seqs = {"a": a, "b": b}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:700], "want": [0, 1, 350, 699]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[700:1300], "want": [0, 599]}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[1300:1500], "want": [0, 100, 199]}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[1500:1501], "want": [0]},
+                                {"id": "b", "tokens": b[:650], "want": [0, 649]}], "end": []},
+    ]
+    for i in range(9):
+        steps.append({"step": 4 + i, "entries": [{"id": "a", "tokens": [a[1501 + i]], "want": [0]},
+                                                  {"id": "b", "tokens": [b[650 + i]], "want": [0]}], "end": []})
+    steps[-1]["end"] = ["a", "b"]
+    from sparseengine_b200.csrc import ops
+    runner = runner_for(folder, name, dtype, steps)
+    before = dict(ops.calls)
+    routed = None
+    if dtype == "bfloat16":
+        got, routed = tu.run_trace_runner(runner, steps, capture=True)
+    else:
+        got = tu.run_trace_runner(runner, steps)
+    took = {k for k, v in ops.calls.items() if v > before.get(k, 0)}
+    if dtype == "bfloat16":
+        assert ("se_attn_prefill_tc" if name == "D" else "se_attn_prefill") in took and "se_attn_decode" in took
+        assert "se_moe_grouped_gemm_tc" in took and "se_paged_attention_plain" not in took
+    else:
+        assert "se_paged_attention_plain" in took and "se_moe_grouped_gemm_plain" in took
+    ref = reference(name, dtype, tensors, seqs, routed)
+    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} long portions")
+    assert len(got) == 4 + 2 + 3 + 1 + 2 + 18
+    ops.tc_check("cuda:0")
+
+
+@pytest.mark.parametrize("dtype", list(ACT))
 def test_cuts_agree_with_each_other_more_tightly_than_with_the_plain(folders, dtype):
     """The same request through different cuts and page sets: the logits differ by
     rounding only (in 32-bit: a few ulp of the order of sums)."""

@@ -19,6 +19,8 @@ TINY = {
     "A": (plain_m2.TINY_A, 0, 0.02, 0.05, 0.0, 4),
     "B": (plain_m2.TINY_B, 1, 0.03, 0.0, 0.1, 8),
     "C": (plain_m2.TINY_C, 2, 0.05, 0.1, 0.05, 16),
+    "D": (plain_m2.TINY_D, 3, 0.04, 0.05, 0.05, 16),
+    "E": (plain_m2.TINY_E, 4, 0.04, 0.05, 0.1, 8),
 }
 
 
