@@ -31,7 +31,8 @@ constexpr int kKeys = 64;
 constexpr int kTiles = 2;                            // query tiles per CTA
 constexpr int kStages = 4;
 constexpr int kLoaderWarp2 = 2 + 4 * kTiles;         // the second loader warp
-constexpr int kThreads = 32 * (kLoaderWarp2 + 1);    // loader, MMA, 4 softmax warps per query tile, loader
+constexpr int kMmaWarp2 = kLoaderWarp2 + 1;          // the MMA issuer of query tile 1 (tile 0: warp 1)
+constexpr int kThreads = 32 * (kMmaWarp2 + 1);       // loader, MMA, 4 softmax warps per query tile, loader, MMA
 constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
 constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
 constexpr int kKVStageBytes = 4 * kHalfBytes;        // K halves, V halves
@@ -155,7 +156,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     auto bar = [&](uint64_t* b) { return smem_u32(b); };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar(&bars.kv_full[s]), 32); mbar_init(bar(&bars.kv_empty[s]), 1); }   // full: every lane of the tile's loader warp
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(&bars.kv_full[s]), 32); mbar_init(bar(&bars.kv_empty[s]), kTiles); }   // full: every lane of the tile's loader warp; empty: both query tiles' MMAs
         for (int x = 0; x < kTiles; ++x) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(bar(&bars.s_full[x][b]), 1);
@@ -238,48 +239,42 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (!ok) { abort_s = 1; if (lane == 0) atomicCAS(error, 0, 11); }
-    } else if (warp == 1) {
-        // ---- MMA issuer ----------------------------------------------------------------------
-        // Order in the tensor pipe per K/V tile j: S_0(j), S_1(j), then P·V of tile j-1 for both
-        // query tiles as their P arrives.  S(j+1) is thus issued before the softmax of tile j has
-        // finished, and the two query tiles' softmax warps keep the pipe fed alternately.
+    } else if (warp == 1 || warp == kMmaWarp2) {
+        // ---- MMA issuers: one warp (one lane) per query tile ---------------------------------------
+        // Order for a tile: S(j), then P·V of tile j-1 as its P arrives; S(j+1) is thus issued
+        // before the softmax of tile j has finished.  The two issuers share the tensor pipe and
+        // do not wait for one another; a K/V stage is free when both have committed its P·V.
         if (lane == 0) {
+            const int x = warp == 1 ? 0 : 1;
             const uint32_t id_s = idesc(kKeys, 0), id_o = idesc(D, 1);
             bool ok = true;
             auto issue_pv = [&](int i) {
+                if (!mbar_wait(bar(&bars.p_full[x]), i & 1, &abort_s)) { ok = false; return; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t va = smem_u32(kv_s) + (i % kStages) * kKVStageBytes + 2 * kHalfBytes;
+                const uint32_t pa = smem_u32(p_s) + x * kPBytes;
 #pragma unroll
-                for (int x = 0; x < kTiles; ++x) {
-                    if (!ok) return;
-                    if (!mbar_wait(bar(&bars.p_full[x]), i & 1, &abort_s)) { ok = false; return; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t pa = smem_u32(p_s) + x * kPBytes;
-#pragma unroll
-                    for (int kk = 0; kk < kKeys / 16; ++kk)  // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-                        umma(tmem_o(x), desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
-                             (i > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(bar(&bars.p_empty[x]));
-                }
+                for (int kk = 0; kk < kKeys / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+                    umma(tmem_o(x), desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
+                         (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(&bars.p_empty[x]));
                 umma_commit(bar(&bars.kv_empty[i % kStages]));
             };
             for (int j = 0; j < num_tiles && ok; ++j) {
                 const int b = j & 1;
                 if (!mbar_wait(bar(&bars.kv_full[j % kStages]), (j / kStages) & 1, &abort_s)) { ok = false; break; }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copies were generic-proxy writes
+                if (j >= 2 && !mbar_wait(bar(&bars.s_empty[x][b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ka = smem_u32(kv_s) + (j % kStages) * kKVStageBytes;
 #pragma unroll
-                for (int x = 0; x < kTiles; ++x) {
-                    if (j >= 2 && !mbar_wait(bar(&bars.s_empty[x][b]), ((j >> 1) - 1) & 1, &abort_s)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-                    for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma(tmem_s(x, b), desc_kmajor(smem_u32(q_s) + x * kQBytes + kb * (kRows * 128)) + (uint64_t)(kk * 2),
-                                 desc_kmajor(ka + kb * kHalfBytes) + (uint64_t)(kk * 2), id_s, (kb > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(bar(&bars.s_full[x][b]));
-                }
-                if (ok && j >= 1) issue_pv(j - 1);
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(tmem_s(x, b), desc_kmajor(smem_u32(q_s) + x * kQBytes + kb * (kRows * 128)) + (uint64_t)(kk * 2),
+                             desc_kmajor(ka + kb * kHalfBytes) + (uint64_t)(kk * 2), id_s, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(&bars.s_full[x][b]));
+                if (j >= 1) issue_pv(j - 1);
             }
             if (ok) issue_pv(num_tiles - 1);
             if (!ok) { abort_s = 1; atomicCAS(error, 0, 12); }
