@@ -1,23 +1,32 @@
 // Prompt-portion attention on 5th-generation tensor cores (bfloat16, head size 128).
 //
-// One CTA per (batch entry, KV head, tile of 128 query rows); a row is one (query token,
-// query head of the GQA group) pair, token-major, so a tile spans ~21 tokens of M2 and all
-// six heads that share the KV head.  Per 64-key tile:
+// One CTA per (batch entry, KV head, 256 query rows); a row is one (query token, query head
+// of the GQA group) pair, token-major, so 128 rows span ~21 tokens of M2 and all six heads
+// that share the KV head.  The CTA holds two query tiles of 128 rows, each with its own four
+// softmax warps and its own MMA-issuing warp; the two tiles take turns on the tensor pipe and
+// share every 64-key K/V tile that is loaded.  Per query tile and K/V tile:
 //
 //   S = Q·Kᵀ        tcgen05.mma, M 128 x N 64 x K 128, Q and K K-major in shared memory
-//                   (128-byte swizzle), S in tensor memory (two buffers);
+//                   (128-byte swizzle), S in tensor memory (two buffers per query tile);
 //   softmax         four warps, one thread per row: tcgen05.ld of its row of S, mask
 //                   (causal, window, end of keys), running maximum and sum in 32-bit, P
 //                   rounded to bfloat16 and written to shared memory as the next A operand;
 //   O += P·V        tcgen05.mma, M 128 x N 128 x K 64, V straight from its pages (dims
 //                   contiguous: the MN-major B operand), O in tensor memory.
 //
-// The running maximum only moves when a row's maximum grows by more than 2^8 (then O and
-// the sum are rescaled), so O is read back from tensor memory rarely; the final division by
-// the sum is exact for whatever reference maximum was used.  Warp roles: warp 0 loads K/V
-// tiles (cp.async, five stages; warps 0 and 6), warp 1 owns tensor memory and issues the MMAs, warps 2-5
-// are the softmax/epilogue warps.  Every mbarrier wait is bounded and reports through the
-// error word.  Arithmetic as the reference's prefill kernel
+// Tensor memory is used in full: O of the two tiles (2 x 128 columns) and their S buffers
+// (2 x 2 x 64).  The running maximum only moves when a row's maximum grows by more than 2^8
+// (then O and the sum are rescaled), so O is read back from tensor memory rarely; the final
+// division by the sum is exact for whatever reference maximum was used.
+//
+// Warp roles (12 warps): warps 0 and 10 gather K/V tiles from their pages with cp.async into
+// four stages, alternately, and tie each tile's barrier to their copies
+// (cp.async.mbarrier.arrive.noinc), so a tile is announced the moment it has landed and the
+// loaders never wait for data; warp 1 owns tensor memory and issues the MMAs of query tile 0,
+// warp 11 those of tile 1 (S(j) first, then P·V of tile j-1 as its P arrives), independently
+// of one another; warps 2-5 and 6-9 are the softmax/epilogue warps of tiles 0 and 1.  A K/V
+// stage is free again when both issuers have committed its P·V.  Every mbarrier wait is
+// bounded and reports through the error word.  Arithmetic as the reference's prefill kernel
 // (src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127).
 #include "common.cuh"
 #include "mma_util.cuh"
