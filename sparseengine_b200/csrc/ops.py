@@ -255,6 +255,36 @@ def tc_check(device) -> None:
                                "its results are not valid")
 
 
+_tc_error_host = {}
+
+
+def tc_error_enqueue(device) -> None:
+    """Queue a copy of the error word to pinned host memory on the current stream: the step
+    function calls this after a forward pass and reads the copy (:func:`tc_error_raise`) once
+    it has synchronised for its own results, so the check costs no synchronisation of its own."""
+    key = torch.device(device)
+    t = _tc_error.get(key)
+    if t is None:
+        return
+    h = _tc_error_host.get(key)
+    if h is None:
+        h = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _tc_error_host[key] = h
+    h.copy_(t, non_blocking=True)
+
+
+def tc_error_raise(device) -> None:
+    """Raise if the copy queued by :func:`tc_error_enqueue` (and since completed) shows a timeout."""
+    key = torch.device(device)
+    h = _tc_error_host.get(key)
+    if h is not None and int(h[0]):
+        code = int(h[0])
+        h.zero_()
+        _tc_error[key].zero_()
+        raise RuntimeError(f"a tensor-core kernel timed out waiting on a barrier (role code {code}); "
+                           "its results are not valid")
+
+
 def gemm_tc_supported(k_dim: int, n_out: int, nt: int = 16) -> bool:
     f = library().se_gemm_tc_supported
     f.restype = _I

@@ -166,7 +166,10 @@ class LLM:
         logits = self.runner.step(entries)
         tokens, logprobs = ([], None)
         if reqs:
-            tokens, logprobs = self.sampler.sample(logits, reqs)
+            from ..csrc import ops
+            ops.tc_error_enqueue(self.runner.device)
+            tokens, logprobs = self.sampler.sample(logits, reqs)      # reads the tokens back: the stream is drained
+            ops.tc_error_raise(self.runner.device)
         finished = self.scheduler.postprocess(plan, tokens, logprobs)
         outs = [self._output(s) for s in finished]
         return outs, (prefill_tokens if prefill_tokens > 0 else -decodes)

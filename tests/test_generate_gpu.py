@@ -193,3 +193,20 @@ def test_many_requests_under_memory_pressure(folder_b, dtype):
             assert got[i] == want[i], i
     c = tight.runner.cache
     assert c.free_pages() == c.groups[0].pool.num_pages and c.groups[0].pool.reused_total > 0
+
+
+def test_a_kernel_that_gave_up_is_reported_by_the_next_step(folder_a):
+    """The tensor-core kernels bound every wait and write a code into a device word when one
+    runs out.  The entry point reads that word with the step's own results: here the word is
+    set by hand (no kernel is made to fail), and the step raises."""
+    from sparseengine_b200 import LLM, SamplingParams
+    from sparseengine_b200.csrc import ops
+    folder, _ = folder_a
+    llm = LLM(folder, dtype="bfloat16", page_size=4, num_kvcache_slots=64, max_model_len=32)
+    llm.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    llm.step()
+    ops.tc_error_flag("cuda:0").fill_(12)
+    with pytest.raises(RuntimeError, match="timed out waiting on a barrier .role code 12"):
+        llm.step()
+    llm.step()                                   # the word was cleared: the engine goes on
+    assert int(ops.tc_error_flag("cuda:0")) == 0
