@@ -262,6 +262,8 @@ def run_ours(args) -> dict:
     e2e = {"value": round(batch * args.steps / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": 4 * batch}
 
+    from sparseengine_b200.csrc import ops
+    ops.tc_check(llm.runner.device)       # a kernel that gave up on a wait would make every figure above void
     hbm = main["bytes"] / (main["ms"] * 1e-3) / 1e9
     return {
         "metric": "decode tokens/s (MiniMax M2 layer sizes, batch 8, context 4096)",
