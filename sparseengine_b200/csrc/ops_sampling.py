@@ -37,3 +37,14 @@ def to_float(src, dst):
         _ptr(src, None, "src"), _ptr(dst, torch.float32, "dst"), src.numel(), dtype_code(src.dtype), _stream()),
         "to_float")
     return dst
+
+
+def top_logprobs(logits, rows, ids, values):
+    """The ``ids.shape[1]`` most likely tokens of the listed rows with their log-probabilities
+    (32-bit log-softmax), most likely first."""
+    count, n = ids.shape
+    _check(_fn("se_top_logprobs", "pppp" "iiii" "p")(
+        _ptr(logits, None, "logits"), _ptr(rows, torch.int32, "rows"), _ptr(ids, torch.int32, "ids"),
+        _ptr(values, torch.float32, "values"), count, logits.shape[1], n, dtype_code(logits.dtype), _stream()),
+        "top_logprobs")
+    return ids, values

@@ -246,6 +246,93 @@ extern "C" int se_apply_penalties(float* logits, const int* pairs, int n, int vo
     SE_LAUNCH_CHECK();
 }
 
+namespace se {
+
+// The n most likely tokens of a row with their log-probabilities (log-softmax in 32-bit of the
+// logits as given), most likely first, equal logits by ascending token id
+// (src/sparseengine/engine/model_runner.py:2528-2569: log_softmax, then topk).  One block per
+// listed row: a pass for the log-sum-exp, then one pass per entry for the best logit after the
+// previous one in that order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+top_logprobs_kernel(const T* __restrict__ logits, const int* __restrict__ rows, int* __restrict__ ids,
+                    float* __restrict__ values, int vocab, int n) {
+    __shared__ float red[33];
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    __shared__ float prev_v_s;
+    __shared__ int prev_i_s;
+    const T* lg = logits + (size_t)rows[blockIdx.x] * vocab;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, to_float(lg[i]));
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = -INFINITY;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(to_float(lg[i]) - mx);
+    sum = block_sum(sum, red);
+    const float lse = mx + logf(sum);
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int r = 0; r < n; ++r) {
+        // the best (value descending, id ascending) strictly after (prev_v, prev_i)
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = to_float(lg[i]);
+            const bool after = v < prev_v || (v == prev_v && i > prev_i);
+            if (after && (v > bv || (v == bv && i < bi))) {
+                bv = v;
+                bi = i;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            best_v[warp] = bv;
+            best_i[warp] = bi;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+                if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) {
+                    bv = best_v[w];
+                    bi = best_i[w];
+                }
+            prev_v_s = bv;
+            prev_i_s = bi;
+            ids[(size_t)blockIdx.x * n + r] = bi == 0x7fffffff ? -1 : bi;        // -1: fewer than n tokens (NaN logits)
+            values[(size_t)blockIdx.x * n + r] = bv - lse;
+        }
+        __syncthreads();
+        prev_v = prev_v_s;
+        prev_i = prev_i_s;
+    }
+}
+
+}  // namespace se
+
+// rows: int32 [count] row indices into logits [*, vocab]; ids int32 [count, n], values float [count, n].
+extern "C" int se_top_logprobs(const void* logits, const int* rows, int* ids, float* values, int count, int vocab, int n,
+                               int dtype, cudaStream_t stream) {
+    if (count <= 0 || n <= 0) return 0;
+    if (n > vocab) return SE_ERR_ARGUMENT;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::top_logprobs_kernel<T><<<count, 256, 0, stream>>>((const T*)logits, rows, ids, values, vocab, n));
+    SE_LAUNCH_CHECK();
+}
+
 extern "C" int se_to_float(const void* src, float* dst, long long n, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
     const int blocks = (int)((n + 1023) / 1024 < 4096 ? (n + 1023) / 1024 : 4096);

@@ -170,7 +170,7 @@ class LLM:
             ops.tc_error_enqueue(self.runner.device)
             tokens, logprobs = self.sampler.sample(logits, reqs)      # reads the tokens back: the stream is drained
             ops.tc_error_raise(self.runner.device)
-        finished = self.scheduler.postprocess(plan, tokens, logprobs)
+        finished = self.scheduler.postprocess(plan, tokens, logprobs, self.sampler.last_top_logprobs if reqs else None)
         outs = [self._output(s) for s in finished]
         return outs, (prefill_tokens if prefill_tokens > 0 else -decodes)
 
@@ -178,8 +178,10 @@ class LLM:
         tok = self._tok() if self._tokenizer_tried or isinstance(self.config.model, str) else None
         text = tok.decode(s.output_ids, skip_special_tokens=True) if tok is not None else ""
         out = {"seq_id": s.seq_id, "text": text, "token_ids": list(s.output_ids), "finish_reason": s.finish_reason}
-        if s.logprobs:
+        if s.params.logprobs is not None and s.logprobs:
             out["logprobs"] = list(s.logprobs)
+        if any(t is not None for t in s.top_logprobs):
+            out["top_logprobs"] = list(s.top_logprobs)
         return out
 
     def generate(self, prompts: Seq, sampling_params=None, use_tqdm: bool = False) -> list:

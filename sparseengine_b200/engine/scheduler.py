@@ -194,7 +194,7 @@ class Scheduler:
         s.status, s.finish_reason = Status.FINISHED, reason
 
     # ---- after the step ----------------------------------------------------------------
-    def postprocess(self, plan: StepPlan, tokens: list, logprobs=None) -> list:
+    def postprocess(self, plan: StepPlan, tokens: list, logprobs=None, top_logprobs=None) -> list:
         """``tokens``: one sampled token per planned item that samples, in plan order.
         Returns the requests that finished."""
         finished = []
@@ -210,6 +210,8 @@ class Scheduler:
             s.output_ids.append(tok)
             if logprobs is not None:
                 s.logprobs.append(logprobs[i])
+            if top_logprobs is not None:
+                s.top_logprobs.append(top_logprobs[i])
             eos = s.params.eos_token_ids or self.eos_token_ids
             if not s.params.ignore_eos and tok in eos:
                 reason = "stop"

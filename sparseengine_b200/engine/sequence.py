@@ -20,6 +20,7 @@ class Sequence:
     params: SamplingParams
     output_ids: list = field(default_factory=list)
     logprobs: list = field(default_factory=list)
+    top_logprobs: list = field(default_factory=list)     # per produced token: {token id: log-probability} or None
     num_computed: int = 0          # tokens whose keys/values are in the cache
     status: Status = Status.WAITING
     preemptions: int = 0

@@ -37,6 +37,9 @@ def row_seed(sampler_seed: int, seq_id, step: int) -> int:
 class Sampler:
     def __init__(self, seed: int = 0):
         self.seed = int(seed)
+        # per row of the last call: {token id: log-probability} of the most likely tokens for
+        # requests with logprobs = n > 0 (src/sparseengine/engine/model_runner.py:2528-2569), else None
+        self.last_top_logprobs = None
 
     def sample(self, logits: torch.Tensor, requests: Sequence[SampleRequest]):
         """logits [n, vocab] (activation dtype) → (token ids list[int], logprobs list or None)."""
@@ -69,11 +72,27 @@ class Sampler:
             top_k = d[3 * n:4 * n]
             top_p = d[4 * n:5 * n].view(torch.float32)
             sops.sample(logits, temp, top_k, top_p, seeds, out, lp)
+        # the n most likely tokens of the rows that asked for them (logprobs = n > 0)
+        top_rows = [i for i, r in enumerate(requests) if r.params.logprobs]
+        top_n = min(max((requests[i].params.logprobs for i in top_rows), default=0), vocab)
+        if top_rows:
+            rows_d = torch.tensor(top_rows, dtype=torch.int32).to(dev)
+            top_ids = torch.empty(len(top_rows), top_n, dtype=torch.int32, device=dev)
+            top_vals = torch.empty(len(top_rows), top_n, dtype=torch.float32, device=dev)
+            sops.top_logprobs(logits, rows_d, top_ids, top_vals)
         tokens = out.tolist()
         logprobs = None
         if want_lp:
             chosen = lp.tolist()
             logprobs = [chosen[i] if r.params.logprobs is not None else None for i, r in enumerate(requests)]
+        self.last_top_logprobs = None
+        if top_rows:
+            ids_h, vals_h = top_ids.tolist(), top_vals.tolist()
+            tops = [None] * n
+            for k, i in enumerate(top_rows):
+                want = min(requests[i].params.logprobs, top_n)
+                tops[i] = {int(t): float(v) for t, v in zip(ids_h[k][:want], vals_h[k][:want]) if t >= 0}
+            self.last_top_logprobs = tops
         return tokens, logprobs
 
     def _penalised(self, logits, requests):

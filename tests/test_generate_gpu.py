@@ -210,3 +210,25 @@ def test_a_kernel_that_gave_up_is_reported_by_the_next_step(folder_a):
         llm.step()
     llm.step()                                   # the word was cleared: the engine goes on
     assert int(ops.tc_error_flag("cuda:0")) == 0
+
+
+def test_logprobs_of_the_chosen_and_of_the_most_likely_tokens(folder_a):
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, tensors = folder_a
+    llm = LLM(folder, dtype="float32", page_size=4, num_kvcache_slots=128, max_model_len=64)
+    prompts = [tu.random_prompt(256, 7, 3), tu.random_prompt(256, 5, 4), tu.random_prompt(256, 6, 5)]
+    params = [SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True, logprobs=3),
+              SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True, logprobs=0)]
+    outs = llm.generate(prompts, params)
+    assert "top_logprobs" not in outs[1] and "logprobs" not in outs[1]
+    assert "top_logprobs" not in outs[2] and len(outs[2]["logprobs"]) == 3       # logprobs=0: the chosen token's only
+    o = outs[0]
+    toks = list(prompts[0])
+    for t, lp, top in zip(o["token_ids"], o["logprobs"], o["top_logprobs"]):
+        ref = torch.log_softmax(plain_m2.forward(plain_m2.TINY_A, tensors, toks)[-1].float(), -1)
+        want = ref.topk(3)
+        assert list(top) == want.indices.tolist() and list(top)[0] == t          # greedy: the chosen is the most likely
+        assert abs(lp - top[t]) < 1e-6
+        torch.testing.assert_close(torch.tensor(list(top.values())), want.values, atol=1e-4, rtol=1e-4)
+        toks.append(t)

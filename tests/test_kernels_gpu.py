@@ -561,3 +561,23 @@ def test_gemv_for_a_handful_of_rows(rows, n_out, k_dim):
     ref = (x.float() @ w.float().t())
     torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), atol=2e-2, rtol=2e-2)
     assert not ops.gemv_supported(17, n_out, k_dim) and not ops.gemv_supported(4, n_out, 40)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_top_logprobs(dtype):
+    """The n most likely tokens of chosen rows with 32-bit log-softmax values, most likely first,
+    equal logits by ascending id."""
+    from sparseengine_b200.csrc import ops_sampling as sops
+    vocab, n = 1003, 5
+    logits = rnd(6, vocab, dtype=dtype, scale=3.0, seed=11)
+    logits[2, 10] = logits[2, 700] = logits[2, 3] = 50.0         # a three-way tie at the top
+    rows = torch.tensor([4, 2, 0], dtype=torch.int32, device=DEV)
+    ids = torch.empty(3, n, dtype=torch.int32, device=DEV)
+    vals = torch.empty(3, n, dtype=torch.float32, device=DEV)
+    sops.top_logprobs(logits, rows, ids, vals)
+    lp = torch.log_softmax(logits.float().cpu(), -1)
+    for k, r in enumerate(rows.tolist()):
+        order = sorted(range(vocab), key=lambda i: (-float(lp[r, i]), i))[:n]
+        assert ids[k].tolist() == order
+        torch.testing.assert_close(vals[k].cpu(), lp[r, order], atol=2e-5, rtol=1e-5)
+    assert ids[1].tolist()[:3] == [3, 10, 700]
