@@ -241,6 +241,25 @@ def run_ours(args) -> dict:
                "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
                "hbm_frac": round(pre_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
 
+    # ---- an extra point: four such prompts in one step (8,192 tokens: towards compute-bound) ----
+    prompts4 = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(4)]
+    ms4 = []
+    for i in range(3):
+        ids4 = [f"q{i}_{j}" for j in range(4)]
+        for sid in ids4:
+            runner.admit(sid)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(sid, p, [PROMPT_LEN - 1]) for sid, p in zip(ids4, prompts4)])
+        e1.record()
+        torch.cuda.synchronize()
+        ms4.append(e0.elapsed_time(e1))
+        for sid in ids4:
+            runner.release(sid)
+    points["prefill_4x2048"] = round(4 * PROMPT_LEN * 1000.0 / min(ms4[1:]), 1)
+    points["prefill_4x2048_frac"] = round(4 * flops / (min(ms4[1:]) * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+
     # ---- end to end through the public API -----------------------------------------------
     sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 16, ignore_eos=True)
     for _ in range(batch):
