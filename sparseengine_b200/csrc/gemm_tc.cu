@@ -132,7 +132,7 @@ struct Params {
     int w_rows_per_expert;      // rows of the 2-D weight view per expert (2I or H)
     int up_offset;              // row offset of the "up" half (MODE_GATE_UP)
     int total_rows;             // dense: number of activation rows
-    int nt;                     // activation rows per tile: 16, 32, 64 or 128
+    int nt;                     // activation rows per tile: 16, 32, 64, 128 or 256
     int stages;                 // depth of the shared-memory ring
 };
 
@@ -199,7 +199,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     __shared__ __align__(16) uint4 sched_s[kSchedSlots];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
-    __shared__ float route_s[2][128];
+    __shared__ float route_s[2][256];
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * kMaxStages]), acc_empty0 = smem_u32(&bars[2 * kMaxStages + 2]);
     const uint32_t sched_full0 = smem_u32(&bars[2 * kMaxStages + 4]);
@@ -207,8 +207,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const uint32_t sched0 = smem_u32(&sched_s[0]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // two accumulator buffers where tensor memory (512 columns) holds them, else one: the
+    // epilogue of an item then ends before the MMAs of the next one begin
+    const int bufs = 2 * NA * nt <= 512 ? 2 : 1;
     uint32_t cols = 32;
-    while ((int)cols < 2 * NA * nt) cols <<= 1;
+    while ((int)cols < bufs * NA * nt) cols <<= 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -343,8 +346,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             bool ok = true;
             for (int j = 0; ok; ++j) {
                 if (by < tiles) {
-                    const int b = used & 1;
-                    if (!mbar_wait(acc_empty0 + 8 * b, ((used >> 1) & 1) ^ 1, &abort_s)) {   // the epilogue has drained buffer b
+                    const int b = used % bufs;
+                    if (!mbar_wait(acc_empty0 + 8 * b, ((used / bufs) & 1) ^ 1, &abort_s)) {   // the epilogue has drained buffer b
                         abort_s = 1;
                         atomicCAS(p.error, 0, 4);
                         break;
@@ -385,7 +388,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         int used = 0;
         for (int j = 0;; ++j) {
             if (by < tiles) {
-                const int b = used & 1;
+                const int b = used % bufs;
                 const int tile = by, n0 = bx * kItemM;
                 int row0 = tile * nt, row_end = p.total_rows;
                 if (p.tile_expert != nullptr) {
@@ -394,10 +397,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 }
                 const int valid = min(nt, row_end - row0);
                 if (MODE == MODE_DOWN) {
-                    if (et < nt) route_s[b][et] = et < valid ? p.route_w[p.sorted[row0 + et]] : 0.f;
+                    for (int e = et; e < nt; e += 128) route_s[b][e] = e < valid ? p.route_w[p.sorted[row0 + e]] : 0.f;
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }
-                if (!mbar_wait(acc_full0 + 8 * b, (used >> 1) & 1, &abort_s)) {
+                if (!mbar_wait(acc_full0 + 8 * b, (used / bufs) & 1, &abort_s)) {
                     abort_s = 1;
                     atomicCAS(p.error, 0, 3);
                     break;
@@ -542,8 +545,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     // A CTA takes 2 * NA * nt columns of tensor memory (512 per SM).  Where two CTAs would
     // fit by shared memory but not by columns, ask for more than half of the shared memory, so
     // that no CTA waits for columns behind a persistent neighbour.
+    const int bufs = 2 * NA * p.nt <= 512 ? 2 : 1;
     int cols = 32;
-    while (cols < 2 * NA * p.nt) cols <<= 1;
+    while (cols < bufs * NA * p.nt) cols <<= 1;
     if (2 * cols > 512) smem = std::max<size_t>(smem, 116 * 1024);
     const int item_m = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
     dim3 grid(ceil_div(p.n_out, item_m), tiles);
@@ -577,7 +581,7 @@ static int pick_stages(int na, int nt) {
 // 1 if the tensor-core path takes these sizes (bf16 only; row pitches must be 16-byte
 // multiples for TMA), else 0.
 extern "C" int se_gemm_tc_supported(int k_dim, int n_out, int nt) {
-    return (k_dim % 8 == 0 && k_dim >= 8 && n_out >= 1 && (nt == 16 || nt == 32 || nt == 64 || nt == 128)) ? 1 : 0;
+    return (k_dim % 8 == 0 && k_dim >= 8 && n_out >= 1 && (nt == 16 || nt == 32 || nt == 64 || nt == 128 || nt == 256)) ? 1 : 0;
 }
 
 extern "C" int se_moe_permute_rows(const void* x, const int* sorted, void* out, int rows, int width, int top_k,

@@ -8,6 +8,7 @@ these functions: without the compiled library they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -294,8 +295,15 @@ def gemm_tc_supported(k_dim: int, n_out: int, nt: int = 16) -> bool:
 
 def moe_tile_rows_tc(assignments: int, experts: int) -> int:
     """Activation rows per tile for the tensor-core grouped GEMM: about twice the mean
-    number of rows per expert, a power of two in [16, 128]."""
+    number of rows per expert, a power of two in [16, 128]; 256 once the mean reaches 192 rows
+    (an expert's weights then cross from L2 to an SM once per 256 rows instead of once per 128,
+    which is what bounds the GEMM when it is no longer bound by HBM)."""
+    forced = os.environ.get("SE_MOE_TILE_ROWS")          # tuning aid
+    if forced:
+        return int(forced)
     want = max(1, -(-2 * assignments // max(experts, 1)))
+    if want >= 384:
+        return 256
     nt = 16
     while nt < want and nt < 128:
         nt *= 2
