@@ -71,6 +71,7 @@ class _DecodeGraph:
 
 class ModelRunner:
     KV_BUCKET = 512               # decode graphs are planned for context lengths rounded up to this
+    MAX_GRAPHS = 64               # captured graphs kept (least recently used go first)
 
     def __init__(self, model: Model, cache: CacheManager, device="cuda:0", decode_graphs: bool = True):
         self.model = model
@@ -239,11 +240,14 @@ class ModelRunner:
                     recorded = ops.launch_count - before
                     ops.launch_count = before            # nothing ran during capture
                     self._graphs[key] = _DecodeGraph(graph, meta, static_logits, recorded)
+                    while len(self._graphs) > self.MAX_GRAPHS:          # dicts keep insertion order
+                        self._graphs.pop(next(iter(self._graphs)))
                 except Exception as exc:                 # capture is an optimisation only
                     self.decode_graphs = False
                     print(f"[sparseengine_b200] CUDA graph capture failed ({exc!r}); decode runs without graphs",
                           flush=True)
             else:
+                self._graphs[key] = self._graphs.pop(key)               # most recently used last
                 entry.graph.replay()
                 self.graph_replays += 1
                 ops.launch_count += entry.kernels

@@ -260,3 +260,23 @@ def test_decode_graphs_give_what_single_launches_give(folders, dtype):
     assert a.keys() == b.keys()
     for k in a:
         assert np.array_equal(a[k], b[k]), k        # same kernels, same plans at these lengths: bit-equal
+
+
+def test_decode_graphs_are_kept_up_to_a_limit(folders):
+    """Graphs are captured per (batch size, context bucket); the least recently used are dropped."""
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, _ = folders["A", "float32"]
+    from sparseengine_b200.engine.factory import build_runner
+    runner = build_runner(folder, dtype="float32", page_size=4, num_pages=64, max_rows=4)
+    runner.MAX_GRAPHS, runner.KV_BUCKET = 3, 4
+    runner.admit("a")
+    outs = []
+    for i in range(30):
+        outs.append(runner.step([StepEntry("a", [i % 7], [0])]).float().cpu())
+        assert len(runner._graphs) <= 3
+    assert runner.graph_replays > 10
+    plain = build_runner(folder, dtype="float32", page_size=4, num_pages=64, max_rows=4, decode_graphs=False)
+    plain.admit("a")
+    for i in range(30):
+        ref = plain.step([StepEntry("a", [i % 7], [0])]).float().cpu()
+        assert (outs[i] - ref).abs().max() < 1e-5
