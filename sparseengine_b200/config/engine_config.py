@@ -30,6 +30,7 @@ class Config:
     sparse_method: str = ""                        # "" or "vanilla": the dense cache
     mlp_chunk_size: int = 16384                    # most rows the feed-forward takes at once
     decode_graph: bool = True                      # replay decode steps as CUDA graphs
+    async_scheduling: bool = True                  # queue the next decode step before the host has read this one's tokens
     enable_profiler: bool = False                  # CUDA-event timing of every part (forces launch-by-launch steps)
     validate_runtime_invariants: bool = False      # host-side checks of every step's index tensors
     throughput_log_interval_s: float = 10.0        # generate() logs tokens/s this often (0 = never)

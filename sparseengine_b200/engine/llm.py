@@ -27,7 +27,7 @@ from ..sampling.sampler import SampleRequest, Sampler
 from .factory import build_runner, require_cuda, resolve_dtype
 from .runner import StepEntry
 from .scheduler import Scheduler
-from .sequence import Sequence
+from .sequence import Sequence, Status
 
 
 def _eos_from_folder(model_dir: str, raw: dict) -> tuple:
@@ -44,6 +44,14 @@ def _eos_from_folder(model_dir: str, raw: dict) -> tuple:
     if v is None:
         return ()
     return tuple(v) if isinstance(v, list) else (int(v),)
+
+
+class _InFlight:
+    """A step that has been queued on the device: its plan and its sampling results on their way."""
+
+    def __init__(self, plan, pending):
+        self.plan = plan
+        self.pending = pending
 
 
 class LLM:
@@ -89,6 +97,8 @@ class LLM:
         self.scheduler = Scheduler(cfg, cache, eos_token_ids=eos, max_model_len=self.max_model_len)
         self.sampler = Sampler(cfg.seed)
         self._next_id = 0
+        self._inflight = None
+        self.steps_ahead = 0           # decode steps queued before the step in front of them had been read
         self._tokenizer = None
         self._tokenizer_tried = False
 
@@ -150,27 +160,77 @@ class LLM:
         return self.scheduler.abort(seq_id)
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        return self.scheduler.is_finished() and self._inflight is None
 
-    def step(self):
-        plan = self.scheduler.schedule()
+    # ---- one step ------------------------------------------------------------------------
+    # A step is queued on the device (forward pass, sampling, copies of the results to pinned
+    # host memory) and read later.  With ``async_scheduling`` the next step of a batch that only
+    # decodes is queued *before* this step's tokens are read: its input tokens are this step's
+    # sampled ids, handed over on the device, so the GPU does not idle while the host reads
+    # tokens, books them and prepares the next launch (the reference's asynchronous scheduling,
+    # src/sparseengine/engine/llm_engine.py:1826-1957).  A request that turns out to have ended
+    # (an end-of-sequence token, an abort) has then one token too many computed; it is dropped
+    # when that step is read.
+
+    def _launch(self, plan, feedback=None) -> "_InFlight":
         entries, reqs = [], []
         for it in plan.items:
             s = it.seq
-            toks = s.slice(it.start, it.n_tokens)
+            ahead = 1 if feedback is not None else 0          # tokens of this request still on their way
+            toks = [0] if feedback is not None else s.slice(it.start, it.n_tokens)
             entries.append(StepEntry(s.seq_id, toks, [it.n_tokens - 1] if it.samples else []))
             if it.samples:
-                reqs.append(SampleRequest(s.params, s.seq_id, len(s.output_ids), s.prompt_ids, s.output_ids))
-        decodes = plan.num_decodes
-        prefill_tokens = plan.num_tokens - decodes
-        logits = self.runner.step(entries)
-        tokens, logprobs = ([], None)
+                reqs.append(SampleRequest(s.params, s.seq_id, len(s.output_ids) + ahead, s.prompt_ids, s.output_ids))
+        logits = self.runner.step(entries, token_feedback=feedback)
+        pending = None
         if reqs:
             from ..csrc import ops
             ops.tc_error_enqueue(self.runner.device)
-            tokens, logprobs = self.sampler.sample(logits, reqs)      # reads the tokens back: the stream is drained
+            pending = self.sampler.submit(logits, reqs)
+        return _InFlight(plan, pending)
+
+    def _may_run_ahead(self, cur: "_InFlight") -> bool:
+        """Whether the step after ``cur`` can be queued before ``cur``'s tokens are known: every
+        resident request decodes and is in ``cur``, none can end by length with the token on its
+        way, nothing waits, nothing needs the tokens on the host, and the pages are there."""
+        sch = self.scheduler
+        if not self.config.async_scheduling or cur.pending is None or sch.waiting or cur.plan.preempted:
+            return False
+        items = cur.plan.items
+        if len(items) != len(sch.running) or len(items) > self.config.max_decoding_seqs:
+            return False
+        for it, s in zip(items, sch.running):
+            if it.seq is not s or it.n_tokens != 1 or not it.samples or not s.in_decode:
+                return False
+            p = s.params
+            if p.has_penalties or p.benchmark_forced_token_ids is not None:
+                return False
+            if len(s.output_ids) + 2 > p.max_tokens or s.num_tokens + 2 > self.max_model_len:
+                return False
+        return self.runner.cache.can_reserve([(it.seq.seq_id, 1) for it in items])
+
+    def step(self):
+        cur = self._inflight
+        self._inflight = None
+        if cur is None:
+            cur = self._launch(self.scheduler.schedule())
+        nxt = None
+        if self._may_run_ahead(cur):
+            from .scheduler import Planned, StepPlan
+            plan = StepPlan()
+            plan.items = [Planned(it.seq, it.start + 1, 1, True) for it in cur.plan.items]
+            nxt = self._launch(plan, feedback=cur.pending.tokens_device)
+            self.steps_ahead += 1
+        tokens, logprobs, tops = ([], None, None)
+        if cur.pending is not None:
+            from ..csrc import ops
+            tokens, logprobs, tops = self.sampler.collect(cur.pending)
             ops.tc_error_raise(self.runner.device)
-        finished = self.scheduler.postprocess(plan, tokens, logprobs, self.sampler.last_top_logprobs if reqs else None)
+        live = sum(1 for it in cur.plan.items if it.seq.status == Status.RUNNING)
+        decodes = min(cur.plan.num_decodes, live)
+        prefill_tokens = cur.plan.num_tokens - cur.plan.num_decodes
+        finished = self.scheduler.postprocess(cur.plan, tokens, logprobs, tops)
+        self._inflight = nxt
         outs = [self._output(s) for s in finished]
         return outs, (prefill_tokens if prefill_tokens > 0 else -decodes)
 
@@ -222,6 +282,7 @@ class LLM:
         c = self.runner.cache
         out = {"steps": self.runner.steps, "tokens": self.runner.tokens,
                "preemptions": self.scheduler.num_preemptions, "graph_replays": self.runner.graph_replays,
+               "steps_ahead": self.steps_ahead,
                "waiting": len(self.scheduler.waiting), "running": len(self.scheduler.running),
                "free_rows": c.free_rows,
                "pages": [{"free": g.pool.free, "total": g.pool.num_pages, "taken": g.pool.taken_total,
@@ -234,6 +295,9 @@ class LLM:
         return out
 
     def exit(self) -> None:
+        if self._inflight is not None and self._inflight.pending is not None:
+            self.sampler.collect(self._inflight.pending)        # let what is queued finish
+        self._inflight = None
         self.runner = None
         self.scheduler = None
         torch.cuda.empty_cache()

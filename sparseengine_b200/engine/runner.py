@@ -100,9 +100,13 @@ class ModelRunner:
         self.cache.release(seq_id)
 
     # ---- the step ------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_feedback: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch.  Returns logits ``[wanted, vocab]`` (activation dtype) in the
         order of the entries and of each entry's ``want``, or ``None`` if nothing is wanted.
+
+        ``token_feedback``: for a step of single tokens, an int32 device tensor with the entries'
+        tokens in their order (the ids a sampler has just written): the step is then queued
+        without the host knowing them; the entries' own ``tokens`` are placeholders.
 
         Raises :class:`OutOfPages` (and changes nothing) if the pages do not suffice.
         The returned tensor may be overwritten by the next step."""
@@ -135,10 +139,13 @@ class ModelRunner:
             if self.validate:
                 self._check_invariants(entries)
             if self.decode_graphs and all(len(e.tokens) == 1 for e in entries):
-                logits = self._step_graph(entries)
+                logits = self._step_graph(entries, token_feedback)
             else:
                 logits = None
             if logits is None:
+                if token_feedback is not None:       # no graph for this step: the host has to see the tokens after all
+                    for e, t in zip(entries, token_feedback.tolist()):
+                        e.tokens = [int(t)]
                 step, want_rows, updates = self._pack(entries)
                 with torch.cuda.device(self.device):
                     for g, (upd, n) in zip(self.cache.groups, updates):
@@ -176,7 +183,7 @@ class ModelRunner:
                     raise AssertionError(f"request {e.seq_id!r}: block table has no valid page for positions {lo}..{end - 1}")
 
     # ---- decode steps as replayed CUDA graphs ------------------------------------------
-    def _step_graph(self, entries):
+    def _step_graph(self, entries, token_feedback=None):
         """Run a decode-only step through a captured graph.  Returns the logits of the wanted
         rows, or ``None`` if this step cannot use a graph (too many block-table updates
         pending, or capture is not possible), in which case nothing has been done."""
@@ -213,6 +220,8 @@ class ModelRunner:
             meta = entry.meta if entry is not None else torch.empty(total, dtype=torch.int32, device=self.device)
             meta.copy_(host[:total], non_blocking=True)
             self._staging.mark(slot)
+            if token_feedback is not None:
+                meta[int(offs[0]):int(offs[0]) + n].copy_(token_feedback[:n])
 
             def view(i, length):
                 return meta[int(offs[i]):int(offs[i]) + length]

@@ -201,6 +201,10 @@ class Scheduler:
         it = iter(range(len(tokens)))
         for item in plan.items:
             s = item.seq
+            if s.status != Status.RUNNING:       # ended (or was preempted) while this step was on its way:
+                if item.samples:                 # its token is one too many
+                    next(it)
+                continue
             s.num_computed += item.n_tokens
             if not item.samples:
                 continue

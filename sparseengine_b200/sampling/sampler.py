@@ -34,22 +34,67 @@ def row_seed(sampler_seed: int, seq_id, step: int) -> int:
     return int.from_bytes(h, "little")
 
 
+class _PinnedPool:
+    """Pinned host buffers for results on their way back, reused (allocating one is slow)."""
+
+    def __init__(self):
+        self.free: dict = {}
+
+    def take(self, n: int, dtype) -> torch.Tensor:
+        size = 1 << max(6, (max(n, 1) - 1).bit_length())
+        lst = self.free.setdefault((size, dtype), [])
+        return lst.pop() if lst else torch.empty(size, dtype=dtype, pin_memory=True)
+
+    def give(self, t: torch.Tensor) -> None:
+        self.free.setdefault((t.numel(), t.dtype), []).append(t)
+
+
+class Pending:
+    """What :meth:`Sampler.submit` queued: the tokens (and log-probabilities) of one step on
+    their way to pinned host memory, and an event that says when they have arrived.
+    ``tokens_device`` are the sampled ids on the device (int32 ``[n]``), for a next step that is
+    launched before the host has seen them."""
+
+    def __init__(self):
+        self.tokens_device = None
+        self.event = None
+        self.n = 0
+        self.requests = ()
+        self.host = {}           # name -> (pinned buffer, shape)
+        self.keep = []           # device tensors that must outlive the copies
+        self.top_rows = []
+        self.top_n = 0
+
+
 class Sampler:
     def __init__(self, seed: int = 0):
         self.seed = int(seed)
         # per row of the last call: {token id: log-probability} of the most likely tokens for
         # requests with logprobs = n > 0 (src/sparseengine/engine/model_runner.py:2528-2569), else None
         self.last_top_logprobs = None
+        self._pool = _PinnedPool()
 
-    def sample(self, logits: torch.Tensor, requests: Sequence[SampleRequest]):
-        """logits [n, vocab] (activation dtype) → (token ids list[int], logprobs list or None)."""
+    def _upload(self, host: np.ndarray, dev) -> torch.Tensor:
+        """A small host array to the device through pinned memory, without blocking the host."""
+        pin = self._pool.take(host.size, torch.int32)
+        pin[:host.size].numpy()[:] = host.view(np.int32)
+        d = torch.empty(host.size, dtype=torch.int32, device=dev)
+        d.copy_(pin[:host.size], non_blocking=True)
+        return d, pin
+
+    def submit(self, logits: torch.Tensor, requests: Sequence[SampleRequest]) -> Pending:
+        """Queue the sampling of every row and the copies of the results to the host; nothing
+        here waits for the device."""
         n, vocab = logits.shape
         if n != len(requests):
             raise ValueError("one sampling request per logits row is needed")
         dev = logits.device
+        pend = Pending()
+        pend.n, pend.requests = n, list(requests)
         want_lp = any(r.params.logprobs is not None for r in requests)
         out = torch.empty(n, dtype=torch.int32, device=dev)
         lp = torch.empty(n, dtype=torch.float32, device=dev) if want_lp else None
+        pins = []
 
         if any(r.params.has_penalties for r in requests):
             logits = self._penalised(logits, requests)
@@ -66,33 +111,70 @@ class Sampler:
                 f[2 * n + i] = r.params.temperature
                 host[3 * n + i] = min(r.params.top_k, vocab)
                 f[4 * n + i] = r.params.top_p
-            d = torch.from_numpy(host.view(np.int32)).to(dev, non_blocking=False)
+            d, pin = self._upload(host, dev)
+            pins.append(pin)
             seeds = d[:2 * n].view(torch.int64)
             temp = d[2 * n:3 * n].view(torch.float32)
             top_k = d[3 * n:4 * n]
             top_p = d[4 * n:5 * n].view(torch.float32)
             sops.sample(logits, temp, top_k, top_p, seeds, out, lp)
+            pend.keep.append(d)
         # the n most likely tokens of the rows that asked for them (logprobs = n > 0)
-        top_rows = [i for i, r in enumerate(requests) if r.params.logprobs]
-        top_n = min(max((requests[i].params.logprobs for i in top_rows), default=0), vocab)
-        if top_rows:
-            rows_d = torch.tensor(top_rows, dtype=torch.int32).to(dev)
-            top_ids = torch.empty(len(top_rows), top_n, dtype=torch.int32, device=dev)
-            top_vals = torch.empty(len(top_rows), top_n, dtype=torch.float32, device=dev)
-            sops.top_logprobs(logits, rows_d, top_ids, top_vals)
-        tokens = out.tolist()
-        logprobs = None
+        pend.top_rows = [i for i, r in enumerate(requests) if r.params.logprobs]
+        pend.top_n = min(max((requests[i].params.logprobs for i in pend.top_rows), default=0), vocab)
+        results = {"tokens": out}
         if want_lp:
-            chosen = lp.tolist()
-            logprobs = [chosen[i] if r.params.logprobs is not None else None for i, r in enumerate(requests)]
-        self.last_top_logprobs = None
-        if top_rows:
-            ids_h, vals_h = top_ids.tolist(), top_vals.tolist()
-            tops = [None] * n
-            for k, i in enumerate(top_rows):
-                want = min(requests[i].params.logprobs, top_n)
+            results["lp"] = lp
+        if pend.top_rows:
+            rows_d, pin = self._upload(np.asarray(pend.top_rows, dtype=np.int32), dev)
+            pins.append(pin)
+            top_ids = torch.empty(len(pend.top_rows), pend.top_n, dtype=torch.int32, device=dev)
+            top_vals = torch.empty(len(pend.top_rows), pend.top_n, dtype=torch.float32, device=dev)
+            sops.top_logprobs(logits, rows_d, top_ids, top_vals)
+            results["top_ids"], results["top_vals"] = top_ids, top_vals
+            pend.keep.append(rows_d)
+        for name, t in results.items():
+            pin = self._pool.take(t.numel(), t.dtype)
+            pin[:t.numel()].copy_(t.reshape(-1), non_blocking=True)
+            pend.host[name] = (pin, tuple(t.shape))
+        pend.keep += list(results.values()) + [logits]
+        pend.tokens_device = out
+        pend.event = torch.cuda.Event()
+        pend.event.record()
+        pend._pins = pins
+        return pend
+
+    def collect(self, pend: Pending):
+        """Wait for what :meth:`submit` queued; returns (tokens, logprobs or None, top log-probabilities or None)."""
+        pend.event.synchronize()
+
+        def host(name):
+            pin, shape = pend.host[name]
+            n = int(np.prod(shape)) if shape else 1
+            return pin[:n].view(*shape).tolist() if len(shape) > 1 else pin[:n].tolist()
+        tokens = host("tokens")
+        logprobs = None
+        if "lp" in pend.host:
+            chosen = host("lp")
+            logprobs = [chosen[i] if r.params.logprobs is not None else None for i, r in enumerate(pend.requests)]
+        tops = None
+        if pend.top_rows:
+            ids_h, vals_h = host("top_ids"), host("top_vals")
+            tops = [None] * pend.n
+            for k, i in enumerate(pend.top_rows):
+                want = min(pend.requests[i].params.logprobs, pend.top_n)
                 tops[i] = {int(t): float(v) for t, v in zip(ids_h[k][:want], vals_h[k][:want]) if t >= 0}
-            self.last_top_logprobs = tops
+        for pin, _ in pend.host.values():
+            self._pool.give(pin)
+        for pin in pend._pins:
+            self._pool.give(pin)
+        pend.host, pend.keep, pend._pins = {}, [], []
+        return tokens, logprobs, tops
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[SampleRequest]):
+        """logits [n, vocab] (activation dtype) → (token ids list[int], logprobs list or None)."""
+        tokens, logprobs, tops = self.collect(self.submit(logits, requests))
+        self.last_top_logprobs = tops
         return tokens, logprobs
 
     def _penalised(self, logits, requests):

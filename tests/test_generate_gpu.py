@@ -232,3 +232,52 @@ def test_logprobs_of_the_chosen_and_of_the_most_likely_tokens(folder_a):
         assert abs(lp - top[t]) < 1e-6
         torch.testing.assert_close(torch.tensor(list(top.values())), want.values, atol=1e-4, rtol=1e-4)
         toks.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_changes_no_token(folder_b, dtype):
+    """With async_scheduling the next decode step is queued before the host has read this
+    step's tokens.  Requests that end by an end-of-sequence token (one step too many is then in
+    flight and must be dropped), by length after 1, 2, 3 ... tokens, by an abort, and requests
+    that arrive in between: all end with the tokens of the synchronous engine."""
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, _ = folder_b
+    kw = dict(dtype=dtype, page_size=8, num_kvcache_slots=1024, max_model_len=128, seed=3)
+    prompts = [tu.random_prompt(384, n, 300 + n) for n in (3, 9, 14, 6, 11, 5)]
+
+    def run(async_scheduling, eos=None, abort_at=None):
+        llm = LLM(folder, async_scheduling=async_scheduling, **kw)
+        lens = [1, 2, 3, 17, 9, 12]
+        sps = [SamplingParams(temperature=0.8, top_p=0.95, max_tokens=n, ignore_eos=eos is None,
+                              eos_token_ids=eos) for n in lens]
+        got, steps, late = {}, 0, list(zip(prompts[4:], sps[4:]))
+        for p, sp in zip(prompts[:4], sps[:4]):
+            llm.add_request(p, sp)
+        aborted = None
+        while late or not llm.is_finished():
+            if steps in (3, 5) and late:               # arrivals while a step may be in flight
+                llm.add_request(*late.pop(0))
+            if abort_at is not None and steps == abort_at:
+                aborted = 3
+                assert llm.abort_request(3)
+            for o in llm.step()[0]:
+                got[o["seq_id"]] = (o["token_ids"], o["finish_reason"])
+            steps += 1
+            assert steps < 200
+        c = llm.runner.cache
+        assert c.free_pages() == c.groups[0].pool.num_pages
+        c.check()
+        assert (llm.steps_ahead > 5) == async_scheduling
+        return got, aborted
+
+    base, _ = run(False)
+    ahead, _ = run(True)
+    assert ahead == base and all(r == "length" for _, r in base.values())
+    # an end-of-sequence id that request 3 produces in the middle of its 17 tokens
+    eos = [base[3][0][6]]
+    base_eos, _ = run(False, eos=eos)
+    ahead_eos, _ = run(True, eos=eos)
+    assert ahead_eos == base_eos and base_eos[3][1] == "stop" and len(base_eos[3][0]) <= 7
+    base_ab, _ = run(False, abort_at=6)
+    ahead_ab, gone = run(True, abort_at=6)
+    assert gone == 3 and 3 not in ahead_ab and ahead_ab == base_ab
