@@ -245,8 +245,8 @@ def test_running_one_step_ahead_changes_no_token(folder_b, dtype):
     kw = dict(dtype=dtype, page_size=8, num_kvcache_slots=1024, max_model_len=128, seed=3)
     prompts = [tu.random_prompt(384, n, 300 + n) for n in (3, 9, 14, 6, 11, 5)]
 
-    def run(async_scheduling, eos=None, abort_at=None):
-        llm = LLM(folder, async_scheduling=async_scheduling, **kw)
+    def run(async_scheduling, eos=None, abort_at=None, **more):
+        llm = LLM(folder, async_scheduling=async_scheduling, **kw, **more)
         lens = [1, 2, 3, 17, 9, 12]
         sps = [SamplingParams(temperature=0.8, top_p=0.95, max_tokens=n, ignore_eos=eos is None,
                               eos_token_ids=eos) for n in lens]
@@ -273,6 +273,8 @@ def test_running_one_step_ahead_changes_no_token(folder_b, dtype):
     base, _ = run(False)
     ahead, _ = run(True)
     assert ahead == base and all(r == "length" for _, r in base.values())
+    # without decode graphs the tokens cannot stay on the device: the step is still queued ahead
+    assert run(True, decode_graph=False, validate_runtime_invariants=True)[0] == base
     # an end-of-sequence id that request 3 produces in the middle of its 17 tokens
     eos = [base[3][0][6]]
     base_eos, _ = run(False, eos=eos)
