@@ -22,6 +22,15 @@ DEV = "cuda:0"
 # ---- a mixer with state of its own: y_t = W · mean(x_0..x_t) ----------------------------
 
 @dataclass(frozen=True)
+class CompressedRotarySpec:
+    rotary_dim: int
+    theta: float
+    factor: float
+    amplitude: float
+    kind: str = "compressed_rotary"
+
+
+@dataclass(frozen=True)
 class RunningMeanSpec:
     kind: str = "running_mean"
     hidden_size: int = 0
@@ -57,6 +66,21 @@ def _register_toy():
 
     register_mixer("running_mean", RunningMean)
 
+    # another position encoding: rotary with compressed positions (every frequency divided by
+    # `factor`) and the rotated dims scaled by `amplitude`; the attention part only asks its
+    # position encoding for (frequencies, number of rotated dims, amplitude)
+    from sparseengine_b200.parts.base import PositionEncoding, register_position
+
+    class CompressedRotary(PositionEncoding):
+        graph_safe = True
+
+        def kernel_args(self, device):
+            r = self.spec.rotary_dim
+            inv = 1.0 / (self.spec.theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
+            return (inv / self.spec.factor).to(device), r, float(self.spec.amplitude)
+
+    register_position("compressed_rotary", CompressedRotary)
+
     @dataclass(frozen=True)
     class ToyConfig:
         raw: tuple
@@ -74,7 +98,8 @@ def _register_toy():
         norm = RMSNormSpec(size=h, eps=cfg.get("eps"))
         att = AttentionSpec(hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, scale=d ** -0.5,
                             qk_norm=None, window=cfg.get("window"),
-                            position=RotarySpec(rotary_dim=d, theta=cfg.get("theta")))
+                            position=CompressedRotarySpec(rotary_dim=d, theta=cfg.get("theta"), factor=cfg.get("factor"),
+                                                          amplitude=cfg.get("amplitude")))
         att_full = AttentionSpec(hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, scale=d ** -0.5,
                                  qk_norm=None, window=None, position=None)
         dense = DenseMLPSpec(hidden_size=h, intermediate_size=cfg.get("inter"))
@@ -110,7 +135,7 @@ def _register_toy():
 
 TOY = {"architectures": ["ToyForCausalLM"], "hidden_size": 40, "vocab_size": 131, "heads": 6, "kv_heads": 2,
        "head_dim": 16, "eps": 2e-6, "window": 5, "theta": 777.0, "inter": 24, "experts": 5, "top_k": 2,
-       "routed_scale": 1.7, "max_pos": 256}
+       "routed_scale": 1.7, "max_pos": 256, "factor": 4.0, "amplitude": 0.5}
 
 
 def toy_tensors(seed=3):
@@ -143,18 +168,25 @@ def toy_plain(t, tokens, act=torch.float32, forced=None):
     hq, hkv, d, inter = c["heads"], c["kv_heads"], c["head_dim"], c["inter"]
     pos = torch.arange(n)
 
+    def compressed_rotary(x):
+        inv = plain_m2.rope_inv_freq(d, c["theta"]) / c["factor"]
+        ang = pos.to(torch.float32).unsqueeze(-1) * inv
+        cos, sin = (torch.cos(ang) * c["amplitude"]).unsqueeze(1), (torch.sin(ang) * c["amplitude"]).unsqueeze(1)
+        x = x.to(torch.float32)
+        x1, x2 = x[..., :d // 2], x[..., d // 2:]
+        return torch.cat((plain_m2._round(x1 * cos - x2 * sin, act), plain_m2._round(x2 * cos + x1 * sin, act)), -1)
+
     def attention(x, l, window, rotate, kv=None):
         qkv = plain_m2.linear(x, t[l + "qkv"], act)
         q = qkv[:, :hq * d].view(n, hq, d)
+        rot = compressed_rotary if rotate else (lambda y: y)
         if kv is None:
             k = qkv[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
             v = qkv[:, (hq + hkv) * d:].view(n, hkv, d)
-            if rotate:
-                k = plain_m2.partial_rotary(k, pos, d, c["theta"], act)
+            k = rot(k)
         else:
             k, v = kv
-        if rotate:
-            q = plain_m2.partial_rotary(q, pos, d, c["theta"], act)
+        q = rot(q)
         o = plain_m2.causal_attention(q, k, v, act, window)
         return plain_m2.linear(o.reshape(n, hq * d), t[l + "o"], act), (k, v)
 
