@@ -14,7 +14,7 @@
 //
 // Rows are "sorted positions" p: the routing build sorts the (token, slot) assignments by
 // expert and lists tiles (expert, first row).  X for MODE_GATE_UP is the token rows
-// gathered into that order (se_moe_permute_rows).  Rounding points follow the reference's
+// gathered into that order (by the routing build, se_moe_route_gather).  Rounding points follow the reference's
 // bf16 pipeline (src/sparseengine/kernels/triton/moe.py:557-563,726-732,1374-1440).
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
@@ -465,14 +465,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     }
 }
 
-// out[p, :] = x[sorted[p] / top_k, :]  (activation rows gathered into expert order)
-__global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted,
-                                    __nv_bfloat16* __restrict__ out, int width, int top_k) {
-    const uint4* src = (const uint4*)(x + (size_t)(sorted[blockIdx.x] / top_k) * width);
-    uint4* dst = (uint4*)(out + (size_t)blockIdx.x * width);
-    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
-}
-
 // ---- host side ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -582,14 +574,6 @@ static int pick_stages(int na, int nt) {
 // multiples for TMA), else 0.
 extern "C" int se_gemm_tc_supported(int k_dim, int n_out, int nt) {
     return (k_dim % 8 == 0 && k_dim >= 8 && n_out >= 1 && (nt == 16 || nt == 32 || nt == 64 || nt == 128 || nt == 256)) ? 1 : 0;
-}
-
-extern "C" int se_moe_permute_rows(const void* x, const int* sorted, void* out, int rows, int width, int top_k,
-                                   cudaStream_t stream) {
-    if (rows <= 0) return 0;
-    if (width % 8) return SE_ERR_UNSUPPORTED;
-    permute_rows_kernel<<<rows, 128, 0, stream>>>((const __nv_bfloat16*)x, sorted, (__nv_bfloat16*)out, width, top_k);
-    SE_LAUNCH_CHECK();
 }
 
 // Grouped expert GEMM on tensor cores (bf16).

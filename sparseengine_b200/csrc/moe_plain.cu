@@ -46,18 +46,11 @@ __global__ void moe_count_rank_kernel(const int* __restrict__ ids, int assignmen
     }
 }
 
-// One block: exclusive scan of counts -> offsets[experts+1], tile list for rows-per-tile
-// `tile_rows`: tile_expert[i], tile_row0[i] (first sorted row), num_tiles[0].
-// All blocks: scatter sorted[offset[e] + rank[a]] = a, inv_pos[a] = that position.
-__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
-                                   const int* __restrict__ counts, int assignments, int experts, int tile_rows,
-                                   int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ inv_pos,
-                                   int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                   int* __restrict__ num_tiles) {
-    extern __shared__ int off[];   // experts + 1 row offsets, then experts + 1 tile offsets
-    int* toff = off + experts + 1;
+// Exclusive scans, by one whole block, of the rows per expert and of the tiles per expert
+// (tile_rows rows each) into off[experts + 1] and toff[experts + 1] (shared memory).
+__device__ __forceinline__ void scan_counts(const int* counts, int experts, int tile_rows, int* off, int* toff) {
     __shared__ int carry[2];
-    // Exclusive scans of the counts and of the tiles per expert, 256 experts at a time.
+    __shared__ int wsum[2][32];
     if (threadIdx.x == 0) carry[0] = carry[1] = 0;
     __syncthreads();
     for (int base = 0; base < experts; base += blockDim.x) {
@@ -72,7 +65,6 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
             const int uc = __shfl_up_sync(0xffffffffu, vc, o), ut = __shfl_up_sync(0xffffffffu, vt, o);
             if (lane >= o) { vc += uc; vt += ut; }
         }
-        __shared__ int wsum[2][32];
         if (lane == 31) { wsum[0][warp] = vc; wsum[1][warp] = vt; }
         __syncthreads();
         int pc = carry[0], pt = carry[1];
@@ -84,24 +76,107 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
     }
     if (threadIdx.x == 0) { off[experts] = carry[0]; toff[experts] = carry[1]; }
     __syncthreads();
-    if (blockIdx.x == 0) {
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-            const int first = toff[e], n = toff[e + 1] - first;
-            for (int i = 0; i < n; ++i) {
-                tile_expert[first + i] = e;
-                tile_row0[first + i] = off[e] + i * tile_rows;
-            }
+}
+
+// The tile list and the offsets, from the scans (one block writes them).
+__device__ __forceinline__ void write_tiles(const int* off, const int* toff, int experts, int tile_rows,
+                                            int* __restrict__ offsets, int* __restrict__ tile_expert,
+                                            int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int first = toff[e], n = toff[e + 1] - first;
+        for (int i = 0; i < n; ++i) {
+            tile_expert[first + i] = e;
+            tile_row0[first + i] = off[e] + i * tile_rows;
         }
-        if (threadIdx.x == 0) num_tiles[0] = toff[experts];
     }
-    __syncthreads();
-    if (blockIdx.x == 0)
-        for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = off[e];
+    if (threadIdx.x == 0) num_tiles[0] = toff[experts];
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = off[e];
+}
+
+// One block: exclusive scan of counts -> offsets[experts+1], tile list for rows-per-tile
+// `tile_rows`: tile_expert[i], tile_row0[i] (first sorted row), num_tiles[0].
+// All blocks: scatter sorted[offset[e] + rank[a]] = a, inv_pos[a] = that position.
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
+                                   const int* __restrict__ counts, int assignments, int experts, int tile_rows,
+                                   int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ inv_pos,
+                                   int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                   int* __restrict__ num_tiles) {
+    extern __shared__ int off[];   // experts + 1 row offsets, then experts + 1 tile offsets
+    int* toff = off + experts + 1;
+    scan_counts(counts, experts, tile_rows, off, toff);
+    if (blockIdx.x == 0) write_tiles(off, toff, experts, tile_rows, offsets, tile_expert, tile_row0, num_tiles);
     for (int a = blockIdx.x * blockDim.x + threadIdx.x; a < assignments; a += gridDim.x * blockDim.x) {
         const int p = off[ids[a]] + rank[a];
         sorted[p] = a;
         inv_pos[a] = p;
     }
+}
+
+// Few assignments (decode steps): the whole routing build in one launch, and with it the
+// gather of the activation rows into expert order that the tensor-core GEMM reads.  Every
+// block builds the same routing in its shared memory (thread e walks the assignments in
+// order and ranks those of expert e, so the order within an expert is the order of the
+// assignments, as above); block 0 writes the tables, and block b copies row b.  Beyond a few
+// hundred assignments the three kernels above are faster (measured at 512: every block's walk
+// over all assignments costs more than the launches it saves).
+constexpr int kRouteSmallAssignments = 256;
+constexpr int kRouteSmallExperts = 1024;
+
+__global__ void __launch_bounds__(256)
+moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts, int tile_rows, int top_k,
+                       int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
+                       int* __restrict__ inv_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                       int* __restrict__ num_tiles, const uint4* __restrict__ x, uint4* __restrict__ xs,
+                       int row_vecs) {
+    extern __shared__ int sm[];
+    int* ids_s = sm;                        // [assignments]
+    int* rank_s = ids_s + assignments;      // [assignments]
+    int* sorted_s = rank_s + assignments;   // [assignments]
+    int* cnt = sorted_s + assignments;      // [experts]
+    int* off = cnt + experts;               // [experts + 1]
+    int* toff = off + experts + 1;          // [experts + 1]
+    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+        ids_s[a] = ids[a];
+        sorted_s[a] = 0;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int c = 0;
+        for (int a = 0; a < assignments; ++a)
+            if (ids_s[a] == e) rank_s[a] = c++;
+        cnt[e] = c;
+    }
+    __syncthreads();
+    scan_counts(cnt, experts, tile_rows, off, toff);
+    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+        const int e = ids_s[a];
+        if ((unsigned)e >= (unsigned)experts) continue;      // not an expert: the caller's fault, nothing is read out of range
+        const int p = off[e] + rank_s[a];
+        sorted_s[p] = a;
+        if (blockIdx.x == 0) {
+            sorted[p] = a;
+            inv_pos[a] = p;
+        }
+    }
+    if (blockIdx.x == 0) {
+        write_tiles(off, toff, experts, tile_rows, offsets, tile_expert, tile_row0, num_tiles);
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = cnt[e];
+    }
+    if (x == nullptr) return;
+    __syncthreads();
+    for (int p = blockIdx.x; p < assignments; p += gridDim.x) {
+        const uint4* src = x + (size_t)(sorted_s[p] / top_k) * row_vecs;
+        uint4* dst = xs + (size_t)p * row_vecs;
+        for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// out[p, :] = x[sorted[p] / top_k, :] in 16-byte words (activation rows gathered into expert order)
+__global__ void gather_sorted_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted,
+                                          uint4* __restrict__ out, int row_vecs, int top_k) {
+    const uint4* src = x + (size_t)(sorted[blockIdx.x] / top_k) * row_vecs;
+    uint4* dst = out + (size_t)blockIdx.x * row_vecs;
+    for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) dst[i] = src[i];
 }
 
 // ---- grouped GEMM on CUDA cores ------------------------------------------------------
@@ -216,16 +291,52 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 
 }  // namespace se
 
-extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, int tile_rows, int* counts, int* rank,
-                                  int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
-                                  int* num_tiles, cudaStream_t stream) {
-    if (assignments <= 0) return 0;
-    if (tile_rows <= 0 || experts <= 0) return SE_ERR_ARGUMENT;
+static int launch_route_build(const int* ids, int assignments, int experts, int tile_rows, int* counts, int* rank,
+                              int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
+                              int* num_tiles, cudaStream_t stream) {
     se::moe_count_rank_kernel<<<experts, assignments > 2048 ? 1024 : 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
     se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
         ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
     SE_LAUNCH_CHECK();
+}
+
+// 1 if a routing build of this size is one launch (se_moe_route_gather then gathers the rows in it too).
+extern "C" int se_moe_route_is_small(int assignments, int experts) {
+    return assignments <= se::kRouteSmallAssignments && experts <= se::kRouteSmallExperts ? 1 : 0;
+}
+
+// The routing build and, if x is given, xs[p, :] = x[sorted[p] / top_k, :] (rows of row_bytes
+// bytes, a multiple of 16, both 16-byte aligned).
+extern "C" int se_moe_route_gather(const int* ids, int assignments, int experts, int tile_rows, int top_k, int* counts,
+                                   int* rank, int* offsets, int* sorted, int* inv_pos, int* tile_expert,
+                                   int* tile_row0, int* num_tiles, const void* x, void* xs, int row_bytes,
+                                   cudaStream_t stream) {
+    if (assignments <= 0) return 0;
+    if (tile_rows <= 0 || experts <= 0 || top_k <= 0) return SE_ERR_ARGUMENT;
+    if (x != nullptr && (row_bytes <= 0 || row_bytes % 16 || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15)))
+        return SE_ERR_UNSUPPORTED;
+    const int row_vecs = x != nullptr ? row_bytes / 16 : 0;
+    if (se_moe_route_is_small(assignments, experts)) {
+        const size_t smem = (size_t)(3 * assignments + 3 * experts + 2) * sizeof(int);
+        const int blocks = x != nullptr ? assignments : 1;
+        se::moe_route_small_kernel<<<blocks, 256, smem, stream>>>(
+            ids, assignments, experts, tile_rows, top_k, counts, offsets, sorted, inv_pos, tile_expert, tile_row0,
+            num_tiles, (const uint4*)x, (uint4*)xs, row_vecs);
+        SE_LAUNCH_CHECK();
+    }
+    const int rc = launch_route_build(ids, assignments, experts, tile_rows, counts, rank, offsets, sorted, inv_pos,
+                                      tile_expert, tile_row0, num_tiles, stream);
+    if (rc != 0 || x == nullptr) return rc;
+    se::gather_sorted_rows_kernel<<<assignments, 128, 0, stream>>>((const uint4*)x, sorted, (uint4*)xs, row_vecs, top_k);
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, int tile_rows, int* counts, int* rank,
+                                  int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
+                                  int* num_tiles, cudaStream_t stream) {
+    return se_moe_route_gather(ids, assignments, experts, tile_rows, 1, counts, rank, offsets, sorted, inv_pos,
+                               tile_expert, tile_row0, num_tiles, nullptr, nullptr, 0, stream);
 }
 
 extern "C" int se_moe_plain_tile_rows() { return se::kBM; }

@@ -26,7 +26,7 @@ _fns: dict = {}
 
 # Kernels launched through these bindings since the process started (a launcher that
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
-KERNELS_PER_CALL = {"se_moe_route_build": 2, "se_attn_decode": 2, "se_router": 2}   # upper bounds per call
+KERNELS_PER_CALL = {"se_attn_decode": 2, "se_router": 2}   # upper bounds per call
 launch_count = 0
 calls: dict = {}     # launcher name -> times called (tests check which kernels a path took)
 
@@ -197,14 +197,27 @@ def moe_plain_tile_rows() -> int:
     return int(f())
 
 
-def moe_route_build(ids, experts: int, tile_rows: int, ws: dict):
+def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None):
     """ws: int32 tensors counts[E], rank[A], offsets[E+1], sorted[A], inv_pos[A],
-    tile_expert[max_tiles], tile_row0[max_tiles], num_tiles[1]."""
+    tile_expert[max_tiles], tile_row0[max_tiles], num_tiles[1].
+    gather = (x [tokens, width], xs [A, width], top_k): also xs[p] = x[sorted[p] // top_k], the
+    activation rows in expert order (in the same launch when there are few assignments)."""
+    global launch_count
     assignments = ids.numel()
-    _check(_fn("se_moe_route_build", "piii" "pppppppp" "p")(
-        _ptr(ids, torch.int32, "ids"), assignments, experts, tile_rows,
+    x = xs = None
+    top_k = row_bytes = 1
+    if gather is not None:
+        x, xs, top_k = gather
+        if x.dtype != xs.dtype or x.shape[1] != xs.shape[1] or xs.shape[0] != assignments:
+            raise ValueError("gather: xs must be [assignments, width] of x's dtype")
+        row_bytes = x.shape[1] * x.element_size()
+    small = bool(library().se_moe_route_is_small(assignments, experts))
+    launch_count += (0 if small else 1) + (0 if small or gather is None else 1)
+    _check(_fn("se_moe_route_gather", "piiii" "pppppppp" "ppi" "p")(
+        _ptr(ids, torch.int32, "ids"), assignments, experts, tile_rows, top_k,
         *[_ptr(ws[k], torch.int32, k) for k in ("counts", "rank", "offsets", "sorted", "inv_pos", "tile_expert",
-                                                 "tile_row0", "num_tiles")], _stream()), "moe_route_build")
+                                                 "tile_row0", "num_tiles")],
+        _ptr(x, None, "x"), _ptr(xs, None, "xs"), row_bytes, _stream()), "moe_route_build")
 
 
 def moe_max_tiles(assignments: int, experts: int, tile_rows: int) -> int:
@@ -308,14 +321,6 @@ def moe_tile_rows_tc(assignments: int, experts: int) -> int:
     while nt < want and nt < 128:
         nt *= 2
     return nt
-
-
-def moe_permute_rows(x, sorted_rows, out, top_k: int):
-    rows, width = out.shape
-    _check(_fn("se_moe_permute_rows", "pppiiip")(
-        _ptr(x, torch.bfloat16, "x"), _ptr(sorted_rows, torch.int32, "sorted"), _ptr(out, torch.bfloat16, "out"),
-        rows, width, top_k, _stream()), "moe_permute_rows")
-    return out
 
 
 def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, nt):

@@ -45,12 +45,12 @@ class _RoutedSwiGLU(FeedForward):
               "offsets": torch.empty(self.num_experts + 1, **i32), "sorted": torch.empty(a, **i32),
               "inv_pos": torch.empty(a, **i32), "tile_expert": torch.empty(max_tiles, **i32),
               "tile_row0": torch.empty(max_tiles, **i32), "num_tiles": torch.empty(1, **i32)}
-        ops.moe_route_build(ids, self.num_experts, tile_rows, ws)
+        # the tensor-core GEMM reads the activation rows in expert order
+        xs = torch.empty(a, self.hidden, dtype=x.dtype, device=dev) if tc else None
+        ops.moe_route_build(ids, self.num_experts, tile_rows, ws, gather=(x, xs, self.top_k) if tc else None)
         act = torch.empty(a, self.inter, dtype=x.dtype, device=dev)
         y = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
         if tc:
-            xs = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
-            ops.moe_permute_rows(x, ws["sorted"], xs, self.top_k)
             ops.moe_grouped_gemm_tc(0, xs, self.w13, ws, None, act, experts=self.num_experts, max_tiles=max_tiles,
                                     n_out=self.inter, k_dim=self.hidden, nt=tile_rows)
             ops.moe_grouped_gemm_tc(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,

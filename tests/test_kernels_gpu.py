@@ -290,6 +290,55 @@ def test_router_tie_order_nan_and_softmax():
     torch.testing.assert_close(w.cpu(), 2.5 * p.gather(1, ids.cpu().long()), atol=1e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,top_k,experts,tile_rows,width", [
+    (1, 8, 256, 16, 3072), (8, 8, 256, 16, 3072), (37, 3, 6, 16, 40), (32, 8, 256, 32, 72),    # one launch
+    (33, 8, 256, 32, 72), (700, 2, 1030, 64, 8), (5, 4, 1025, 16, 24)])                        # three launches
+def test_routing_build_and_row_gather(dtype, tokens, top_k, experts, tile_rows, width):
+    """Assignments sorted by expert (stably), the tile list, and the activation rows gathered
+    into that order; few assignments take the single-launch kernel, the rest the three kernels."""
+    from sparseengine_b200.csrc import ops
+    g = torch.Generator().manual_seed(tokens + experts)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).int()
+    if tokens >= 8:
+        ids[: tokens // 2, 0] = 3          # one expert with many rows: several tiles
+    a = tokens * top_k
+    flat = ids.view(-1)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    max_tiles = ops.moe_max_tiles(a, experts, tile_rows)
+    ws = {"counts": torch.full((experts,), -7, **i32), "rank": torch.full((a,), -7, **i32),
+          "offsets": torch.full((experts + 1,), -7, **i32), "sorted": torch.full((a,), -7, **i32),
+          "inv_pos": torch.full((a,), -7, **i32), "tile_expert": torch.full((max_tiles,), -7, **i32),
+          "tile_row0": torch.full((max_tiles,), -7, **i32), "num_tiles": torch.full((1,), -7, **i32)}
+    x = rnd(tokens, width, dtype=dtype, seed=5)
+    xs = torch.zeros(a, width, dtype=dtype, device=DEV)
+    small = bool(ops.library().se_moe_route_is_small(a, experts))
+    assert small == (a <= 256 and experts <= 1024)
+    before = ops.launch_count
+    ops.moe_route_build(flat.contiguous().to(DEV), experts, tile_rows, ws, gather=(x, xs, top_k))
+    assert ops.launch_count - before == (1 if small else 3)
+    order = torch.sort(flat.long(), stable=True).indices
+    counts = torch.bincount(flat.long(), minlength=experts)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)])
+    assert torch.equal(ws["sorted"].cpu().long(), order)
+    assert torch.equal(ws["offsets"].cpu().long(), offsets)
+    assert torch.equal(ws["counts"].cpu().long(), counts)
+    inv = torch.empty(a, dtype=torch.long)
+    inv[order] = torch.arange(a)
+    assert torch.equal(ws["inv_pos"].cpu().long(), inv)
+    tiles = [(e, int(offsets[e]) + r) for e in range(experts) for r in range(0, int(counts[e]), tile_rows)]
+    n = int(ws["num_tiles"][0])
+    assert n == len(tiles) <= max_tiles
+    assert ws["tile_expert"][:n].tolist() == [t[0] for t in tiles]
+    assert ws["tile_row0"][:n].tolist() == [t[1] for t in tiles]
+    assert torch.equal(xs.cpu(), x.cpu()[order // top_k])
+    # without the gather: the same tables
+    ws2 = {k: torch.full_like(v, -7) for k, v in ws.items()}
+    ops.moe_route_build(flat.contiguous().to(DEV), experts, tile_rows, ws2)
+    for k in ("offsets", "sorted", "inv_pos", "num_tiles"):
+        assert torch.equal(ws2[k], ws[k]), k
+
+
 @pytest.mark.parametrize("path", ["cuda_cores", "tensor_cores"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,hidden,inter,experts,top_k", [
