@@ -96,7 +96,7 @@ def bench_experts(a, dev):
     ops.tc_check(dev)
     by = distinct * 3 * a.inter * a.hidden * 2
     fl = a.tokens * k * 3 * 2 * a.inter * a.hidden
-    return ms, by, fl, {"distinct_experts": distinct, "kernels": "route build, permute, gate/up+SwiGLU, down, combine"}
+    return ms, by, fl, {"distinct_experts": distinct, "kernels": "route build with row gather, gate/up+SwiGLU, down, combine"}
 
 
 def _filled_cache(a, dev, kv_lens):
