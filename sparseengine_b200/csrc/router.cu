@@ -269,19 +269,58 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
 }
 
 // Few tokens (decode): the latency of one warp walking a whole gate row dominates, so a
-// block of 8 warps takes 2 experts, 4 warps each on one quarter of the row.
+// block of 8 warps takes 2 experts, 4 warps each on one quarter of the row.  A lane's share
+// of the gate row (up to kGatePre 16-byte groups: widths up to 4096) is asked for before the
+// tokens are staged, so that the two trips to memory overlap; the sums are formed in the
+// order of quarter_dot.
+constexpr int kGatePre = 8;
+
 template <typename T>
 __global__ void router_logits_small_kernel(const T* __restrict__ x, const float* __restrict__ gate,
                                            float* __restrict__ logits, int tokens, int hidden, int experts) {
     extern __shared__ __align__(16) float xs[];              // [tokens <= kRouterTokens][hidden]
     __shared__ float part[kRouterWarps][kRouterTokens];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    load_tokens(x, xs, tokens * hidden);
-    __syncthreads();
     const int e = blockIdx.x * 2 + (warp >> 2), quarter = warp & 3;
     const float* g[1] = {gate + (size_t)min(e, experts - 1) * hidden};
+    const int n4 = hidden >> 2;
+    const int per = (n4 + 3) / 4, a = quarter * per, b = min(n4, a + per);
+    const bool pre = (hidden & 3) == 0 && per <= 32 * kGatePre;
+    float4 gv[kGatePre];
+    if (pre) {
+#pragma unroll
+        for (int u = 0; u < kGatePre; ++u) {
+            const int i = a + lane + 32 * u;
+            if (i < b) gv[u] = __ldg(reinterpret_cast<const float4*>(g[0]) + i);
+        }
+    }
+    load_tokens(x, xs, tokens * hidden);
+    __syncthreads();
     float acc[kRouterTokens][1];
-    quarter_dot<kRouterTokens, 1>(xs, hidden, tokens, g, quarter, lane, acc);
+    if (pre) {
+#pragma unroll
+        for (int j = 0; j < kRouterTokens; ++j) acc[j][0] = 0.f;
+#pragma unroll
+        for (int u = 0; u < kGatePre; ++u) {
+            const int i = a + lane + 32 * u;
+            if (i < b) {
+#pragma unroll
+                for (int j = 0; j < kRouterTokens; ++j) {
+                    if (j < tokens) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xs + j * hidden + 4 * i);
+                        acc[j][0] = fmaf(xv.x, gv[u].x, acc[j][0]);
+                        acc[j][0] = fmaf(xv.y, gv[u].y, acc[j][0]);
+                        acc[j][0] = fmaf(xv.z, gv[u].z, acc[j][0]);
+                        acc[j][0] = fmaf(xv.w, gv[u].w, acc[j][0]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kRouterTokens; ++j) acc[j][0] = warp_sum(acc[j][0]);
+    } else {
+        quarter_dot<kRouterTokens, 1>(xs, hidden, tokens, g, quarter, lane, acc);
+    }
     if (lane == 0)
 #pragma unroll
         for (int j = 0; j < kRouterTokens; ++j) part[warp][j] = acc[j][0];
@@ -305,6 +344,7 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     float* pj = sel;                     // [experts] probabilities
     float* sj = pj + padded;             // [experts] selection scores (16-byte aligned)
     int* ranks = (int*)(sj + padded);    // [experts]
+    float* w_s = (float*)(ranks + padded);   // [top_k] probabilities of the chosen, in slot order
     __shared__ float red[33];
     __shared__ float thr_s;
     const int t = blockIdx.x;
@@ -321,14 +361,20 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
         float sum = 0.f;
         for (int e = threadIdx.x; e < experts; e += blockDim.x) sum += expf(lg[e] - mx);
         sum = block_sum(sum, red);
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) pj[e] = expf(lg[e] - mx) / sum;
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+            const float pe = expf(lg[e] - mx) / sum;
+            const float s = pe + (bias ? bias[e] : 0.f);
+            pj[e] = pe;
+            sj[e] = (s == s) ? s : INFINITY;
+        }
     } else {
-        for (int e = threadIdx.x; e < experts; e += blockDim.x) pj[e] = 1.f / (1.f + expf(-lg[e]));
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        const float s = pj[e] + (bias ? bias[e] : 0.f);
-        sj[e] = (s == s) ? s : INFINITY;
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) {     // logit and bias: one trip to memory
+            const float l = lg[e], bv = bias ? bias[e] : 0.f;
+            const float pe = 1.f / (1.f + expf(-l));
+            const float s = pe + bv;
+            pj[e] = pe;
+            sj[e] = (s == s) ? s : INFINITY;
+        }
     }
     __syncthreads();
     // rank of e = number of experts that precede it in (score descending, index ascending);
@@ -377,19 +423,18 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
         if (chosen) {
             const int slot = gr ? pg : n_greater + pt;
             ids[(size_t)t * top_k + slot] = e;
-            weights[(size_t)t * top_k + slot] = pj[e];
+            w_s[slot] = pj[e];
         }
         __syncthreads();
         if (threadIdx.x == 0)
             for (int w = 0; w < nwarps; ++w) { run[0] += wcount[0][w]; run[1] += wcount[1][w]; }
         __syncthreads();
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float* w = weights + (size_t)t * top_k;
+    // every writer adds the chosen probabilities in slot order, as one thread would
+    for (int k = threadIdx.x; k < top_k; k += blockDim.x) {
         float sum = 0.f;
-        for (int s = 0; s < top_k; ++s) sum += w[s];
-        for (int s = 0; s < top_k; ++s) w[s] = (renormalize ? w[s] / sum : w[s]) * routed_scale;
+        for (int s = 0; s < top_k; ++s) sum += w_s[s];
+        weights[(size_t)t * top_k + k] = (renormalize ? w_s[k] / sum : w_s[k]) * routed_scale;
     }
 }
 
@@ -482,7 +527,7 @@ router_select_warp_kernel(const float* __restrict__ logits, const float* __restr
 // impl: 0 = by sizes, 1 = the block-per-token kernel, 2 = the warp-per-token kernel
 static int launch_select(const float* logits, const float* bias, int* ids, float* weights, int tokens, int experts,
                          int top_k, int score_fn, int renormalize, float routed_scale, int impl, cudaStream_t stream) {
-    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 3 * sizeof(float);
+    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
     const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256;
     if (impl == 2 && !warp_ok) return SE_ERR_UNSUPPORTED;
     if (smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
@@ -519,7 +564,7 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
     if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
     const int tile_tokens = tokens < se::kRouterTokens ? tokens : se::kRouterTokens;
     const size_t smem = (size_t)tile_tokens * hidden * sizeof(float);
-    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 3 * sizeof(float);
+    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
     if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
     SE_DISPATCH_DTYPE(dtype, T, {
         if (tokens <= se::kRouterTokens) {
