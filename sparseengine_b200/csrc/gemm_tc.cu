@@ -200,6 +200,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ float route_s[2][256];
+    __shared__ int valid_s[kSchedSlots];     // activation rows of the loader's last items (see the MMA thread)
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kMaxStages]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * kMaxStages]), acc_empty0 = smem_u32(&bars[2 * kMaxStages + 2]);
     const uint32_t sched_full0 = smem_u32(&bars[2 * kMaxStages + 4]);
@@ -262,10 +263,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             int it = 0;
             bool ok = true;
             int asked = 0;          // requests made so far
-            int expert = 0, row0 = by * nt;
+            int used = 0;           // items with work so far
+            int expert = 0, row0 = by * nt, row_end = p.total_rows;
             if (p.tile_expert != nullptr && by < tiles) {
                 expert = p.tile_expert[by];
                 row0 = p.tile_row0[by];
+                row_end = p.offsets[expert + 1];
             }
             for (int j = 0; ok; ++j) {
                 // ask for the item after this one; the answer comes while this item streams
@@ -284,7 +287,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 // the ring is full), and the next tile's expert and first row are fetched then,
                 // so the first copies of the next item do not wait for them.
                 bool answered = false, more = false;
-                int expert_next = 0, row0_next = 0;
+                int expert_next = 0, row0_next = 0, row_end_next = p.total_rows;
                 auto read_answer = [&]() {
                     answered = true;
                     more = next_item(j, 0);
@@ -292,9 +295,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     if (more && p.tile_expert != nullptr && by < tiles) {
                         expert_next = p.tile_expert[by];
                         row0_next = p.tile_row0[by];
+                        row_end_next = p.offsets[expert_next + 1];
                     }
                 };
                 if (tile < tiles) {
+                    // the item's activation rows, for the MMA thread: written before this item's first
+                    // arrival on a `full` barrier, which the MMA thread waits for before it reads it
+                    valid_s[used % kSchedSlots] = min(nt, row_end - row0);
+                    ++used;
                     const int wy = expert * p.w_rows_per_expert + n0;
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         if (kb == num_kb / 2) {
@@ -323,6 +331,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 if (!ok || !more) break;
                 expert = expert_next;
                 row0 = row0_next;
+                row_end = row_end_next;
             }
             if (abort_s) {
                 // let what is still in flight land before the CTA's shared memory goes away:
@@ -341,7 +350,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(nt);
+            // An item whose tile holds fewer rows than nt (the last tile of an expert) runs MMAs of
+            // just those rows, rounded up to 16: N is a field of the instruction descriptor.
+            uint32_t idesc = instr_desc(nt);
             int it = 0, used = 0;       // used: items that took an accumulator buffer
             bool ok = true;
             for (int j = 0; ok; ++j) {
@@ -364,6 +375,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                             break;
                         }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        if (kb == 0) idesc = instr_desc(max(16, (valid_s[used % kSchedSlots] + 15) & ~15));
                         const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
                         const uint64_t da = smem_desc(a), db = smem_desc(a + NA * kTileABytes);
 #pragma unroll

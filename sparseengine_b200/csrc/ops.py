@@ -307,18 +307,19 @@ def gemm_tc_supported(k_dim: int, n_out: int, nt: int = 16) -> bool:
 
 
 def moe_tile_rows_tc(assignments: int, experts: int) -> int:
-    """Activation rows per tile for the tensor-core grouped GEMM: about twice the mean
-    number of rows per expert, a power of two in [16, 128]; 256 once the mean reaches 192 rows
-    (an expert's weights then cross from L2 to an SM once per 256 rows instead of once per 128,
-    which is what bounds the GEMM when it is no longer bound by HBM)."""
+    """Activation rows per tile for the tensor-core grouped GEMM: the power of two in [16, 256]
+    that is at least 4/3 of the mean number of rows per expert.  A tile that holds fewer rows
+    (an expert's last one) runs MMAs of its own rows only, so a large tile wastes no tensor
+    work; what a tile size costs is shared memory per stage, what it saves is that an expert's
+    weights cross from L2 to an SM once per tile.  Measured at M2 sizes over 256 experts
+    (expert layer, ms, best first): 512 tokens 32 > 64 > 16; 1,024 and 1,536 tokens 64 > 32, 128;
+    3,072 tokens 128 > 256 > 64; 4,096 tokens and more 256 > 128."""
     forced = os.environ.get("SE_MOE_TILE_ROWS")          # tuning aid
     if forced:
         return int(forced)
-    want = max(1, -(-2 * assignments // max(experts, 1)))
-    if want >= 384:
-        return 256
+    want = -(-4 * assignments // (3 * max(experts, 1)))
     nt = 16
-    while nt < want and nt < 128:
+    while nt < want and nt < 256:
         nt *= 2
     return nt
 
