@@ -231,15 +231,25 @@ def run_ours(args) -> dict:
         runner.release(f"p{i}")
     pms = min(pre_ms[1:])
     flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
-    # With 2,048 tokens over top-k of many experts, every expert's weights are still read once
-    # per layer, which bounds this prefill by HBM rather than by the tensor cores: hbm_frac is
-    # the bytes it has to read (all weights once, the prompt's K/V once) over time and peak.
-    experts = cfg.get("num_local_experts", 0)
-    pre_bytes = (args.layers * (mb["dense_layer"] + experts * mb["expert"] + PROMPT_LEN * mb["kv_token_layer"])
+    # hbm_frac: the bytes this prefill has to read (the weights of the experts it touches, counted
+    # on one more step, and the dense weights once; the prompt's K/V once) over time and peak.
+    # With random weights the deeper layers route most tokens to the same experts, so the step
+    # touches far fewer than all experts; evenly routed it would be bound by reading them all.
+    ffs = [b_.feed_forward for b_ in runner.model.blocks]
+    for f in ffs:
+        f.capture = []
+    runner.admit("pc")
+    runner.step([StepEntry("pc", prompt, [PROMPT_LEN - 1])])
+    runner.release("pc")
+    touched = [len(set(torch.cat([c.view(-1) for c in f.capture]).tolist())) if f.capture else 0 for f in ffs]
+    for f in ffs:
+        f.capture = None
+    pre_bytes = (args.layers * (mb["dense_layer"] + PROMPT_LEN * mb["kv_token_layer"]) + sum(touched) * mb["expert"]
                  + mb["lm_head"])
     prefill = {"value": round(PROMPT_LEN * 1000.0 / pms, 1), "tokens": PROMPT_LEN, "ms": round(pms, 3),
                "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
-               "hbm_frac": round(pre_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+               "hbm_frac": round(pre_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+               "distinct_experts_per_layer": round(sum(touched) / max(len(touched), 1), 1)}
 
     # ---- an extra point: four such prompts in one step (8,192 tokens: towards compute-bound) ----
     prompts4 = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(4)]
