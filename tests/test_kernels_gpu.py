@@ -343,7 +343,7 @@ def test_routing_build_and_row_gather(dtype, tokens, top_k, experts, tile_rows, 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,hidden,inter,experts,top_k", [
     (5, 64, 32, 4, 2), (70, 96, 48, 8, 3), (33, 80, 40, 6, 4), (130, 200, 72, 16, 5), (1, 64, 32, 4, 2),
-    (300, 264, 136, 3, 2)])
+    (300, 264, 136, 3, 2), (150, 264, 136, 4, 2)])      # the last two: tiles of 256 and of 128 rows
 def test_routed_experts(dtype, tokens, hidden, inter, experts, top_k, path):
     """Grouped gate/up + SwiGLU, grouped down x routing weight and the combine, on CUDA cores
     (any dtype) and on tensor cores (bfloat16: TMA + tcgen05), against the plain loop."""
@@ -436,7 +436,7 @@ def test_penalties():
     assert logits.cpu().tolist() == [[0.5, -4.5, 1.0, 0.5], [1.0, -2.0, 3.0, 0.25]]
 
 
-@pytest.mark.parametrize("tokens", [1, 8, 64, 700])
+@pytest.mark.parametrize("tokens", [1, 8, 64, 700, 2500, 4100])      # tiles of 16, 16, 16, 32, 128 and 256 rows
 def test_tensor_core_experts_at_m2_layer_sizes(tokens):
     """256 experts, top-8, width 3072, expert width 1536: the tensor-core path against the
     CUDA-core path of the same engine (the plain loop on a CPU would take minutes)."""
