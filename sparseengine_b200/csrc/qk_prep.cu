@@ -121,42 +121,48 @@ qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T
                    const int* __restrict__ table, int table_stride, T* __restrict__ cache, T* __restrict__ q_out,
                    int hq, int hkv, int d, int rot, float eps, float rope_scale, int page_size, int write_cache) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
+    __shared__ float scratch[33];
     const int t = blockIdx.x;
     const int qn = hq * d, kn = hkv * d;
     const T* row = qkv + (size_t)t * (qn + 2 * kn);
+    // The trips to memory that depend on one another (position and request -> table row -> page)
+    // are started first and used last, so that they overlap the loads of the statistics.
     const int pos = positions[t];
+    const int ts = write_cache ? token_seq[t] : 0;
     const int half = rot / 2;
+    // statistics of the whole q and k projections of this token (the row is re-read from L1/L2 below)
+    float ss_q = 0.f, ss_k = 0.f;
+    if (q_w != nullptr) {
+        for (int i = threadIdx.x * 8; i < qn; i += blockDim.x * 8) {
+            float v[8];
+            load8(row + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss_q += v[j] * v[j];
+        }
+        for (int i = threadIdx.x * 8; i < kn; i += blockDim.x * 8) {
+            float v[8];
+            load8(row + qn + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss_k += v[j] * v[j];
+        }
+    }
+    const int table_row = write_cache ? seq_rows[ts] : 0;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         float s, c;
         sincosf((float)pos * inv_freq[j], &s, &c);
         cs[j] = c * rope_scale;
         cs[half + j] = s * rope_scale;
     }
-    __syncthreads();
-    // statistics of the whole q and k projections of this token (the row is re-read from L1/L2 below)
+    const int page = write_cache ? table[(size_t)table_row * table_stride + pos / page_size] : 0;
     float inv_q = 1.f, inv_k = 1.f;
     if (q_w != nullptr) {
-        __shared__ float scratch[33];
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-            const T* part = row + (which ? qn : 0);
-            const int n = which ? kn : qn;
-            float ss = 0.f;
-            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
-                float v[8];
-                load8(part + i, v);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-            }
-            ss = block_sum(ss, scratch);
-            (which ? inv_k : inv_q) = 1.0f / sqrtf(ss / (float)n + eps);
-        }
+        inv_q = 1.0f / sqrtf(block_sum(ss_q, scratch) / (float)qn + eps);
+        inv_k = 1.0f / sqrtf(block_sum(ss_k, scratch) / (float)kn + eps);
     }
+    __syncthreads();                       // cos/sin are in shared memory
     T* kv_base = nullptr;
-    if (write_cache) {
-        const int page = table[(size_t)seq_rows[token_seq[t]] * table_stride + pos / page_size];
+    if (write_cache)
         kv_base = cache + (size_t)page * 2 * hkv * page_size * d + (size_t)(pos % page_size) * d;
-    }
     const int groups = d / 8, rot_groups = half / 8;
     const int live = groups - rot_groups;                  // items per head: rotated pairs, then pass-through groups
     const int qk_heads = hq + (write_cache ? hkv : 0);
