@@ -107,7 +107,7 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
 
 // Many tokens: a block of 8 warps takes 32 tokens x 16 experts; warp w owns the 8 x 8
 // sub-tile (tokens 8*(w/2).., experts 8*(w%2)..) with 64 accumulators per lane.  The token
-// and gate rows are staged through shared memory in chunks of 32 16-byte groups, which are
+// and gate rows are staged through shared memory (two buffers) in chunks of 32 16-byte groups, which are
 // exactly the groups the 32 lanes take in one step of the fixed summation order (see
 // quarter_dot), so every (token, expert, quarter, lane) partial sum is accumulated in the
 // same order as in the other kernels; quarters are reduced by the same butterfly and
@@ -120,6 +120,7 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
 // 16-byte group -- so that one 16-byte shared-memory load yields two packed operands.  Every
 // accumulator still sees its four products per group in the order x, y, z, w.
 constexpr int kBigTokens = 32, kBigExperts = 16;
+constexpr int kBigBufs = 2;        // staging buffers: chunk g + 1 is written while chunk g is read, one barrier per chunk
 
 __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
     unsigned long long d;
@@ -163,8 +164,8 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
                            int tokens, int hidden, int experts) {
     extern __shared__ __align__(16) float tiled_smem[];
     float (*xs)[kBigTokens][128] = reinterpret_cast<float (*)[kBigTokens][128]>(tiled_smem);
-    float (*gs)[kBigExperts][128] = reinterpret_cast<float (*)[kBigExperts][128]>(tiled_smem + 2 * kBigTokens * 128);
-    float (*qsum)[4][64] = reinterpret_cast<float (*)[4][64]>(tiled_smem + 2 * (kBigTokens + kBigExperts) * 128);
+    float (*gs)[kBigExperts][128] = reinterpret_cast<float (*)[kBigExperts][128]>(tiled_smem + kBigBufs * kBigTokens * 128);
+    float (*qsum)[4][64] = reinterpret_cast<float (*)[4][64]>(tiled_smem + kBigBufs * (kBigTokens + kBigExperts) * 128);
     const int t0 = blockIdx.x * kBigTokens, e0 = blockIdx.y * kBigExperts;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wt = (warp >> 1) * 8, we = (warp & 1) * 8;
@@ -197,68 +198,81 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
         *reinterpret_cast<float4*>(&gs[buf][2 * warp + 1][4 * lane]) = make_float4(gr[0].z, gr[1].z, gr[0].w, gr[1].w);
     };
 
-    for (int quarter = 0; quarter < 4; ++quarter) {
+    // The chunks of the four quarters form one stream of 4 * cpq chunks, so that the staging runs
+    // ahead across the quarters' ends too (the last chunks of a short quarter are empty).  Chunk
+    // g + 1 is written to its buffer and chunk g + 2 is asked for before chunk g is used.
+    const int cpq = (per + 31) / 32, total = 4 * cpq;
+    auto fetch_chunk = [&](int g) {
+        const int qa = (g / cpq) * per;
+        fetch(qa + 32 * (g % cpq), min(n4, qa + per));
+    };
+    unsigned long long acc2[8][4];               // [token][expert pair]: the sums for experts we + 2p and we + 2p + 1
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int p = 0; p < 4; ++p) acc2[i][p] = 0ull;
+    fetch_chunk(0);
+    stash(0);
+    if (total > 1) fetch_chunk(1);
+    __syncthreads();
+    for (int g = 0; g < total; ++g) {
+        const int buf = g % kBigBufs;
+        const int quarter = g / cpq, c = g % cpq;
         const int a = quarter * per, b = min(n4, a + per);
-        const int chunks = a < b ? (b - a + 31) / 32 : 0;
-        unsigned long long acc2[8][4];           // [token][expert pair]: the sums for experts we + 2p and we + 2p + 1
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int p = 0; p < 4; ++p) acc2[i][p] = 0ull;
-        if (chunks > 0) fetch(a, b);
-        for (int c = 0; c < chunks; ++c) {
-            const int buf = c & 1;
-            stash(buf);
-            __syncthreads();
-            if (c + 1 < chunks) fetch(a + 32 * (c + 1), b);
-            if (a + 32 * c + lane < b) {         // lanes past the quarter's end add nothing (as in quarter_dot)
-                unsigned long long gxy[4][2], gzw[4][2];
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const float4 ga = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p][4 * lane]);
-                    const float4 gb = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p + 1][4 * lane]);
-                    gxy[p][0] = pair2(ga.x, ga.y);
-                    gxy[p][1] = pair2(ga.z, ga.w);
-                    gzw[p][0] = pair2(gb.x, gb.y);
-                    gzw[p][1] = pair2(gb.z, gb.w);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][wt + i][4 * lane]);
-                    const unsigned long long xx = dup2(xv.x), xy = dup2(xv.y), xz = dup2(xv.z), xw = dup2(xv.w);
-#pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        acc2[i][p] = fma2(xx, gxy[p][0], acc2[i][p]);
-                        acc2[i][p] = fma2(xy, gxy[p][1], acc2[i][p]);
-                        acc2[i][p] = fma2(xz, gzw[p][0], acc2[i][p]);
-                        acc2[i][p] = fma2(xw, gzw[p][1], acc2[i][p]);
-                    }
-                }
-            }
-            // the buffer written two chunks ahead is this one: everyone must be done reading it
-            if (c + 2 < chunks) __syncthreads();
-        }
-        float acc[8][8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
+        if (g + 1 < total) stash((g + 1) % kBigBufs);
+        if (g + 2 < total) fetch_chunk(g + 2);
+        if (a + 32 * c + lane < b) {             // lanes past the quarter's end add nothing (as in quarter_dot)
+            unsigned long long gxy[4][2], gzw[4][2];
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                acc[i][2 * p] = __uint_as_float((unsigned)(acc2[i][p] & 0xffffffffull));
-                acc[i][2 * p + 1] = __uint_as_float((unsigned)(acc2[i][p] >> 32));
+                const float4 ga = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p][4 * lane]);
+                const float4 gb = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p + 1][4 * lane]);
+                gxy[p][0] = pair2(ga.x, ga.y);
+                gxy[p][1] = pair2(ga.z, ga.w);
+                gzw[p][0] = pair2(gb.x, gb.y);
+                gzw[p][1] = pair2(gb.z, gb.w);
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][wt + i][4 * lane]);
+                const unsigned long long xx = dup2(xv.x), xy = dup2(xv.y), xz = dup2(xv.z), xw = dup2(xv.w);
+                // four independent accumulators between the dependent steps of each one
+#pragma unroll
+                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xx, gxy[p][0], acc2[i][p]);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xy, gxy[p][1], acc2[i][p]);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xz, gzw[p][0], acc2[i][p]);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xw, gzw[p][1], acc2[i][p]);
+            }
+        }
+        if (c == cpq - 1) {                      // the quarter is complete
+            float acc[8][8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    acc[i][2 * p] = __uint_as_float((unsigned)(acc2[i][p] & 0xffffffffull));
+                    acc[i][2 * p + 1] = __uint_as_float((unsigned)(acc2[i][p] >> 32));
+                    acc2[i][p] = 0ull;
+                }
+            // 64 sums over the lanes at once: each step halves the values a lane holds and adds
+            // the partner's copy of the half it keeps.  The pairs are those of warp_sum (lanes
+            // l and l ^ 16, then ^ 8, 4, 2, 1) and a + b = b + a, so every total has warp_sum's
+            // bits; lane l ends with the totals of values 2l and 2l + 1.
+            float* v = &acc[0][0];
+            halve_over_lanes<64, 16>(v, lane);
+            halve_over_lanes<32, 8>(v, lane);
+            halve_over_lanes<16, 4>(v, lane);
+            halve_over_lanes<8, 2>(v, lane);
+            halve_over_lanes<4, 1>(v, lane);
+            qsum[warp][quarter][2 * lane] = v[0];
+            qsum[warp][quarter][2 * lane + 1] = v[1];
+        }
+        // chunk g + 1 is in its buffer for everyone, and everyone is done with chunk g - 1's buffer,
+        // which the next iteration writes
         __syncthreads();
-        // 64 sums over the lanes at once: each step halves the values a lane holds and adds
-        // the partner's copy of the half it keeps.  The pairs are those of warp_sum (lanes
-        // l and l ^ 16, then ^ 8, 4, 2, 1) and a + b = b + a, so every total has warp_sum's
-        // bits; lane l ends with the totals of values 2l and 2l + 1.
-        float* v = &acc[0][0];
-        halve_over_lanes<64, 16>(v, lane);
-        halve_over_lanes<32, 8>(v, lane);
-        halve_over_lanes<16, 4>(v, lane);
-        halve_over_lanes<8, 2>(v, lane);
-        halve_over_lanes<4, 1>(v, lane);
-        qsum[warp][quarter][2 * lane] = v[0];
-        qsum[warp][quarter][2 * lane + 1] = v[1];
     }
     __syncwarp();
     for (int o = lane; o < 64; o += 32) {
@@ -577,7 +591,7 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                 (const T*)x, gate, logits, tokens, hidden, experts);
         } else if ((hidden & 3) == 0) {
             dim3 grid(se::ceil_div(tokens, se::kBigTokens), se::ceil_div(experts, se::kBigExperts));
-            const int tiled_smem = (2 * (se::kBigTokens + se::kBigExperts) * 128 + 8 * 4 * 64) * (int)sizeof(float);
+            const int tiled_smem = (se::kBigBufs * (se::kBigTokens + se::kBigExperts) * 128 + 8 * 4 * 64) * (int)sizeof(float);
             cudaError_t e = cudaFuncSetAttribute(se::router_logits_tiled_kernel<T>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tiled_smem);
             if (e != cudaSuccess) return (int)e;
