@@ -117,6 +117,32 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", list(ACT))
+@pytest.mark.parametrize("name", ["A", "D"])
+@pytest.mark.parametrize("seed", [3, 11, 12])
+def test_random_schedules_give_the_plain_logits(folders, name, dtype, seed):
+    """Random request lengths, random cuts, random subsets of the live requests in a step and
+    random places asked for, with a pool exactly as large as the schedule needs."""
+    folder, tensors = folders[name, dtype]
+    rng = np.random.RandomState(seed)
+    vocab = tu.TINY[name][0]["vocab_size"]
+    lens = [int(x) for x in rng.randint(2, 160, size=rng.randint(4, 9))]
+    seqs = {f"s{i}": tu.random_prompt(vocab, n, 31 * seed + i) for i, n in enumerate(lens)}
+    steps = tu.trace_random(seqs, seed)
+    runner = runner_for(folder, name, dtype, steps)
+    routed = None
+    if dtype == "bfloat16":
+        got, routed = tu.run_trace_runner(runner, steps, capture=True)
+    else:
+        got = tu.run_trace_runner(runner, steps)
+    assert len(got) == sum(len(e["want"]) for s in steps for e in s["entries"])
+    ref = reference(name, dtype, tensors, seqs, routed)
+    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} random schedule {seed}")
+    pool = runner.cache.groups[0].pool
+    assert pool.free == pool.num_pages
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", list(ACT))
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_long_portions_through_the_tensor_core_attention(folders, name, dtype):
     """Portions of more than 512 tokens take the prompt-portion attention kernels (tcgen05 for

@@ -125,6 +125,47 @@ def trace_mixed(seqs: dict, live: int = 4, chunk: int = 6, decode_tail: int = 5,
     return steps
 
 
+def trace_random(seqs: dict, seed: int, live: int = 4) -> list:
+    """A random schedule: requests start at random times (up to ``live`` at once), every step
+    takes a random subset of them, each with one token, a few, or dozens (cut anywhere), and asks
+    for the logits at all, some or none of them (the last token of a request is always asked
+    for)."""
+    rng = np.random.RandomState(seed)
+    waiting = list(seqs.items())
+    active: dict = {}
+    steps = []
+    n = 0
+    while waiting or active:
+        while waiting and len(active) < live and (not active or rng.rand() < 0.7):
+            sid, toks = waiting.pop(0)
+            active[sid] = [toks, 0]
+        entries, end = [], []
+        ids = list(active)
+        for sid in ids:
+            toks, a = active[sid]
+            if len(ids) > 1 and rng.rand() < 0.25:
+                continue
+            kind = rng.rand()
+            size = 1 if kind < 0.4 else int(rng.randint(2, 9)) if kind < 0.8 else int(rng.randint(9, 70))
+            b = a + min(size, len(toks) - a)
+            m = b - a
+            pick = rng.rand()
+            want = [] if pick < 0.15 else list(range(m)) if pick < 0.6 else sorted(
+                set(int(x) for x in rng.randint(0, m, size=max(1, m // 2))))
+            if b == len(toks) and (m - 1) not in want:
+                want.append(m - 1)
+            entries.append({"id": sid, "tokens": toks[a:b], "want": want})
+            active[sid][1] = b
+            if b == len(toks):
+                end.append(sid)
+        for sid in end:
+            del active[sid]
+        if entries:
+            steps.append({"step": n, "entries": entries, "end": end})
+            n += 1
+    return steps
+
+
 def max_live_tokens(steps, round_to: int = 64) -> int:
     """The --max-tokens a trace needs: the most tokens live requests hold at any time,
     each request's count rounded up to ``round_to``."""
