@@ -108,7 +108,7 @@ extern "C" int se_rmsnorm(const void* x, const void* residual, const void* w, vo
     if (smem > 200 * 1024) return SE_ERR_UNSUPPORTED;
     const int threads = hidden >= 8192 ? 512 : hidden >= 2048 ? 256 : 128;
     SE_DISPATCH_DTYPE(dtype, T, {
-        if (smem > 48 * 1024) {
+        if (smem > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
             cudaError_t e = cudaFuncSetAttribute(se::rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }

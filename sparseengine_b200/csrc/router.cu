@@ -552,7 +552,7 @@ static int launch_select(const float* logits, const float* bias, int* ids, float
             logits, bias, ids, weights, tokens, experts, top_k, renormalize, routed_scale);
         SE_LAUNCH_CHECK();
     }
-    if (smem_sel > 48 * 1024) {
+    if (smem_sel > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
         cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);
         if (e != cudaSuccess) return (int)e;
     }
@@ -582,7 +582,7 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
     if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
     SE_DISPATCH_DTYPE(dtype, T, {
         if (tokens <= se::kRouterTokens) {
-            if (smem > 48 * 1024) {
+            if (smem > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
                 cudaError_t e = cudaFuncSetAttribute(se::router_logits_small_kernel<T>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
@@ -598,7 +598,7 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
             se::router_logits_tiled_kernel<T><<<grid, 256, tiled_smem, stream>>>((const T*)x, gate, logits, tokens, hidden,
                                                                                   experts);
         } else {
-            if (smem > 48 * 1024) {
+            if (smem > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
                 cudaError_t e = cudaFuncSetAttribute(se::router_logits_kernel<T>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;

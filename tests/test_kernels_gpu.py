@@ -39,7 +39,8 @@ def test_embed_and_gather(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,hidden,eps", [(1, 64, 1e-6), (7, 3072, 1e-5), (33, 1000, 1e-6), (3, 20000, 1e-6)])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 64, 1e-6), (7, 3072, 1e-5), (33, 1000, 1e-6), (3, 20000, 1e-6),
+                                             (2, 12288, 1e-6)])      # the last: a row of exactly 48 KB
 def test_rmsnorm_with_and_without_residual(dtype, rows, hidden, eps):
     from sparseengine_b200.csrc import ops
     x, r = rnd(rows, hidden, dtype=dtype, seed=1), rnd(rows, hidden, dtype=dtype, scale=3.0, seed=2)
@@ -187,7 +188,8 @@ def test_attention_finds_a_far_key_among_hundreds():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,hidden,experts,top_k,bias", [
-    (5, 64, 4, 2, False), (9, 96, 8, 3, True), (700, 80, 6, 4, True), (3, 3072, 256, 8, True), (1, 200, 37, 5, True)])
+    (5, 64, 4, 2, False), (9, 96, 8, 3, True), (700, 80, 6, 4, True), (3, 3072, 256, 8, True), (1, 200, 37, 5, True),
+    (4, 3072, 256, 8, True)])      # the last: its staged tokens are exactly 48 KB of shared memory
 def test_router(dtype, tokens, hidden, experts, top_k, bias):
     from sparseengine_b200.csrc import ops
     x = rnd(tokens, hidden, dtype=dtype, seed=1)
