@@ -116,6 +116,45 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
     runner.cache.check()
 
 
+def random_configuration(rng) -> dict:
+    """Sizes drawn at random from what the architecture allows: head sizes in steps of 16, any
+    number of heads and groups, widths and vocabularies that are no power of two."""
+    d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128]))
+    hkv, group = int(rng.randint(1, 5)), int(rng.randint(1, 7))
+    rot = min(int(rng.choice([2, 4, 8, 16, d // 2, d])), d)
+    experts = int(rng.randint(2, 10))
+    cfg = dict(plain_m2.TINY_A)
+    cfg.update(num_hidden_layers=int(rng.randint(1, 4)), hidden_size=int(rng.choice([24, 40, 50, 64, 72, 75, 96, 100, 136, 200])),
+               num_attention_heads=hkv * group, num_key_value_heads=hkv, head_dim=d, rotary_dim=rot - rot % 2,
+               rope_theta=float(rng.choice([1e4, 5e4, 1e6, 5e6])), rms_norm_eps=float(rng.choice([1e-6, 1e-5, 3e-6])),
+               num_local_experts=experts, num_experts_per_tok=int(rng.randint(1, experts + 1)),
+               intermediate_size=int(rng.choice([16, 24, 40, 52, 64, 72])), vocab_size=int(rng.randint(40, 500)),
+               max_position_embeddings=4096)
+    return cfg
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_random_configurations_in_32_bit(seed, tmp_path):
+    """Eight configurations drawn at random, each with a random schedule, in 32-bit (where the
+    comparison is tight enough to show a kernel that mishandles a size)."""
+    rng = np.random.RandomState(5000 + seed)
+    cfg = random_configuration(rng)
+    name = f"random{seed}"
+    tu.TINY[name] = (cfg, 100 + seed, float(rng.choice([0.02, 0.05, 0.1])), 0.05, 0.05, int(rng.choice([4, 8, 16, 32])))
+    try:
+        tensors = tu.make_model_folder(str(tmp_path), name, "float32")
+        lens = [int(x) for x in rng.randint(2, 120, size=5)]
+        seqs = {f"s{i}": tu.random_prompt(cfg["vocab_size"], m, 7 * seed + i) for i, m in enumerate(lens)}
+        steps = tu.trace_random(seqs, seed)
+        runner = runner_for(str(tmp_path), name, "float32", steps)
+        got = tu.run_trace_runner(runner, steps)
+        ref = reference(name, "float32", tensors, seqs)
+        tu.compare(got, ref, *TOL["float32"], what=f"{cfg}")
+        runner.cache.check()
+    finally:
+        del tu.TINY[name]
+
+
 @pytest.mark.parametrize("dtype", list(ACT))
 @pytest.mark.parametrize("name", ["A", "D"])
 @pytest.mark.parametrize("seed", [3, 11, 12])
