@@ -9,6 +9,7 @@
 // of the chosen, divided by their sum (:202-238, epsilon 0 for M2:
 // src/sparseengine/kernels/triton/minimax_m2_router.py:50-63).
 #include "common.cuh"
+#include "mma_util.cuh"
 
 namespace se {
 
@@ -107,44 +108,35 @@ __global__ void router_logits_kernel(const T* __restrict__ x, const float* __res
 
 // Many tokens: a block of 8 warps takes 32 tokens x 16 experts; warp w owns the 8 x 8
 // sub-tile (tokens 8*(w/2).., experts 8*(w%2)..) with 64 accumulators per lane.  The token
-// and gate rows are staged through shared memory (two buffers) in chunks of 32 16-byte groups, which are
-// exactly the groups the 32 lanes take in one step of the fixed summation order (see
-// quarter_dot), so every (token, expert, quarter, lane) partial sum is accumulated in the
-// same order as in the other kernels; quarters are reduced by the same butterfly and
-// combined as (q0 + q1) + (q2 + q3).  Needs hidden % 4 == 0.
+// and gate rows go to shared memory with cp.async in chunks of 32 16-byte groups (three
+// chunks in flight, one block barrier per chunk), which are exactly the groups the 32 lanes
+// take in one step of the fixed summation order (see quarter_dot), so every (token, expert,
+// quarter, lane) partial sum is accumulated in the same order as in the other kernels;
+// quarters are reduced by the same butterfly and combined as (q0 + q1) + (q2 + q3).  The
+// chunks of the four quarters form one stream, so the copies run ahead across the quarters'
+// ends too.  Token rows stay in their own type in shared memory and are widened when they are
+// read.  Needs hidden % 4 == 0.
 //
-// The multiply-adds are the packed ones of this architecture (fma.rn.f32x2: two independent
-// IEEE fp32 fused multiply-adds per instruction): an accumulator pair holds one token's sums
-// for two neighbouring experts, the token's value is duplicated into both halves, and the gate
-// rows are staged pair-interleaved -- (g0.x, g1.x, g0.y, g1.y) and (g0.z, g1.z, g0.w, g1.w) per
-// 16-byte group -- so that one 16-byte shared-memory load yields two packed operands.  Every
-// accumulator still sees its four products per group in the order x, y, z, w.
+// Plain fused multiply-adds: the packed fma.rn.f32x2 of this architecture occupies its pipe
+// for twice as long as a scalar one (measured: 3.7 pipe cycles per packed instruction), and the
+// scalar ones spread over both multiply-add pipes.
 constexpr int kBigTokens = 32, kBigExperts = 16;
-constexpr int kBigBufs = 2;        // staging buffers: chunk g + 1 is written while chunk g is read, one barrier per chunk
+constexpr int kBigStages = 3;
 
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ unsigned long long dup2(float v) {
-    unsigned long long d;
-    asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "f"(v));
-    return d;
-}
-__device__ __forceinline__ unsigned long long pair2(float lo, float hi) {
-    unsigned long long d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-    return d;
+__device__ __forceinline__ void cp_async_small(uint32_t dst, const void* src, int bytes, bool valid) {
+    const int n = valid ? bytes : 0;           // the rest of the destination is filled with zeros
+    if (bytes == 16)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 
-// four consecutive elements as 32-bit values (the address is 4-element aligned)
-__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+// the four elements of a staged group as 32-bit values
+__device__ __forceinline__ float4 staged4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 staged4(const __nv_bfloat16* p) {
     const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    return make_float4(a.x, a.y, b.x, b.y);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
 }
 
 template <int N, int M>
@@ -162,117 +154,99 @@ template <typename T>
 __global__ void __launch_bounds__(256, 2)
 router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ gate, float* __restrict__ logits,
                            int tokens, int hidden, int experts) {
-    extern __shared__ __align__(16) float tiled_smem[];
-    float (*xs)[kBigTokens][128] = reinterpret_cast<float (*)[kBigTokens][128]>(tiled_smem);
-    float (*gs)[kBigExperts][128] = reinterpret_cast<float (*)[kBigExperts][128]>(tiled_smem + kBigBufs * kBigTokens * 128);
-    float (*qsum)[4][64] = reinterpret_cast<float (*)[4][64]>(tiled_smem + kBigBufs * (kBigTokens + kBigExperts) * 128);
+    extern __shared__ __align__(16) uint8_t tiled_smem[];
+    constexpr int kXStage = kBigTokens * 128 * (int)sizeof(T), kGStage = kBigExperts * 128 * (int)sizeof(float);
+    uint8_t* xs_base = tiled_smem;                                  // [stages][tokens][128] of T
+    uint8_t* gs_base = tiled_smem + kBigStages * kXStage;           // [stages][experts][128] float
+    float (*qsum)[4][64] = reinterpret_cast<float (*)[4][64]>(tiled_smem + kBigStages * (kXStage + kGStage));
     const int t0 = blockIdx.x * kBigTokens, e0 = blockIdx.y * kBigExperts;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wt = (warp >> 1) * 8, we = (warp & 1) * 8;
     const int n4 = hidden >> 2;
     const int per = (n4 + 3) / 4;
+    const int cpq = (per + 31) / 32, total = 4 * cpq;      // chunks per quarter (the last of a short quarter are empty)
 
-    // staging: thread -> 4 token groups (token tid/32 + 8*i, group tid%32) and 2 gate groups
-    float4 xr[4], gr[2];
-    auto fetch = [&](int first, int last) {     // groups first + lane .. (< last) of every row
-        const int i = first + lane;
+    // Chunk -> stage: thread (warp, lane) copies group `lane` of tokens warp, warp + 8, .. and of
+    // experts 2 warp, 2 warp + 1.  Tokens, experts and groups past the end are read from the last
+    // valid one instead (their sums are never used: see the guards below), so no copy has a
+    // condition.  The chunk to load next is tracked by (quarter, chunk in quarter), without a division.
+    const T* x_src[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int t = t0 + warp + 8 * k;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (i < last && t < tokens) v = load4(x + (size_t)t * hidden + 4 * i);
-            xr[k] = v;
-        }
+    for (int k = 0; k < 4; ++k) x_src[k] = x + (size_t)min(t0 + warp + 8 * k, tokens - 1) * hidden;
+    const float* g_src[2];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {            // the two experts of pair `warp`
-            const int e = min(e0 + 2 * warp + k, experts - 1);
-            gr[k] = i < last ? __ldg(reinterpret_cast<const float4*>(gate + (size_t)e * hidden) + i)
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    };
-    auto stash = [&](int buf) {
+    for (int k = 0; k < 2; ++k) g_src[k] = gate + (size_t)min(e0 + 2 * warp + k, experts - 1) * hidden;
+    const uint32_t xs0 = se::mma::smem_u32(xs_base) + (uint32_t)((warp * 128 + 4 * lane) * sizeof(T));
+    const uint32_t gs0 = se::mma::smem_u32(gs_base) + (uint32_t)((2 * warp * 128 + 4 * lane) * sizeof(float));
+    int load_q = 0, load_c = 0, load_stage = 0;
+    auto load_next = [&]() {
+        const int i = min(load_q * per + 32 * load_c + lane, n4 - 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) *reinterpret_cast<float4*>(&xs[buf][warp + 8 * k][4 * lane]) = xr[k];
-        // pair `warp` of the block's experts: rows 2 warp (x and y halves) and 2 warp + 1 (z and w halves)
-        *reinterpret_cast<float4*>(&gs[buf][2 * warp][4 * lane]) = make_float4(gr[0].x, gr[1].x, gr[0].y, gr[1].y);
-        *reinterpret_cast<float4*>(&gs[buf][2 * warp + 1][4 * lane]) = make_float4(gr[0].z, gr[1].z, gr[0].w, gr[1].w);
+        for (int k = 0; k < 4; ++k)
+            cp_async_small(xs0 + (uint32_t)(load_stage * kXStage + k * 8 * 128 * (int)sizeof(T)), x_src[k] + 4 * i,
+                           4 * (int)sizeof(T), true);
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+            cp_async_small(gs0 + (uint32_t)(load_stage * kGStage + k * 128 * (int)sizeof(float)), g_src[k] + 4 * i, 16, true);
+        if (++load_c == cpq) { load_c = 0; ++load_q; }
+        if (++load_stage == kBigStages) load_stage = 0;
     };
 
-    // The chunks of the four quarters form one stream of 4 * cpq chunks, so that the staging runs
-    // ahead across the quarters' ends too (the last chunks of a short quarter are empty).  Chunk
-    // g + 1 is written to its buffer and chunk g + 2 is asked for before chunk g is used.
-    const int cpq = (per + 31) / 32, total = 4 * cpq;
-    auto fetch_chunk = [&](int g) {
-        const int qa = (g / cpq) * per;
-        fetch(qa + 32 * (g % cpq), min(n4, qa + per));
-    };
-    unsigned long long acc2[8][4];               // [token][expert pair]: the sums for experts we + 2p and we + 2p + 1
+    float acc[8][8];                          // [token][expert]
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int p = 0; p < 4; ++p) acc2[i][p] = 0ull;
-    fetch_chunk(0);
-    stash(0);
-    if (total > 1) fetch_chunk(1);
-    __syncthreads();
-    for (int g = 0; g < total; ++g) {
-        const int buf = g % kBigBufs;
-        const int quarter = g / cpq, c = g % cpq;
+        for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+    for (int g = 0; g < kBigStages - 1; ++g) {
+        if (g < total) load_next();
+        se::mma::cp_async_commit();
+    }
+    int stage = 0;
+    for (int quarter = 0; quarter < 4; ++quarter) {
         const int a = quarter * per, b = min(n4, a + per);
-        if (g + 1 < total) stash((g + 1) % kBigBufs);
-        if (g + 2 < total) fetch_chunk(g + 2);
-        if (a + 32 * c + lane < b) {             // lanes past the quarter's end add nothing (as in quarter_dot)
-            unsigned long long gxy[4][2], gzw[4][2];
+        for (int c = 0; c < cpq; ++c) {
+            se::mma::cp_async_wait<kBigStages - 2>();
+            __syncthreads();  // this chunk is there for everyone, and everyone is done with the one before, whose stage is refilled now
+            if (load_q < 4) load_next();
+            se::mma::cp_async_commit();
+            if (a + 32 * c + lane < b) {         // lanes past the quarter's end add nothing (as in quarter_dot)
+                const T* xs = reinterpret_cast<const T*>(xs_base + (size_t)stage * kXStage) + wt * 128 + 4 * lane;
+                const float* gs = reinterpret_cast<const float*>(gs_base + (size_t)stage * kGStage) + we * 128 + 4 * lane;
+                float4 gv[8];
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const float4 ga = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p][4 * lane]);
-                const float4 gb = *reinterpret_cast<const float4*>(&gs[buf][we + 2 * p + 1][4 * lane]);
-                gxy[p][0] = pair2(ga.x, ga.y);
-                gxy[p][1] = pair2(ga.z, ga.w);
-                gzw[p][0] = pair2(gb.x, gb.y);
-                gzw[p][1] = pair2(gb.z, gb.w);
-            }
+                for (int e = 0; e < 8; ++e) gv[e] = *reinterpret_cast<const float4*>(gs + e * 128);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][wt + i][4 * lane]);
-                const unsigned long long xx = dup2(xv.x), xy = dup2(xv.y), xz = dup2(xv.z), xw = dup2(xv.w);
-                // four independent accumulators between the dependent steps of each one
+                for (int i = 0; i < 8; ++i) {
+                    const float4 xv = staged4(xs + i * 128);
+                    // every accumulator takes its four products in the order x, y, z, w
 #pragma unroll
-                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xx, gxy[p][0], acc2[i][p]);
+                    for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(xv.x, gv[e].x, acc[i][e]);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xy, gxy[p][1], acc2[i][p]);
+                    for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(xv.y, gv[e].y, acc[i][e]);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xz, gzw[p][0], acc2[i][p]);
+                    for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(xv.z, gv[e].z, acc[i][e]);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) acc2[i][p] = fma2(xw, gzw[p][1], acc2[i][p]);
-            }
-        }
-        if (c == cpq - 1) {                      // the quarter is complete
-            float acc[8][8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    acc[i][2 * p] = __uint_as_float((unsigned)(acc2[i][p] & 0xffffffffull));
-                    acc[i][2 * p + 1] = __uint_as_float((unsigned)(acc2[i][p] >> 32));
-                    acc2[i][p] = 0ull;
+                    for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(xv.w, gv[e].w, acc[i][e]);
                 }
-            // 64 sums over the lanes at once: each step halves the values a lane holds and adds
-            // the partner's copy of the half it keeps.  The pairs are those of warp_sum (lanes
-            // l and l ^ 16, then ^ 8, 4, 2, 1) and a + b = b + a, so every total has warp_sum's
-            // bits; lane l ends with the totals of values 2l and 2l + 1.
-            float* v = &acc[0][0];
-            halve_over_lanes<64, 16>(v, lane);
-            halve_over_lanes<32, 8>(v, lane);
-            halve_over_lanes<16, 4>(v, lane);
-            halve_over_lanes<8, 2>(v, lane);
-            halve_over_lanes<4, 1>(v, lane);
-            qsum[warp][quarter][2 * lane] = v[0];
-            qsum[warp][quarter][2 * lane + 1] = v[1];
+            }
+            if (++stage == kBigStages) stage = 0;
         }
-        // chunk g + 1 is in its buffer for everyone, and everyone is done with chunk g - 1's buffer,
-        // which the next iteration writes
-        __syncthreads();
+        // The quarter is complete.  64 sums over the lanes at once: each step halves the values a
+        // lane holds and adds the partner's copy of the half it keeps.  The pairs are those of
+        // warp_sum (lanes l and l ^ 16, then ^ 8, 4, 2, 1) and a + b = b + a, so every total has
+        // warp_sum's bits; lane l ends with the totals of values 2l and 2l + 1.
+        float* v = &acc[0][0];
+        halve_over_lanes<64, 16>(v, lane);
+        halve_over_lanes<32, 8>(v, lane);
+        halve_over_lanes<16, 4>(v, lane);
+        halve_over_lanes<8, 2>(v, lane);
+        halve_over_lanes<4, 1>(v, lane);
+        qsum[warp][quarter][2 * lane] = v[0];
+        qsum[warp][quarter][2 * lane + 1] = v[1];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
     }
     __syncwarp();
     for (int o = lane; o < 64; o += 32) {
@@ -591,7 +565,8 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                 (const T*)x, gate, logits, tokens, hidden, experts);
         } else if ((hidden & 3) == 0) {
             dim3 grid(se::ceil_div(tokens, se::kBigTokens), se::ceil_div(experts, se::kBigExperts));
-            const int tiled_smem = (se::kBigBufs * (se::kBigTokens + se::kBigExperts) * 128 + 8 * 4 * 64) * (int)sizeof(float);
+            const int tiled_smem = se::kBigStages * (se::kBigTokens * 128 * (int)sizeof(T) + se::kBigExperts * 128 * (int)sizeof(float)) +
+                                   8 * 4 * 64 * (int)sizeof(float);
             cudaError_t e = cudaFuncSetAttribute(se::router_logits_tiled_kernel<T>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tiled_smem);
             if (e != cudaSuccess) return (int)e;
