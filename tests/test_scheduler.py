@@ -175,3 +175,54 @@ def test_max_decoding_seqs_blocks_new_prompts():
     sched.add(seq(2, 3, max_tokens=3, ignore_eos=True))
     plan, _ = run_step(sched, cm)
     assert [it.seq.seq_id for it in plan.items] == [0]        # one decode a step, no new prompt meanwhile
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_workloads_finish_every_request_and_leak_nothing(seed):
+    """Random prompt lengths, output lengths, arrival times, aborts, cache sizes and budgets:
+    every step stays inside its budgets and continues each request where it stood, every request
+    ends with the tokens it asked for (or aborted), and all pages and rows come back."""
+    import random
+    rng = random.Random(seed)
+    page = rng.choice([1, 2, 4, 8])
+    budget = rng.choice([4, 8, 16, 64])
+    pages = rng.randint(12, 40) * (8 // page)
+    sched, cm = make(num_pages=pages, page_size=page, max_model_len=pages * page,
+                     max_num_batched_tokens=budget, max_num_seqs_in_batch=rng.choice([1, 2, 4]),
+                     max_num_seqs_in_gpu=rng.choice([2, 4, 8]), max_decoding_seqs=rng.choice([2, 4, 8]),
+                     engine_prefill_chunk_size=rng.choice([3, 8, 64]),
+                     decode_reservation_tokens=rng.choice([0, 4]))
+    todo = [seq(i, rng.randint(1, 30), max_tokens=rng.randint(1, 12), ignore_eos=True) for i in range(20)]
+    want = {s.seq_id: s.params.max_tokens for s in todo}
+    aborted, done = set(), {}
+    pending = list(todo)
+    for step in range(3000):
+        for _ in range(rng.randint(0, 2)):
+            if pending:
+                sched.add(pending.pop(0))
+        if rng.random() < 0.05 and (sched.running or sched.waiting):
+            victim = rng.choice(list(sched.running) + list(sched.waiting))
+            assert sched.abort(victim.seq_id)
+            aborted.add(victim.seq_id)
+        if sched.is_finished():
+            if not pending:
+                break
+            continue
+        plan, fin = run_step(sched, cm)
+        assert 0 < plan.num_tokens <= budget
+        ids = [it.seq.seq_id for it in plan.items]
+        assert len(ids) == len(set(ids))
+        for it in plan.items:
+            # a portion starts where the request stood before this step, and samples only at its end
+            assert it.start == it.seq.num_computed - it.n_tokens or it.seq.status.name == "FINISHED"
+            assert it.n_tokens >= 1
+        for s in fin:
+            done[s.seq_id] = s
+        cm.check()
+    else:
+        raise AssertionError("the workload did not finish")
+    assert set(done) | aborted == set(want)
+    for sid, s in done.items():
+        assert len(s.output_ids) == want[sid] and s.finish_reason == "length"
+    assert cm.free_pages() == pages and cm.free_rows == sched.config.max_num_seqs_in_gpu
+    cm.check()
