@@ -17,7 +17,10 @@ When pages run out while decoding: the request admitted last is **preempted** â€
 pages and row are freed and it returns to the front of the waiting queue with its prompt
 and the tokens it has produced; when readmitted it prefills all of them again and goes
 on (recompute, cf. src/sparseengine/engine/scheduler.py:336-424).  Because sampling noise is
-keyed by (request, number of produced tokens), the continuation is the same.  A single
+keyed by (request, number of produced tokens), the continuation draws the same noise; its
+logits are those of a prompt step over the recomputed tokens instead of decode steps, equal up to
+rounding, so a sampled token changes only where the draw falls on the edge between two tokens
+(measured in bfloat16: one token in about 2,000).  A single
 request that cannot take one more token with the whole cache to itself is an error, not
 a loop.
 """
