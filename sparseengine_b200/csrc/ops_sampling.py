@@ -6,7 +6,7 @@ import torch
 from .ops import _check, _fn, _ptr, _stream, dtype_code
 
 
-def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None):
+def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None, impl: int = 0):
     rows, vocab = logits.shape
     if temperature is None and logprob is None and vocab >= 16384:
         # greedy over a large vocabulary: two stages, many blocks per row
@@ -16,11 +16,11 @@ def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None):
             _ptr(logits, None, "logits"), _ptr(out, torch.int32, "out"), _ptr(pval), _ptr(pidx), rows, vocab,
             dtype_code(logits.dtype), _stream()), "argmax")
         return out
-    _check(_fn("se_sample", "ppppppp" "iii" "p")(
+    _check(_fn("se_sample", "ppppppp" "iiii" "p")(
         _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
         _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),
         _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"), rows, vocab,
-        dtype_code(logits.dtype), _stream()), "sample")
+        dtype_code(logits.dtype), impl, _stream()), "sample")
     return out
 
 

@@ -430,6 +430,40 @@ def test_sampling_distribution_topk_topp():
     assert out[:2].cpu().tolist() == a[2:]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,scale", [(200064, 2.0), (200064, 6.0), (5003, 3.0), (300, 1.0)])
+def test_sampling_fast_path_picks_what_the_definition_picks(dtype, vocab, scale):
+    """The fast path (byte-wise top-k threshold, cut and draw over a short list in shared memory)
+    against the same kernel with every cut and the draw over the whole row: same tokens and
+    log-probabilities, for top-k, top-p, both, ties at the k-th value, and rows whose candidates
+    do not fit the list (flat distributions), which fall back to the whole row."""
+    from sparseengine_b200.csrc import ops_sampling as sops
+    rows = 24
+    logits = rnd(rows, vocab, dtype=dtype, scale=scale, seed=21)
+    logits[3, 5:40] = logits[3].max() + 1.0                       # 35 entries tie at the top
+    logits[4] = 0.0                                               # a flat row
+    temp = torch.tensor([0.7, 1.0, 1.3] * 8, device=DEV)
+    top_k = torch.tensor([0, 50, 1, 20, 7, 1000, 0, 3] * 3, dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([0.9, 1.0, 0.5, 0.95, 0.3, 0.99, 1e-4, 0.8, 1.0, 0.6, 0.9, 0.2] * 2, device=DEV)
+    agree = 0
+    for trial in range(4):
+        seeds = torch.arange(rows, dtype=torch.int64, device=DEV) * 104729 + 31 * trial
+        fast, slow = (torch.empty(rows, dtype=torch.int32, device=DEV) for _ in range(2))
+        lp_fast, lp_slow = (torch.empty(rows, dtype=torch.float32, device=DEV) for _ in range(2))
+        sops.sample(logits, temp, top_k, top_p, seeds, fast, lp_fast, impl=0)
+        sops.sample(logits, temp, top_k, top_p, seeds, slow, lp_slow, impl=1)
+        assert torch.equal(fast, slow), (trial, fast.tolist(), slow.tolist())
+        torch.testing.assert_close(lp_fast, lp_slow, atol=1e-6, rtol=1e-6)
+        agree += rows
+        # top-k alone, and top-p alone
+        zero_k, one_p = torch.zeros_like(top_k), torch.ones_like(top_p)
+        for kk, pp in ((top_k, one_p), (zero_k, top_p)):
+            sops.sample(logits, temp, kk, pp, seeds, fast, None, impl=0)
+            sops.sample(logits, temp, kk, pp, seeds, slow, None, impl=1)
+            assert torch.equal(fast, slow), (trial, fast.tolist(), slow.tolist())
+    assert agree == 4 * rows
+
+
 def test_penalties():
     from sparseengine_b200.csrc import ops_sampling as sops
     logits = torch.tensor([[1.0, -2.0, 3.0, 0.5], [1.0, -2.0, 3.0, 0.5]], device=DEV)
