@@ -16,6 +16,18 @@ def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None, impl: in
             _ptr(logits, None, "logits"), _ptr(out, torch.int32, "out"), _ptr(pval), _ptr(pidx), rows, vocab,
             dtype_code(logits.dtype), _stream()), "argmax")
         return out
+    if (impl == 0 and temperature is not None and top_k is None and top_p is None and vocab >= 16384
+            and rows <= 256):
+        # no cuts, a large vocabulary, few rows: many blocks per row
+        f32 = dict(dtype=torch.float32, device=logits.device)
+        i32 = dict(dtype=torch.int32, device=logits.device)
+        ws = [torch.empty(rows * 64, **f32), torch.empty(rows * 64, **i32), torch.empty(rows * 64, **f32),
+              torch.empty(rows * 64, **f32), torch.empty(rows * 64, **i32)]
+        _check(_fn("se_sample_plain", "ppppp" "ppppp" "iii" "p")(
+            _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
+            _ptr(seeds, torch.int64, "seeds"), _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"),
+            *[_ptr(w) for w in ws], rows, vocab, dtype_code(logits.dtype), _stream()), "sample_plain")
+        return out
     _check(_fn("se_sample", "ppppppp" "iiii" "p")(
         _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
         _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),

@@ -424,6 +424,84 @@ __global__ void argmax_final_kernel(const float* __restrict__ pval, const int* _
     if (threadIdx.x == 0) out[row] = best.i;
 }
 
+// Rows without a top-k or top-p cut, over a large vocabulary with few rows: like the two-stage
+// argmax, every row is cut into `chunks` slices that blocks take in parallel.  After the partial
+// maxima (argmax_partial_kernel) each block knows the row's maximum and takes, over its slice,
+// the partial normaliser and the partial winner of the race; the last kernel merges them.  The
+// winner is the one the one-block kernel finds (same value per entry, same rule for ties); the
+// normaliser is summed slice by slice.
+template <typename T>
+__global__ void sample_plain_partial_kernel(const T* __restrict__ logits, const float* __restrict__ temperature,
+                                            const unsigned long long* __restrict__ seeds,
+                                            const float* __restrict__ pval, const int* __restrict__ pidx,
+                                            float* __restrict__ zpart, float* __restrict__ rval, int* __restrict__ ridx,
+                                            int vocab, int chunks) {
+    __shared__ ArgMax am[33];
+    __shared__ float red[33];
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const float temp = temperature[row];
+    const bool greedy = temp <= 1e-10f;
+    const float inv_t = greedy ? 1.f : 1.f / temp;
+    ArgMax best{0.f, -1};
+    for (int c = 0; c < chunks; ++c) best = better(best, ArgMax{pval[row * chunks + c], pidx[row * chunks + c]});
+    const float mx = best.v * inv_t;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int a = chunk * per, b = min(vocab, a + per);
+    const T* x = logits + (size_t)row * vocab;
+    const unsigned long long seed = seeds[row];
+    float z = 0.f;
+    ArgMax pick{0.f, -1};
+    for (int i = a + threadIdx.x; i < b; i += blockDim.x) {
+        const float s = to_float(x[i]) * inv_t;
+        const float w = expf(s - mx);
+        z += w;
+        if (!greedy) {
+            uint32_t r[4];
+            philox4x32_10((uint32_t)(i >> 2), 0u, 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), r);
+            const float u = ((float)r[i & 3] + 0.5f) * 2.3283064365386963e-10f;   // (0, 1)
+            const float e = fmaxf(-logf(u), 1e-10f);
+            pick = better(pick, ArgMax{w / e, i});
+        }
+    }
+    z = block_sum(z, red);
+    pick = block_argmax(pick, am);
+    if (threadIdx.x == 0) {
+        zpart[row * chunks + chunk] = z;
+        rval[row * chunks + chunk] = pick.v;
+        ridx[row * chunks + chunk] = pick.i;
+    }
+}
+
+__global__ void sample_plain_final_kernel(const void* __restrict__ logits, int dtype, const float* __restrict__ temperature,
+                                          const float* __restrict__ pval, const int* __restrict__ pidx,
+                                          const float* __restrict__ zpart, const float* __restrict__ rval,
+                                          const int* __restrict__ ridx, int* __restrict__ out,
+                                          float* __restrict__ logprob, int vocab, int chunks) {
+    const int row = blockIdx.x;
+    if (threadIdx.x != 0) return;
+    const float temp = temperature[row];
+    const bool greedy = temp <= 1e-10f;
+    const float inv_t = greedy ? 1.f : 1.f / temp;
+    ArgMax best{0.f, -1}, pick{0.f, -1};
+    float z = 0.f;
+    for (int c = 0; c < chunks; ++c) {
+        best = better(best, ArgMax{pval[row * chunks + c], pidx[row * chunks + c]});
+        pick = better(pick, ArgMax{rval[row * chunks + c], ridx[row * chunks + c]});
+        z += zpart[row * chunks + c];
+    }
+    const int tok = greedy ? best.i : pick.i;
+    out[row] = tok;
+    if (logprob != nullptr) {
+        if (greedy) {
+            logprob[row] = -logf(z);
+        } else {
+            const float v = dtype == SE_DTYPE_BF16 ? to_float(((const __nv_bfloat16*)logits)[(size_t)row * vocab + tok])
+                                                   : ((const float*)logits)[(size_t)row * vocab + tok];
+            logprob[row] = v * inv_t - best.v * inv_t - logf(z);
+        }
+    }
+}
+
 // pairs: n entries (row, token, flags); flags bit 0 = in prompt or completion (repetition),
 // bit 1 = in completion (presence).  logits is float32 [rows, vocab], changed in place.
 __global__ void penalties_kernel(float* logits, const int* __restrict__ pairs, int n, int vocab,
@@ -473,6 +551,25 @@ extern "C" int se_sample(const void* logits, const float* temperature, const int
     SE_DISPATCH_DTYPE(dtype, T,
         (se::sample_kernel<T, false><<<rows, se::kSampleThreads, 0, stream>>>((const T*)logits, temperature, top_k, top_p,
                                                                               seeds, out, logprob, vocab)));
+    SE_LAUNCH_CHECK();
+}
+
+// Rows without top-k or top-p cuts (temperature rows and greedy rows), many blocks per row.
+// Workspaces of rows * 64 entries each: pval, zpart, rval (float), pidx, ridx (int).
+extern "C" int se_sample_plain(const void* logits, const float* temperature, const unsigned long long* seeds, int* out,
+                               float* logprob, float* pval, int* pidx, float* zpart, float* rval, int* ridx, int rows,
+                               int vocab, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (temperature == nullptr || seeds == nullptr) return SE_ERR_ARGUMENT;
+    const int chunks = 64;
+    dim3 grid(rows, chunks);
+    SE_DISPATCH_DTYPE(dtype, T, {
+        se::argmax_partial_kernel<T><<<grid, 256, 0, stream>>>((const T*)logits, pval, pidx, vocab, chunks);
+        se::sample_plain_partial_kernel<T><<<grid, 256, 0, stream>>>((const T*)logits, temperature, seeds, pval, pidx,
+                                                                     zpart, rval, ridx, vocab, chunks);
+    });
+    se::sample_plain_final_kernel<<<rows, 32, 0, stream>>>(logits, dtype, temperature, pval, pidx, zpart, rval, ridx, out,
+                                                           logprob, vocab, chunks);
     SE_LAUNCH_CHECK();
 }
 

@@ -117,6 +117,8 @@ class Sampler:
             temp = d[2 * n:3 * n].view(torch.float32)
             top_k = d[3 * n:4 * n]
             top_p = d[4 * n:5 * n].view(torch.float32)
+            if not any(0 < r.params.top_k < vocab or r.params.top_p < 1.0 for r in requests):
+                top_k = top_p = None            # no cuts anywhere: the kernels with many blocks per row
             sops.sample(logits, temp, top_k, top_p, seeds, out, lp)
             pend.keep.append(d)
         # the n most likely tokens of the rows that asked for them (logprobs = n > 0)

@@ -464,6 +464,27 @@ def test_sampling_fast_path_picks_what_the_definition_picks(dtype, vocab, scale)
     assert agree == 4 * rows
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampling_without_cuts_many_blocks_per_row(dtype):
+    """Temperature rows (and greedy rows among them) over a large vocabulary take kernels with
+    many blocks per row: the same tokens as the one-block kernel, log-probabilities to rounding."""
+    from sparseengine_b200.csrc import ops_sampling as sops
+    rows, vocab = 9, 200064
+    logits = rnd(rows, vocab, dtype=dtype, scale=3.0, seed=33)
+    logits[2, 7] = logits[2, 150000] = logits[2].max() + 2.0          # a tie at the top of a greedy row
+    temp = torch.tensor([0.7, 1.0, 0.0, 1.3, 0.0, 0.5, 2.0, 1.0, 0.9], device=DEV)
+    for trial in range(3):
+        seeds = torch.arange(rows, dtype=torch.int64, device=DEV) * 7919 + trial
+        many, one = (torch.empty(rows, dtype=torch.int32, device=DEV) for _ in range(2))
+        lp_many, lp_one = (torch.empty(rows, dtype=torch.float32, device=DEV) for _ in range(2))
+        before = dict(sops.calls) if hasattr(sops, "calls") else None
+        sops.sample(logits, temp, None, None, seeds, many, lp_many)
+        sops.sample(logits, temp, None, None, seeds, one, lp_one, impl=1)
+        assert torch.equal(many, one), (many.tolist(), one.tolist())
+        assert int(many[2]) == 7
+        torch.testing.assert_close(lp_many, lp_one, atol=2e-5, rtol=1e-5)
+
+
 def test_penalties():
     from sparseengine_b200.csrc import ops_sampling as sops
     logits = torch.tensor([[1.0, -2.0, 3.0, 0.5], [1.0, -2.0, 3.0, 0.5]], device=DEV)
