@@ -28,10 +28,14 @@ def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None, impl: in
             _ptr(seeds, torch.int64, "seeds"), _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"),
             *[_ptr(w) for w in ws], rows, vocab, dtype_code(logits.dtype), _stream()), "sample_plain")
         return out
-    _check(_fn("se_sample", "ppppppp" "iiii" "p")(
+    spill = None
+    if impl == 0 and temperature is not None and (top_k is not None or top_p is not None):
+        # room for a row's list of candidates when it does not fit into shared memory
+        spill = torch.empty(rows * 3 * vocab, dtype=torch.float32, device=logits.device)
+    _check(_fn("se_sample", "pppppppp" "iiii" "p")(
         _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
         _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),
-        _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"), rows, vocab,
+        _ptr(out, torch.int32, "out"), _ptr(logprob, torch.float32, "logprob"), _ptr(spill), rows, vocab,
         dtype_code(logits.dtype), impl, _stream()), "sample")
     return out
 

@@ -191,7 +191,7 @@ template <typename T, bool FAST>
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const T* __restrict__ logits, const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds, int* __restrict__ out,
-              float* __restrict__ logprob, int vocab) {
+              float* __restrict__ logprob, float* __restrict__ spill, int vocab) {
     extern __shared__ __align__(16) uint8_t cand_raw[];         // FAST: float s[kCand], int index[kCand], float weight[kCand]
     __shared__ ArgMax am[33];
     __shared__ float red[33];
@@ -302,32 +302,42 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ temperatur
         if (threadIdx.x == 0) out[row] = best.i;
         return;
     }
-    // Which entries go on the list: all kept ones if they fit; else, with a top-p cut, those within
-    // the smallest distance whose mass is safely beyond the cut (what lies further cannot be chosen).
+    // Which entries go on the list: all kept ones if they fit into shared memory; else, with a top-p
+    // cut, those within the smallest distance whose mass is safely beyond the cut (what lies further
+    // cannot be chosen); a list too long for shared memory goes to the row's workspace in global memory.
     bool listed = false, all_kept = false;
     float reach = INFINITY;
     int mine = 0;                                // entries of this thread that go on the list
+    float listed_count = 0.f;
     if (survey) {
         block_sum_n<2 * kTaus + 1>(near, part);
-        if (near[2 * kTaus] >= 1.f && near[2 * kTaus] <= (float)kCand) {
-            listed = all_kept = true;
+        const float all = near[2 * kTaus];
+        if (all >= 1.f) {
+            all_kept = true;
+            listed_count = all;
             mine = (int)my_count[kTaus];
-        } else if (p_cut < 1.f) {
+            if (all > (float)kCand && p_cut < 1.f) {
 #pragma unroll
-            for (int j = 0; j < kTaus; ++j)
-                if (!listed && near[j] > p_cut * z * 1.0001f && near[kTaus + j] >= 1.f && near[kTaus + j] <= (float)kCand) {
-                    listed = true;
-                    reach = kTau[j];
-                    mine = (int)my_count[j];
-                }
+                for (int j = 0; j < kTaus; ++j)
+                    if (all_kept && near[j] > p_cut * z * 1.0001f && near[kTaus + j] >= 1.f) {
+                        all_kept = false;
+                        reach = kTau[j];
+                        listed_count = near[kTaus + j];
+                        mine = (int)my_count[j];
+                    }
+            }
+            // a long list in global memory pays only while it is much shorter than the row
+            listed = listed_count <= (float)kCand || (spill != nullptr && listed_count * 4.f <= (float)vocab);
         }
     }
     const unsigned long long seed = seeds[row];
     ArgMax pick{0.f, -1};
     if (listed) {
-        float* cs = reinterpret_cast<float*>(cand_raw);
-        int* ci = reinterpret_cast<int*>(cand_raw) + kCand;
-        float* ce = reinterpret_cast<float*>(cand_raw) + 2 * kCand;
+        const bool in_shared = listed_count <= (float)kCand;
+        float* spill_row = in_shared ? nullptr : spill + (size_t)row * 3 * vocab;
+        float* cs = in_shared ? reinterpret_cast<float*>(cand_raw) : spill_row;
+        int* ci = in_shared ? reinterpret_cast<int*>(cand_raw) + kCand : reinterpret_cast<int*>(spill_row + vocab);
+        float* ce = in_shared ? reinterpret_cast<float*>(cand_raw) + 2 * kCand : spill_row + 2 * (size_t)vocab;
         int n = 0;
         int at = block_exclusive_scan(mine, warp_tot, &n);
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -525,12 +535,14 @@ __global__ void to_float_kernel(const T* __restrict__ src, float* __restrict__ d
 
 }  // namespace se
 
-// temperature/top_k/top_p/seeds may be null (then every row is greedy).  impl: 0 = the fast
+// temperature/top_k/top_p/seeds may be null (then every row is greedy).  spill: optional workspace of
+// rows * 3 * vocab floats for lists that do not fit into shared memory (without it such rows take the
+// whole-row form).  impl: 0 = the fast
 // path where it applies, 1 = every cut and the draw over the whole row (the definition; tests
 // compare the two).
 extern "C" int se_sample(const void* logits, const float* temperature, const int* top_k, const float* top_p,
-                         const unsigned long long* seeds, int* out, float* logprob, int rows, int vocab, int dtype,
-                         int impl, cudaStream_t stream) {
+                         const unsigned long long* seeds, int* out, float* logprob, float* spill, int rows, int vocab,
+                         int dtype, int impl, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (temperature != nullptr && seeds == nullptr) return SE_ERR_ARGUMENT;
     if (impl != 0 && impl != 1) return SE_ERR_ARGUMENT;
@@ -544,13 +556,13 @@ extern "C" int se_sample(const void* logits, const float* temperature, const int
                 configured = true;
             }
             se::sample_kernel<T, true><<<rows, se::kSampleThreads, smem, stream>>>((const T*)logits, temperature, top_k,
-                                                                                   top_p, seeds, out, logprob, vocab);
+                                                                                   top_p, seeds, out, logprob, spill, vocab);
         });
         SE_LAUNCH_CHECK();
     }
     SE_DISPATCH_DTYPE(dtype, T,
         (se::sample_kernel<T, false><<<rows, se::kSampleThreads, 0, stream>>>((const T*)logits, temperature, top_k, top_p,
-                                                                              seeds, out, logprob, vocab)));
+                                                                              seeds, out, logprob, nullptr, vocab)));
     SE_LAUNCH_CHECK();
 }
 
