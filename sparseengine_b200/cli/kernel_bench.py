@@ -93,7 +93,7 @@ def bench_experts(a, dev):
         sets[i[0] % len(sets)].run_experts(x, ids, wt)
         i[0] += 1
     ms = timed(run, a.iters)
-    ops.tc_check(dev)
+    ops.error_check(dev)
     by = distinct * 3 * a.inter * a.hidden * 2
     fl = a.tokens * k * 3 * 2 * a.inter * a.hidden
     return ms, by, fl, {"distinct_experts": distinct, "kernels": "route build with row gather, gate/up+SwiGLU, down, combine"}
@@ -149,7 +149,7 @@ def bench_attention_prefill(a, dev):
         fn(q, cache, table, rows, cu, kvl, out, entries=1, max_q_len=t, num_heads=a.heads,
            num_kv_heads=a.kv_heads, head_dim=a.head_dim, page_size=a.page_size, scale=a.head_dim ** -0.5)
     ms = timed(run, a.iters)
-    ops.tc_check(dev)
+    ops.error_check(dev)
     keys = a.context_prefix * t + t * (t + 1) / 2
     fl = 4 * a.heads * a.head_dim * keys
     by = (a.context_prefix + t) * 2 * a.kv_heads * a.head_dim * 2 + 2 * t * a.heads * a.head_dim * 2

@@ -37,6 +37,9 @@ class Config:
     tiny_random: bool = False                      # random weights instead of a checkpoint
     tiny_random_config: Optional[str] = None       # JSON file of size overrides for the model's config.json
     tiny_random_seed: int = 0
+    tiny_random_std: float = 0.02                  # random matrices N(0, std)
+    tiny_random_norm_std: float = 0.0              # random norm weights 1 + N(0, std)
+    tiny_random_bias_std: float = 0.0              # random router selection bias N(0, std)
     eos: int = -1
     eos_token_ids: tuple = field(default_factory=tuple)
     # this engine's own
@@ -45,6 +48,7 @@ class Config:
     seed: int = 0                                  # sampler seed
     device: str = "cuda:0"
     state_slot_bytes: int = 0                      # reserved per-request state for sparse methods (unused)
+    kernel_tuning: dict = field(default_factory=dict)   # thresholds between kernels (engine/factory.py: KERNEL_TUNING_KEYS)
 
     def __post_init__(self):
         if self.sparse_method not in ("", "vanilla"):
@@ -73,6 +77,8 @@ class Config:
         if self.state_slot_bytes < 0:
             raise ValueError("state_slot_bytes must not be negative")
         self.eos_token_ids = tuple(int(t) for t in self.eos_token_ids)
+        if not isinstance(self.kernel_tuning, dict):
+            raise ValueError("kernel_tuning must be a JSON object / dict")
 
     # Keys a tiny-random override file may shrink (src/sparseengine/debug/tiny_random.py:15-26).
     TINY_RANDOM_KEYS = ("head_dim", "hidden_size", "intermediate_size", "max_position_embeddings", "num_attention_heads",

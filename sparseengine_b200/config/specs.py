@@ -50,8 +50,13 @@ class RotarySpec:
     kind: str = "rotary"
     rotary_dim: int = 0
     theta: float = 10000.0
-    pairing: str = "split_half"   # x[i] pairs with x[i + rotary_dim/2]
-    scaling: float = 1.0          # multiplies cos and sin (1.0 without yarn)
+    # which dims form rotated pair i: "split_half" (i, i + rotary_dim/2), "interleaved"
+    # (2i, 2i+1), "interleaved_to_split_half" (reads 2i, 2i+1; writes i, i + rotary_dim/2)
+    pairing: str = "split_half"
+    scaling: float = 1.0          # multiplies cos and sin (beside what frequency_scaling brings)
+    # the configuration's frequency-scaling entries (linear, llama3, yarn) as a sorted tuple of
+    # (key, value) pairs, or None; worked into the frequency table on the host
+    frequency_scaling: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -140,4 +145,5 @@ class ModelSpec:
     embed_source: str = "model.embed_tokens.weight"
     head_source: Optional[str] = "lm_head.weight"   # None = tied to the embedding
     ignored_prefixes: tuple = ()                    # checkpoint names skipped at load
+    ignored_rule: Optional[Any] = None              # name -> bool: further names skipped at load
     stored_dtype: str = "bfloat16"

@@ -12,6 +12,8 @@
 // 32-bit, probabilities rounded to bfloat16 before they multiply V, the output rounded once.
 //
 // Any page size; head sizes 64 and 128 (others use the plain kernel); a window is honoured.
+// A block-table entry outside [0, num_pages) is not followed: the rows it stands for are
+// zero-filled and a code goes to the error word.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -31,7 +33,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                    const int* __restrict__ token_seq, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
-                   int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split) {
+                   int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split,
+                   int num_pages, int* __restrict__ error) {
     constexpr int kChunks = D / 8;                   // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * D * 2;    // one K or V tile
     extern __shared__ __align__(128) uint8_t smem[];
@@ -89,17 +92,20 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         static_assert(kThreads % kChunks == 0 && kTileKeys % kRowStep == 0, "tile copy mapping");
         const int c = threadIdx.x % kChunks, r0t = threadIdx.x / kChunks;
         const __nv_bfloat16* srcs[kIters];
+        bool page_ok[kIters];
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int j = base + r0t + k * kRowStep;
             const int jj = j < ke ? j : ks;      // any valid key: the copy is zero-filled when out of range
             const int page = row_table[jj / page_size];
-            srcs[k] = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            // an entry that names no page of the pool is not followed: its rows are zero-filled
+            page_ok[k] = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_DECODE);
+            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
         }
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int r = r0t + k * kRowStep;
-            const bool ok = base + r < ke;
+            const bool ok = base + r < ke && page_ok[k];
             cp_async16(smem_u32(kbase) + tile_off<D>(r, c), srcs[k], ok);
             cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
         }
@@ -257,7 +263,7 @@ template <int D>
 static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
                   const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int tokens,
                   int hq, int hkv, int page_size, float scale, int window, int splits, int keys_per_split,
-                  cudaStream_t stream) {
+                  int num_pages, int* error, cudaStream_t stream) {
     const int group = hq / hkv;
     const int gtiles = (group + 15) / 16;
     const size_t stage_smem = (size_t)kStages * 2 * kTileKeys * D * 2;
@@ -273,7 +279,7 @@ static int launch(const void* q, const void* cache, const int* table, int table_
     attn_decode_kernel<D><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, token_seq, positions,
         (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits,
-        keys_per_split);
+        keys_per_split, num_pages, error);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) {
@@ -295,14 +301,17 @@ extern "C" int se_attn_decode_supported(int head_dim, int hq, int hkv) {
 extern "C" int se_attn_decode(const void* q, const void* cache, const int* table, int table_stride,
                               const int* seq_rows, const int* token_seq, const int* positions, void* out,
                               float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int page_size,
-                              float scale, int window, int splits, int keys_per_split, cudaStream_t stream) {
+                              float scale, int window, int splits, int keys_per_split, int num_pages, int* error,
+                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!se_attn_decode_supported(head_dim, hq, hkv) || splits < 1 || keys_per_split <= 0 || keys_per_split % 64)
         return SE_ERR_UNSUPPORTED;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
     if (head_dim == 64)
         return se::dec::launch<64>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
-                                   tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, stream);
+                                   tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
+                                   stream);
     return se::dec::launch<128>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
-                                tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, stream);
+                                tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
+                                stream);
 }

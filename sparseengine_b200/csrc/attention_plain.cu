@@ -7,6 +7,10 @@
 // probability is rounded to the activation type before it multiplies V; the output is
 // rounded once.  Reference: src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127,
 // src/sparseengine/kernels/triton/gqa_flash_decoding_stage1.py:69-120.
+//
+// A block-table entry outside [0, num_pages) is not followed: the key is left out and a code
+// goes to the error word (the reference checks such indices on the host behind a debug
+// switch, src/sparseengine/layers/attention_backend.py:155-215).
 #include "common.cuh"
 
 namespace se {
@@ -19,7 +23,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
                                              const int* __restrict__ table, int table_stride,
                                              const int* __restrict__ seq_rows, const int* __restrict__ token_seq,
                                              const int* __restrict__ positions, T* __restrict__ out, int hq, int hkv,
-                                             int d, int page_size, float scale, int window) {
+                                             int d, int page_size, float scale, int window, int num_pages,
+                                             int* __restrict__ error) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (hq / hkv);
@@ -41,6 +46,7 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
     float m = -INFINITY, l = 0.f;
     for (int j = lo + warp; j <= pos; j += kAttnWarps) {
         const int page = row_table[j / page_size];
+        if (!page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_PLAIN)) continue;     // warp-uniform: the key is left out
         const T* kp = cache + (size_t)page * page_elems + head_off + (size_t)(j % page_size) * d;
         const T* vp = kp + v_off;
         float s = 0.f;
@@ -89,13 +95,13 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
 extern "C" int se_paged_attention_plain(const void* q, const void* cache, const int* table, int table_stride,
                                         const int* seq_rows, const int* token_seq, const int* positions, void* out,
                                         int tokens, int hq, int hkv, int d, int page_size, float scale, int window,
-                                        int dtype, cudaStream_t stream) {
+                                        int num_pages, int* error, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d > 32 * se::kMaxDimPerLane || d <= 0 || hkv <= 0 || hq % hkv) return SE_ERR_UNSUPPORTED;
     dim3 grid(tokens, hq);
     SE_DISPATCH_DTYPE(dtype, T,
         se::paged_attention_plain_kernel<T><<<grid, 32 * se::kAttnWarps, 0, stream>>>(
             (const T*)q, (const T*)cache, table, table_stride, seq_rows, token_seq, positions, (T*)out, hq, hkv, d,
-            page_size, scale, window));
+            page_size, scale, window, num_pages, error));
     SE_LAUNCH_CHECK();
 }

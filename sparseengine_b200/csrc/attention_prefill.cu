@@ -11,7 +11,9 @@
 // cache before this kernel runs.  Reference arithmetic:
 // src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127.
 //
-// Any page size; head sizes 64 and 128 (others use the plain kernel).
+// Any page size; head sizes 64 and 128 (others use the plain kernel).  A block-table entry
+// outside [0, num_pages) is not followed: its rows are zero-filled and a code goes to the
+// error word.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -31,7 +33,8 @@ __global__ void __launch_bounds__(kThreads)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                     const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                     const int* __restrict__ cu_q, const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out,
-                    int hq, int hkv, int page_size, float scale_log2, int window) {
+                    int hq, int hkv, int page_size, float scale_log2, int window, int num_pages,
+                    int* __restrict__ error) {
     constexpr int kChunks = D / 8;
     constexpr int kTileBytes = kTileKeys * D * 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -106,17 +109,22 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         static_assert(kThreads % kChunks == 0 && kTileKeys % kRowStep == 0, "tile copy mapping");
         const int c = threadIdx.x % kChunks, r0t = threadIdx.x / kChunks;
         const __nv_bfloat16* srcs[kIters];
+        bool page_ok[kIters];
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int j = base + r0t + k * kRowStep;
-            const int jj = j < k_end ? j : k_end - 1;      // any valid key: the copy is zero-filled when out of range
+            // a key every row of the tile may see (clamped into [k_lo, k_end)): rows outside that range
+            // are zero-filled, never read, so a page the window has left behind, which may belong to
+            // another request by now, is not touched
+            const int jj = min(max(j, k_lo), k_end - 1);
             const int page = row_table[jj / page_size];
-            srcs[k] = cache + (size_t)page * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            page_ok[k] = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_PREFILL);
+            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
         }
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int r = r0t + k * kRowStep;
-            const bool ok = base + r < k_end;
+            const bool ok = base + r < k_end && base + r >= k_lo && page_ok[k];
             cp_async16(smem_u32(kbase) + tile_off<D>(r, c), srcs[k], ok);
             cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
         }
@@ -229,7 +237,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int D>
 static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
                   const int* cu_q, const int* kv_len, void* out, int entries, int max_q_len, int hq, int hkv,
-                  int page_size, float scale, int window, cudaStream_t stream) {
+                  int page_size, float scale, int window, int num_pages, int* error, cudaStream_t stream) {
     const size_t smem = (size_t)kStages * 2 * kTileKeys * D * 2;
     static bool configured = false;
     if (!configured) {
@@ -241,7 +249,7 @@ static int launch(const void* q, const void* cache, const int* table, int table_
     dim3 grid(ceil_div(max_q_len * group, kTileRows), hkv, entries);
     attn_prefill_kernel<D><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
-        (__nv_bfloat16*)out, hq, hkv, page_size, scale * 1.4426950408889634f, window);
+        (__nv_bfloat16*)out, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages, error);
     return (int)cudaGetLastError();
 }
 
@@ -253,13 +261,13 @@ static int launch(const void* q, const void* cache, const int* table, int table_
 extern "C" int se_attn_prefill(const void* q, const void* cache, const int* table, int table_stride,
                                const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int entries,
                                int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale, int window,
-                               cudaStream_t stream) {
+                               int num_pages, int* error, cudaStream_t stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!(head_dim == 64 || head_dim == 128) || hkv <= 0 || hq % hkv || entries > 65535 || hkv > 65535)
         return SE_ERR_UNSUPPORTED;
     if (head_dim == 64)
         return se::pre::launch<64>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, hq,
-                                   hkv, page_size, scale, window, stream);
+                                   hkv, page_size, scale, window, num_pages, error, stream);
     return se::pre::launch<128>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, hq, hkv,
-                                page_size, scale, window, stream);
+                                page_size, scale, window, num_pages, error, stream);
 }

@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                        const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out,
-                       int* error, int hq, int hkv, int page_size, float scale_log2, int window) {
+                       int* error, int hq, int hkv, int page_size, float scale_log2, int window, int num_pages) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                               // [2 tiles][2 halves][128 rows][128 B]
@@ -214,12 +214,16 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         auto issue = [&](int tile) {
             uint8_t* st = kv_s + (size_t)(tile % kStages) * kKVStageBytes;
             const int base = k_begin + tile * kKeys;
+            // Keys outside [k_lo, k_end) are zero-filled, never read: a page the window has left
+            // behind may belong to another request by now.  An entry that names no page of the pool
+            // is not followed either (address 0 marks its row; a code goes to the error word).
             unsigned long long src_row[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int j = min(base + 32 * h + lane, k_end - 1);
+                const int j = min(max(base + 32 * h + lane, k_lo), k_end - 1);
                 const int page = row_table[j / page_size];
-                src_row[h] = (unsigned long long)(cache + (size_t)page * page_elems + head_off + (size_t)(j % page_size) * D);
+                const bool in_pool = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_PREFILL_TC);
+                src_row[h] = in_pool ? (unsigned long long)(cache + (size_t)page * page_elems + head_off + (size_t)(j % page_size) * D) : 0ull;
             }
             const int c = lane & 15;
 #pragma unroll 4
@@ -227,8 +231,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 const int r = 2 * k + (lane >> 4);
                 const unsigned long long a = __shfl_sync(0xffffffffu, src_row[0], r & 31);
                 const unsigned long long b = __shfl_sync(0xffffffffu, src_row[1], r & 31);
-                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(r < 32 ? a : b) + c * 8;
-                const bool ok = base + r < k_end;
+                const unsigned long long row_addr = r < 32 ? a : b;
+                const bool ok = base + r < k_end && base + r >= k_lo && row_addr != 0ull;
+                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(ok ? row_addr : (unsigned long long)cache) + c * 8;
                 const uint32_t off = (c >> 3) * kHalfBytes + sw128(r, c & 7);
                 cp_async16(smem_u32(st) + off, src, ok);
                 cp_async16(smem_u32(st) + 2 * kHalfBytes + off, src + v_off, ok);
@@ -424,7 +429,7 @@ extern "C" int se_attn_prefill_tc_supported(int head_dim, int hq, int hkv) {
 extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* table, int table_stride,
                                   const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int* error,
                                   int entries, int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale,
-                                  int window, cudaStream_t stream) {
+                                  int window, int num_pages, cudaStream_t stream) {
     using namespace se::fa;
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
@@ -439,6 +444,6 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
     dim3 grid(se::ceil_div(max_q_len * group, kTiles * kRows), hkv, entries);
     attn_prefill_tc_kernel<<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
-        (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window);
+        (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages);
     return (int)cudaGetLastError();
 }

@@ -66,6 +66,25 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Codes a kernel writes into the library's error word (one int per device, 0 = fine; the
+// first failure stays).  1..19: a bounded wait on a barrier ran out (the number names the
+// waiting role).  From 20: an index a kernel was given points outside what it may touch; the
+// access is skipped and the code names the kernel.
+#define SE_CODE_BAD_PAGE_QK_PREP 21
+#define SE_CODE_BAD_PAGE_ATTN_PLAIN 22
+#define SE_CODE_BAD_PAGE_ATTN_DECODE 23
+#define SE_CODE_BAD_PAGE_ATTN_PREFILL 24
+#define SE_CODE_BAD_PAGE_ATTN_PREFILL_TC 25
+#define SE_CODE_BAD_TABLE_UPDATE 26
+
+// True if block-table entry `page` names a page of a pool of `num_pages`; otherwise the code
+// goes to the error word (if there is one) and the caller leaves the page alone.
+__device__ __forceinline__ bool page_in_pool(int page, int num_pages, int* error, int code) {
+    if ((unsigned)page < (unsigned)num_pages) return true;
+    if (error != nullptr) atomicCAS(error, 0, code);
+    return false;
+}
+
 // Eight consecutive elements as 32-bit values, with 16-byte loads; `p` must be 16-byte
 // aligned (float32 takes two such loads).
 __device__ __forceinline__ void load8(const float* p, float* v) {

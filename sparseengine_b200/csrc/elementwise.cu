@@ -77,18 +77,32 @@ __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restr
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[d + i] = src[s + i];
 }
 
-// updates: n triples (row, index, page); table[row * stride + index] = page.
-__global__ void table_update_kernel(int* table, int stride, const int* __restrict__ updates, int n) {
+// updates: n triples (row, index, page); table[row * stride + index] = page.  A triple whose
+// row, index or page lies outside the table or the pool is not applied, and a code goes to
+// the error word.
+__device__ __forceinline__ void apply_table_update(int* table, int rows, int stride, const int* __restrict__ updates,
+                                                   int i, int num_pages, int* error) {
+    const int row = updates[3 * i], index = updates[3 * i + 1], page = updates[3 * i + 2];
+    if ((unsigned)row >= (unsigned)rows || (unsigned)index >= (unsigned)stride ||
+        !page_in_pool(page, num_pages, nullptr, 0)) {
+        if (error != nullptr) atomicCAS(error, 0, SE_CODE_BAD_TABLE_UPDATE);
+        return;
+    }
+    table[(size_t)row * stride + index] = page;
+}
+
+__global__ void table_update_kernel(int* table, int rows, int stride, const int* __restrict__ updates, int n,
+                                    int num_pages, int* error) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) table[(size_t)updates[3 * i] * stride + updates[3 * i + 1]] = updates[3 * i + 2];
+    if (i < n) apply_table_update(table, rows, stride, updates, i, num_pages, error);
 }
 
 // The same with the number of triples read from device memory (for replayed CUDA graphs,
 // where the launch is fixed and the count changes from step to step).
-__global__ void table_update_dyn_kernel(int* table, int stride, const int* __restrict__ updates,
-                                        const int* __restrict__ count, int max_n) {
+__global__ void table_update_dyn_kernel(int* table, int rows, int stride, const int* __restrict__ updates,
+                                        const int* __restrict__ count, int max_n, int num_pages, int* error) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < min(count[0], max_n)) table[(size_t)updates[3 * i] * stride + updates[3 * i + 1]] = updates[3 * i + 2];
+    if (i < min(count[0], max_n)) apply_table_update(table, rows, stride, updates, i, num_pages, error);
 }
 
 }  // namespace se
@@ -101,11 +115,14 @@ extern "C" int se_embed_gather(const void* table, const int* ids, void* out, int
     SE_LAUNCH_CHECK();
 }
 
+// The widest row the norm takes: it is kept in shared memory in 32-bit (200 KB).
+extern "C" int se_rmsnorm_max_width() { return 200 * 1024 / (int)sizeof(float); }
+
 extern "C" int se_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* residual_out,
                           int rows, int hidden, float eps, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (hidden > se_rmsnorm_max_width()) return SE_ERR_UNSUPPORTED;
     const size_t smem = (size_t)hidden * sizeof(float);
-    if (smem > 200 * 1024) return SE_ERR_UNSUPPORTED;
     const int threads = hidden >= 8192 ? 512 : hidden >= 2048 ? 256 : 128;
     SE_DISPATCH_DTYPE(dtype, T, {
         if (smem > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
@@ -126,15 +143,17 @@ extern "C" int se_gather_rows(const void* src, const int* idx, void* dst, int ro
     SE_LAUNCH_CHECK();
 }
 
-extern "C" int se_table_update(int* table, int stride, const int* updates, int n, cudaStream_t stream) {
+extern "C" int se_table_update(int* table, int rows, int stride, const int* updates, int n, int num_pages, int* error,
+                               cudaStream_t stream) {
     if (n <= 0) return 0;
-    se::table_update_kernel<<<se::ceil_div(n, 256), 256, 0, stream>>>(table, stride, updates, n);
+    se::table_update_kernel<<<se::ceil_div(n, 256), 256, 0, stream>>>(table, rows, stride, updates, n, num_pages, error);
     SE_LAUNCH_CHECK();
 }
 
-extern "C" int se_table_update_dyn(int* table, int stride, const int* updates, const int* count, int max_n,
-                                   cudaStream_t stream) {
+extern "C" int se_table_update_dyn(int* table, int rows, int stride, const int* updates, const int* count, int max_n,
+                                   int num_pages, int* error, cudaStream_t stream) {
     if (max_n <= 0) return 0;
-    se::table_update_dyn_kernel<<<se::ceil_div(max_n, 256), 256, 0, stream>>>(table, stride, updates, count, max_n);
+    se::table_update_dyn_kernel<<<se::ceil_div(max_n, 256), 256, 0, stream>>>(table, rows, stride, updates, count, max_n,
+                                                                              num_pages, error);
     SE_LAUNCH_CHECK();
 }

@@ -78,6 +78,18 @@ __device__ __forceinline__ void scan_counts(const int* counts, int experts, int 
     __syncthreads();
 }
 
+// stats[0] += experts that got at least one row, stats[1] += 1 (one block calls this, once per
+// routing build): how many experts' weights the steps of a run have to read, counted where
+// the counts already are.
+__device__ __forceinline__ void count_used_experts(const int* counts, int experts, unsigned long long* stats) {
+    if (stats == nullptr) return;
+    int mine = 0;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) mine += counts[e] > 0 ? 1 : 0;
+    mine = __reduce_add_sync(0xffffffffu, mine);
+    if ((threadIdx.x & 31) == 0 && mine > 0) atomicAdd(&stats[0], (unsigned long long)mine);
+    if (threadIdx.x == 0) atomicAdd(&stats[1], 1ull);
+}
+
 // The tile list and the offsets, from the scans (one block writes them).
 __device__ __forceinline__ void write_tiles(const int* off, const int* toff, int experts, int tile_rows,
                                             int* __restrict__ offsets, int* __restrict__ tile_expert,
@@ -100,13 +112,18 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
                                    const int* __restrict__ counts, int assignments, int experts, int tile_rows,
                                    int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ inv_pos,
                                    int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                   int* __restrict__ num_tiles) {
+                                   int* __restrict__ num_tiles, unsigned long long* stats) {
     extern __shared__ int off[];   // experts + 1 row offsets, then experts + 1 tile offsets
     int* toff = off + experts + 1;
     scan_counts(counts, experts, tile_rows, off, toff);
-    if (blockIdx.x == 0) write_tiles(off, toff, experts, tile_rows, offsets, tile_expert, tile_row0, num_tiles);
+    if (blockIdx.x == 0) {
+        write_tiles(off, toff, experts, tile_rows, offsets, tile_expert, tile_row0, num_tiles);
+        count_used_experts(counts, experts, stats);
+    }
     for (int a = blockIdx.x * blockDim.x + threadIdx.x; a < assignments; a += gridDim.x * blockDim.x) {
-        const int p = off[ids[a]] + rank[a];
+        const int e = ids[a];
+        if ((unsigned)e >= (unsigned)experts) continue;      // not an expert: no rank was written for it, nothing is indexed with it
+        const int p = off[e] + rank[a];
         sorted[p] = a;
         inv_pos[a] = p;
     }
@@ -127,7 +144,7 @@ moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts
                        int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
                        int* __restrict__ inv_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                        int* __restrict__ num_tiles, const uint4* __restrict__ x, uint4* __restrict__ xs,
-                       int row_vecs) {
+                       int row_vecs, unsigned long long* stats) {
     extern __shared__ int sm[];
     int* ids_s = sm;                        // [assignments]
     int* rank_s = ids_s + assignments;      // [assignments]
@@ -161,6 +178,7 @@ moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts
     if (blockIdx.x == 0) {
         write_tiles(off, toff, experts, tile_rows, offsets, tile_expert, tile_row0, num_tiles);
         for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = cnt[e];
+        count_used_experts(cnt, experts, stats);
     }
     if (x == nullptr) return;
     __syncthreads();
@@ -291,13 +309,18 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 
 }  // namespace se
 
+// Most experts the routing build takes: its scans keep two ints per expert in the 48 KB of
+// shared memory a kernel has without asking.
+extern "C" int se_moe_max_experts() { return (48 * 1024 / (int)sizeof(int) - 2) / 2 - 64; }
+
 static int launch_route_build(const int* ids, int assignments, int experts, int tile_rows, int* counts, int* rank,
                               int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
-                              int* num_tiles, cudaStream_t stream) {
+                              int* num_tiles, unsigned long long* stats, cudaStream_t stream) {
     se::moe_count_rank_kernel<<<experts, assignments > 2048 ? 1024 : 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
     se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
-        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
+        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles,
+        stats);
     SE_LAUNCH_CHECK();
 }
 
@@ -307,13 +330,15 @@ extern "C" int se_moe_route_is_small(int assignments, int experts) {
 }
 
 // The routing build and, if x is given, xs[p, :] = x[sorted[p] / top_k, :] (rows of row_bytes
-// bytes, a multiple of 16, both 16-byte aligned).
+// bytes, a multiple of 16, both 16-byte aligned).  stats (optional, two 64-bit counters):
+// [0] += experts with at least one row, [1] += 1.
 extern "C" int se_moe_route_gather(const int* ids, int assignments, int experts, int tile_rows, int top_k, int* counts,
                                    int* rank, int* offsets, int* sorted, int* inv_pos, int* tile_expert,
                                    int* tile_row0, int* num_tiles, const void* x, void* xs, int row_bytes,
-                                   cudaStream_t stream) {
+                                   unsigned long long* stats, cudaStream_t stream) {
     if (assignments <= 0) return 0;
     if (tile_rows <= 0 || experts <= 0 || top_k <= 0) return SE_ERR_ARGUMENT;
+    if (experts > se_moe_max_experts()) return SE_ERR_UNSUPPORTED;
     if (x != nullptr && (row_bytes <= 0 || row_bytes % 16 || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15)))
         return SE_ERR_UNSUPPORTED;
     const int row_vecs = x != nullptr ? row_bytes / 16 : 0;
@@ -322,11 +347,11 @@ extern "C" int se_moe_route_gather(const int* ids, int assignments, int experts,
         const int blocks = x != nullptr ? assignments : 1;
         se::moe_route_small_kernel<<<blocks, 256, smem, stream>>>(
             ids, assignments, experts, tile_rows, top_k, counts, offsets, sorted, inv_pos, tile_expert, tile_row0,
-            num_tiles, (const uint4*)x, (uint4*)xs, row_vecs);
+            num_tiles, (const uint4*)x, (uint4*)xs, row_vecs, stats);
         SE_LAUNCH_CHECK();
     }
     const int rc = launch_route_build(ids, assignments, experts, tile_rows, counts, rank, offsets, sorted, inv_pos,
-                                      tile_expert, tile_row0, num_tiles, stream);
+                                      tile_expert, tile_row0, num_tiles, stats, stream);
     if (rc != 0 || x == nullptr) return rc;
     se::gather_sorted_rows_kernel<<<assignments, 128, 0, stream>>>((const uint4*)x, sorted, (uint4*)xs, row_vecs, top_k);
     SE_LAUNCH_CHECK();
@@ -336,7 +361,7 @@ extern "C" int se_moe_route_build(const int* ids, int assignments, int experts, 
                                   int* offsets, int* sorted, int* inv_pos, int* tile_expert, int* tile_row0,
                                   int* num_tiles, cudaStream_t stream) {
     return se_moe_route_gather(ids, assignments, experts, tile_rows, 1, counts, rank, offsets, sorted, inv_pos,
-                               tile_expert, tile_row0, num_tiles, nullptr, nullptr, 0, stream);
+                               tile_expert, tile_row0, num_tiles, nullptr, nullptr, 0, nullptr, stream);
 }
 
 extern "C" int se_moe_plain_tile_rows() { return se::kBM; }
@@ -427,7 +452,8 @@ extern "C" int se_moe_route_build_no_alloc(const int* ids, int assignments, int 
     se::moe_count_rank_kernel<<<experts, assignments > 2048 ? 1024 : 256, 0, stream>>>(ids, assignments, counts, rank);
     const int blocks = min(se::ceil_div(assignments, 256), 64);
     se::moe_scatter_kernel<<<blocks, 256, (2 * experts + 2) * sizeof(int), stream>>>(
-        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles);
+        ids, rank, counts, assignments, experts, tile_rows, offsets, sorted, inv_pos, tile_expert, tile_row0, num_tiles,
+        nullptr);
     return (int)cudaGetLastError();
 }
 

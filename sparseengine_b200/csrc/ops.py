@@ -35,6 +35,28 @@ def library():
     return _build.load()
 
 
+# Sizes beyond which a kernel refuses (SE_ERR_UNSUPPORTED).  The parts check them when they are
+# built, so that a model this library cannot run fails at construction with the limit named,
+# not at its first step; the numbers restate the launchers' own (a GPU test compares them with
+# what the compiled library reports through `limit`).
+LIMITS = {
+    "rmsnorm_max_width": 51200,             # a row is kept in shared memory in 32-bit
+    "router_max_experts": 12800,            # four floats per expert in shared memory during selection
+    "router_max_unaligned_width": 6400,     # widths that are no multiple of 4 keep 8 token rows in shared memory
+    "moe_max_experts": 6079,                # the routing build's scans keep two ints per expert in shared memory
+    "attention_max_head_dim": 256,          # in steps of 16
+    "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
+}
+
+
+def limit(name: str) -> int:
+    """A size limit as the compiled library reports it."""
+    f = getattr(library(), "se_" + name)
+    f.restype = _I
+    f.argtypes = []
+    return int(f())
+
+
 def _fn(name: str, sig: str):
     global launch_count
     launch_count += KERNELS_PER_CALL.get(name, 1)
@@ -111,48 +133,62 @@ def gather_rows(src, idx, out):
     return out
 
 
-def table_update(table, updates, n: int):
-    _check(_fn("se_table_update", "pipip")(
-        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(updates, torch.int32, "updates"), n, _stream()),
-        "table_update")
+def table_update(table, updates, n: int, num_pages: int):
+    """Apply ``n`` (row, index, page) triples to a block table of a pool of ``num_pages`` pages."""
+    _check(_fn("se_table_update", "piipiipp")(
+        _ptr(table, torch.int32, "table"), table.shape[0], table.shape[1], _ptr(updates, torch.int32, "updates"), n,
+        num_pages, _ptr(error_word(table.device)), _stream()), "table_update")
 
 
-def table_update_dyn(table, updates, count, max_n: int):
-    _check(_fn("se_table_update_dyn", "pippip")(
-        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(updates, torch.int32, "updates"),
-        _ptr(count, torch.int32, "count"), max_n, _stream()), "table_update_dyn")
+def table_update_dyn(table, updates, count, max_n: int, num_pages: int):
+    _check(_fn("se_table_update_dyn", "piippiipp")(
+        _ptr(table, torch.int32, "table"), table.shape[0], table.shape[1], _ptr(updates, torch.int32, "updates"),
+        _ptr(count, torch.int32, "count"), max_n, num_pages, _ptr(error_word(table.device)), _stream()),
+        "table_update_dyn")
 
 
 # ---- attention ---------------------------------------------------------------------------
 
+ROTARY_PAIRING = {"split_half": 0, "interleaved_to_split_half": 1, "interleaved": 3}
+
+
 def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads,
-            num_kv_heads, head_dim, rotary_dim, eps, rope_scale, page_size, write_cache=True):
+            num_kv_heads, head_dim, rotary_dim, eps, rope_scale, page_size, write_cache=True,
+            pairing: str = "split_half", num_pages=None):
+    """``num_pages``: the pool the block table's entries must lie in (default: the pages ``cache``
+    holds); an entry outside it is not followed and shows in the error word."""
     tokens = qkv.shape[0]
     dt = qkv.dtype
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
         raise ValueError("qkv width does not match the head counts")
+    if pairing not in ROTARY_PAIRING:
+        raise ValueError(f"rotary pairing {pairing!r} is not known; known: {sorted(ROTARY_PAIRING)}")
     inv_rms = None
     if q_w is not None and tokens > 64:      # many tokens: norm statistics once per token, not once per head
         inv_rms = torch.empty(tokens, 2, dtype=torch.float32, device=qkv.device)
-    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iipip")(
+    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iip" "iip" "ip")(
         _ptr(qkv, None, "qkv"), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
         _ptr(inv_freq, torch.float32, "inv_freq"), _ptr(positions, torch.int32, "positions"),
         _ptr(token_seq, torch.int32, "token_seq"), _ptr(seq_rows, torch.int32, "seq_rows"),
         _ptr(table, torch.int32, "table"), table.shape[1], _ptr(cache, dt, "cache"), _ptr(q_out, dt, "q_out"),
         tokens, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), float(rope_scale),
-        page_size, int(write_cache), _ptr(inv_rms), dtype_code(dt), _stream()), "qk_prep")
+        page_size, int(write_cache), _ptr(inv_rms), ROTARY_PAIRING[pairing],
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(qkv.device)),
+        dtype_code(dt), _stream()), "qk_prep")
     return q_out
 
 
 def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads,
-                          head_dim, page_size, scale, window=None):
+                          head_dim, page_size, scale, window=None, num_pages=None):
     tokens = q.shape[0]
     dt = q.dtype
-    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiii" "f" "iip")(
+    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiii" "f" "iip" "ip")(
         _ptr(q, None, "q"), _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
         _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, dt, "out"), tokens, num_heads, num_kv_heads,
-        head_dim, page_size, float(scale), int(window or 0), dtype_code(dt), _stream()), "paged_attention_plain")
+        head_dim, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
+        dtype_code(dt), _stream()), "paged_attention_plain")
     return out
 
 
@@ -197,11 +233,12 @@ def moe_plain_tile_rows() -> int:
     return int(f())
 
 
-def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None):
+def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None, stats=None):
     """ws: int32 tensors counts[E], rank[A], offsets[E+1], sorted[A], inv_pos[A],
     tile_expert[max_tiles], tile_row0[max_tiles], num_tiles[1].
     gather = (x [tokens, width], xs [A, width], top_k): also xs[p] = x[sorted[p] // top_k], the
-    activation rows in expert order (in the same launch when there are few assignments)."""
+    activation rows in expert order (in the same launch when there are few assignments).
+    stats: optional int64[2] on the device; [0] += experts that got a row, [1] += 1."""
     global launch_count
     assignments = ids.numel()
     x = xs = None
@@ -213,11 +250,12 @@ def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None):
         row_bytes = x.shape[1] * x.element_size()
     small = bool(library().se_moe_route_is_small(assignments, experts))
     launch_count += (0 if small else 1) + (0 if small or gather is None else 1)
-    _check(_fn("se_moe_route_gather", "piiii" "pppppppp" "ppi" "p")(
+    _check(_fn("se_moe_route_gather", "piiii" "pppppppp" "ppi" "pp")(
         _ptr(ids, torch.int32, "ids"), assignments, experts, tile_rows, top_k,
         *[_ptr(ws[k], torch.int32, k) for k in ("counts", "rank", "offsets", "sorted", "inv_pos", "tile_expert",
                                                  "tile_row0", "num_tiles")],
-        _ptr(x, None, "x"), _ptr(xs, None, "xs"), row_bytes, _stream()), "moe_route_build")
+        _ptr(x, None, "x"), _ptr(xs, None, "xs"), row_bytes, _ptr(stats, torch.int64, "stats"), _stream()),
+        "moe_route_build")
 
 
 def moe_max_tiles(assignments: int, experts: int, tile_rows: int) -> int:
@@ -244,59 +282,78 @@ def moe_combine(y, inv_pos, out, top_k: int):
 
 # ---- tensor-core GEMMs (bf16; csrc/gemm_tc.cu) ---------------------------------------------
 
-_tc_error = {}
+_error_words = {}
+
+# What a code in the error word says (csrc/common.cuh).
+_WAIT_ROLES = "a tensor-core kernel timed out waiting on a barrier (role code {code}); its results are not valid"
+_INDEX_CODES = {21: "the q/k preparation kernel", 22: "the plain attention kernel", 23: "the split-key decode attention kernel",
+                24: "the prompt-portion attention kernel", 25: "the tcgen05 prompt-portion attention kernel",
+                26: "the block-table update kernel"}
 
 
-def tc_error_flag(device) -> torch.Tensor:
-    """The device word the tensor-core kernels write when one of their bounded waits runs
-    out (0 = all fine).  One per device, created on first use."""
-    key = torch.device(device)
-    t = _tc_error.get(key)
+def error_text(code: int) -> str:
+    if code in _INDEX_CODES:
+        return (f"{_INDEX_CODES[code]} was given a block-table entry outside its page pool (code {code}); "
+                "the access was skipped, the step's results are not valid")
+    return _WAIT_ROLES.format(code=code)
+
+
+def error_word(device) -> torch.Tensor:
+    """The device word the kernels write when a bounded wait runs out or an index they were
+    given points outside what they may touch (0 = all fine; the first code stays).  One per
+    device, created on first use."""
+    t = _error_words.get(device)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=key)
-        _tc_error[key] = t
+        key = _device_key(device)
+        t = _error_words.get(key)
+        if t is None:
+            t = torch.zeros(1, dtype=torch.int32, device=key)
+            _error_words[key] = t
     return t
 
 
-def tc_check(device) -> None:
-    """Raise if a tensor-core kernel gave up on a wait (reads one word from the device)."""
-    t = _tc_error.get(torch.device(device))
+def _device_key(device) -> torch.device:
+    key = torch.device(device)
+    return torch.device(key.type, torch.cuda.current_device()) if key.index is None else key
+
+
+def error_check(device) -> None:
+    """Raise if a kernel reported a failure (reads one word from the device)."""
+    t = _error_words.get(_device_key(device))
     if t is not None:
         code = int(t.item())
         if code:
             t.zero_()
-            raise RuntimeError(f"a tensor-core kernel timed out waiting on a barrier (role code {code}); "
-                               "its results are not valid")
+            raise RuntimeError(error_text(code))
 
 
-_tc_error_host = {}
+_error_host = {}
 
 
-def tc_error_enqueue(device) -> None:
+def error_enqueue(device) -> None:
     """Queue a copy of the error word to pinned host memory on the current stream: the step
-    function calls this after a forward pass and reads the copy (:func:`tc_error_raise`) once
+    function calls this after a forward pass and reads the copy (:func:`error_raise`) once
     it has synchronised for its own results, so the check costs no synchronisation of its own."""
-    key = torch.device(device)
-    t = _tc_error.get(key)
+    key = _device_key(device)
+    t = _error_words.get(key)
     if t is None:
         return
-    h = _tc_error_host.get(key)
+    h = _error_host.get(key)
     if h is None:
         h = torch.zeros(1, dtype=torch.int32).pin_memory()
-        _tc_error_host[key] = h
+        _error_host[key] = h
     h.copy_(t, non_blocking=True)
 
 
-def tc_error_raise(device) -> None:
-    """Raise if the copy queued by :func:`tc_error_enqueue` (and since completed) shows a timeout."""
-    key = torch.device(device)
-    h = _tc_error_host.get(key)
+def error_raise(device) -> None:
+    """Raise if the copy queued by :func:`error_enqueue` (and since completed) shows a failure."""
+    key = _device_key(device)
+    h = _error_host.get(key)
     if h is not None and int(h[0]):
         code = int(h[0])
         h.zero_()
-        _tc_error[key].zero_()
-        raise RuntimeError(f"a tensor-core kernel timed out waiting on a barrier (role code {code}); "
-                           "its results are not valid")
+        _error_words[key].zero_()
+        raise RuntimeError(error_text(code))
 
 
 def gemm_tc_supported(k_dim: int, n_out: int, nt: int = 16) -> bool:
@@ -328,7 +385,7 @@ def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max
     _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiii" "p")(
         mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
         _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
-        _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(tc_error_flag(a.device)),
+        _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(a.device)),
         a.shape[0], experts, max_tiles, n_out, k_dim, nt, _stream()), "moe_grouped_gemm_tc")
     return out
 
@@ -338,7 +395,7 @@ def gemm_tc_dense(x, w, out, nt: int = 128):
     n_out = w.shape[0]
     _check(_fn("se_gemm_tc_dense", "pppp" "iiii" "p")(
         _ptr(x, torch.bfloat16, "x"), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
-        _ptr(tc_error_flag(x.device)), rows, n_out, k_dim, nt, _stream()), "gemm_tc_dense")
+        _ptr(error_word(x.device)), rows, n_out, k_dim, nt, _stream()), "gemm_tc_dense")
     return out
 
 
@@ -351,11 +408,26 @@ def attn_decode_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> b
     return bool(f(head_dim, num_heads, num_kv_heads))
 
 
-def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: int, sms: int = 148,
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device)."""
+    key = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    n = _sm_counts.get(key)
+    if n is None:
+        n = _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return n
+
+
+def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: int, sms: Optional[int] = None,
                      ctas_per_sm: int = 2):
     """How many key splits, and how many keys each.  CTAs = tokens x KV heads x splits run in
-    waves of ``sms * ctas_per_sm``; a CTA costs its 64-key tiles plus about three tiles of
+    waves of ``sms * ctas_per_sm`` (``sms``: the device's count unless given; two CTAs of the
+    kernel fit an SM by shared memory); a CTA costs its 64-key tiles plus about three tiles of
     fixed work.  Pick the split count with the least waves x cost."""
+    if sms is None:
+        sms = sm_count()
     group = num_heads // num_kv_heads
     base = tokens * num_kv_heads * (-(-group // 16))
     slots = sms * ctas_per_sm
@@ -374,29 +446,31 @@ def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: i
 
 
 def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,
-                scale, window=None, max_keys: int):
+                scale, window=None, max_keys: int, num_pages=None):
     tokens = q.shape[0]
-    splits, per = attn_decode_plan(tokens, num_heads, num_kv_heads, max_keys)
+    splits, per = attn_decode_plan(tokens, num_heads, num_kv_heads, max_keys, sms=sm_count(q.device))
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty(tokens * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(tokens * num_heads * splits * 2, dtype=torch.float32, device=q.device)
-    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "p")(
+    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "ip" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml),
-        tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per, _stream()),
+        tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per,
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)), _stream()),
         "attn_decode")
     return out
 
 
 def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
-                 head_dim, page_size, scale, window=None):
-    _check(_fn("se_attn_prefill", "pppipppp" "iiiiii" "f" "ip")(
+                 head_dim, page_size, scale, window=None, num_pages=None):
+    _check(_fn("se_attn_prefill", "pppipppp" "iiiiii" "f" "i" "ip" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), entries, max_q_len, num_heads,
-        num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()), "attn_prefill")
+        num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)), _stream()), "attn_prefill")
     return out
 
 
@@ -408,13 +482,14 @@ def attn_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int) 
 
 
 def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
-                    head_dim, page_size, scale, window=None):
+                    head_dim, page_size, scale, window=None, num_pages=None):
     """Prompt-portion attention on tcgen05 (head size 128)."""
-    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ip")(
+    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
-        _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), _ptr(tc_error_flag(q.device)),
-        entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _stream()),
+        _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(q.device)),
+        entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _stream()),
         "attn_prefill_tc")
     return out
 

@@ -30,8 +30,9 @@ def sample(logits, temperature, top_k, top_p, seeds, out, logprob=None, impl: in
         return out
     spill = None
     if impl == 0 and temperature is not None and (top_k is not None or top_p is not None):
-        # room for a row's list of candidates when it does not fit into shared memory
-        spill = torch.empty(rows * 3 * vocab, dtype=torch.float32, device=logits.device)
+        # room for a row's list of candidates when it does not fit into shared memory: three
+        # arrays of up to a quarter of the row each (a longer list takes the whole-row form)
+        spill = torch.empty(rows * 3 * (-(-vocab // 4)), dtype=torch.float32, device=logits.device)
     _check(_fn("se_sample", "pppppppp" "iiii" "p")(
         _ptr(logits, None, "logits"), _ptr(temperature, torch.float32, "temperature"),
         _ptr(top_k, torch.int32, "top_k"), _ptr(top_p, torch.float32, "top_p"), _ptr(seeds, torch.int64, "seeds"),

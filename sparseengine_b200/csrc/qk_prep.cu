@@ -8,6 +8,17 @@
 // (split-half pairing, 32-bit arithmetic), angle = position * inv_freq in 32-bit
 // (:190-222); KV write src/sparseengine/kernels/triton/store_kvcache.py:10-30.
 //
+// The position encoding is data: `inv_freq[rot/2]` is a table of one frequency per rotated
+// pair (any scaling of the frequencies is done by whoever builds the table), `rope_scale`
+// multiplies cos and sin, and `pairing` says which dims form pair i and where its results go:
+// bit 0 set = the inputs are the adjacent dims (2i, 2i+1), clear = the split halves
+// (i, i + rot/2); bit 1 says the same of the outputs.  0 is the split-half form, 3 the
+// adjacent-pairs form, 1 reads adjacent pairs and writes split halves
+// (src/sparseengine/layers/rotary_embedding.py:115-127).
+//
+// A block-table entry outside [0, num_pages) is not followed: the K/V write is skipped and a
+// code goes to the error word.
+//
 // Cache layout of one cache layer: [page][K|V][kv head][slot in page][head_dim].
 #include "common.cuh"
 
@@ -25,7 +36,7 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
                                const int* __restrict__ table, int table_stride, T* __restrict__ cache,
                                T* __restrict__ q_out, int hq, int hkv, int d, int rot, float eps,
                                float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms,
-                               int heads_per_block) {
+                               int heads_per_block, int pairing, int num_pages, int* __restrict__ error) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -76,6 +87,7 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
         T* k_dst = nullptr;
         if (!is_q) {
             const int page = table[(size_t)seq_rows[token_seq[t]] * table_stride + pos / page_size];
+            if (!page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_QK_PREP)) continue;     // block-uniform
             const size_t page_elems = (size_t)2 * hkv * page_size * d;
             k_dst = cache + (size_t)page * page_elems + (size_t)h * page_size * d + (size_t)(pos % page_size) * d;
         }
@@ -87,14 +99,16 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
             // cast(x32 * inv) * cast(w), the product rounded once more
             return round_act<T>(round_act<T>(v * inv) * to_float(w[h * d + dim]));
         };
-        // items i over [0, d - half): i < half is a rotated pair (dims i, i + half), the rest
-        // are the pass-through dims i + half
+        // items i over [0, d - half): i < half is rotated pair i (its dims by `pairing`), the
+        // rest are the pass-through dims i + half
         for (int i = threadIdx.x; i < d - half; i += blockDim.x) {
             if (i < half) {
-                const float x1 = normed(i), x2 = normed(i + half);
+                const int in1 = (pairing & 1) ? 2 * i : i, in2 = (pairing & 1) ? 2 * i + 1 : i + half;
+                const int out1 = (pairing & 2) ? 2 * i : i, out2 = (pairing & 2) ? 2 * i + 1 : i + half;
+                const float x1 = normed(in1), x2 = normed(in2);
                 const float c = cs[i], s = cs[half + i];
-                dst[i] = from_float<T>(x1 * c - x2 * s);
-                dst[i + half] = from_float<T>(x2 * c + x1 * s);
+                dst[out1] = from_float<T>(x1 * c - x2 * s);
+                dst[out2] = from_float<T>(x2 * c + x1 * s);
             } else {
                 dst[i + half] = from_float<T>(normed(i + half));
             }
@@ -119,7 +133,8 @@ qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T
                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
                    const int* __restrict__ token_seq, const int* __restrict__ seq_rows,
                    const int* __restrict__ table, int table_stride, T* __restrict__ cache, T* __restrict__ q_out,
-                   int hq, int hkv, int d, int rot, float eps, float rope_scale, int page_size, int write_cache) {
+                   int hq, int hkv, int d, int rot, float eps, float rope_scale, int page_size, int write_cache,
+                   int num_pages, int* __restrict__ error) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -154,6 +169,7 @@ qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T
         cs[half + j] = s * rope_scale;
     }
     const int page = write_cache ? table[(size_t)table_row * table_stride + pos / page_size] : 0;
+    if (write_cache && !page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_QK_PREP)) write_cache = 0;   // q only
     float inv_q = 1.f, inv_k = 1.f;
     if (q_w != nullptr) {
         inv_q = 1.0f / sqrtf(block_sum(ss_q, scratch) / (float)qn + eps);
@@ -245,21 +261,22 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
                           const int* positions, const int* token_seq, const int* seq_rows, const int* table,
                           int table_stride, void* cache, void* q_out, int tokens, int hq, int hkv, int d,
                           int rot, float eps, float rope_scale, int page_size, int write_cache, float* inv_rms,
-                          int dtype, cudaStream_t stream) {
+                          int pairing, int num_pages, int* error, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (rot < 0 || rot > d || (rot & 1)) return SE_ERR_ARGUMENT;
+    if (rot < 0 || rot > d || (rot & 1) || pairing < 0 || pairing > 3) return SE_ERR_ARGUMENT;
     if (inv_freq == nullptr) rot = 0;
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
     // many tokens and sizes that allow 16-byte groups: one block per token does everything
     const int elem = dtype == SE_DTYPE_BF16 ? 2 : 4;
-    const bool vec = tokens > 64 && (q_w == nullptr) == (k_w == nullptr) && d % 8 == 0 && (rot / 2) % 8 == 0 &&
+    const bool vec = tokens > 64 && pairing == 0 && (q_w == nullptr) == (k_w == nullptr) && d % 8 == 0 && (rot / 2) % 8 == 0 &&
                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0 &&
                      ((size_t)page_size * d * elem) % 16 == 0;
     if (vec) {
         SE_DISPATCH_DTYPE(dtype, T,
             se::qk_prep_vec_kernel<T><<<tokens, 256, smem, stream>>>(
                 (const T*)qkv, (const T*)q_w, (const T*)k_w, inv_freq, positions, token_seq, seq_rows, table,
-                table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size, write_cache));
+                table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size, write_cache,
+                num_pages, error));
         SE_LAUNCH_CHECK();
     }
     // inv_rms: optional float [tokens, 2] workspace; when given (many tokens) the statistics
@@ -274,6 +291,6 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
         se::qk_prep_kernel<T><<<dim3(tokens, se::ceil_div(hq + hkv, heads_per_block)), 128, smem, stream>>>(
             (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
             seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
-            write_cache, two_pass ? inv_rms : nullptr, heads_per_block));
+            write_cache, two_pass ? inv_rms : nullptr, heads_per_block, pairing, num_pages, error));
     SE_LAUNCH_CHECK();
 }

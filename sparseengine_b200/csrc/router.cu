@@ -518,7 +518,7 @@ static int launch_select(const float* logits, const float* bias, int* ids, float
     const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
     const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256;
     if (impl == 2 && !warp_ok) return SE_ERR_UNSUPPORTED;
-    if (smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    if (experts > 200 * 1024 / 16) return SE_ERR_UNSUPPORTED;
     // A warp's selection is one long chain of dependent steps (8 us for a token, against 6.6 us
     // for the block kernel), so it pays when there are tokens enough to fill the SMs with warps.
     if (impl == 2 || (impl == 0 && warp_ok && tokens >= 128)) {
@@ -544,6 +544,11 @@ extern "C" int se_router_select(const float* logits, const float* bias, int* ids
     return launch_select(logits, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, impl, stream);
 }
 
+// Most experts the selection takes (four floats per expert in 200 KB of shared memory), and the
+// widest row whose width is no multiple of 4.
+extern "C" int se_router_max_experts() { return 200 * 1024 / 16; }
+extern "C" int se_router_max_unaligned_width() { return 200 * 1024 / (se::kRouterTokens * (int)sizeof(float)); }
+
 // logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
                          float* logits, int tokens, int hidden, int experts, int top_k, int score_fn,
@@ -552,10 +557,13 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
     if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
     const int tile_tokens = tokens < se::kRouterTokens ? tokens : se::kRouterTokens;
     const size_t smem = (size_t)tile_tokens * hidden * sizeof(float);
-    const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
-    if (smem > 200 * 1024 || smem_sel > 200 * 1024) return SE_ERR_UNSUPPORTED;
+    // The kernels that keep a tile of token rows in shared memory take rows up to 200 KB / 8
+    // tokens; wider rows go to the tiled kernel (same order of sums), which needs a width that is
+    // a multiple of 4.
+    const bool rows_fit = smem <= 200 * 1024;
+    if (experts > se_router_max_experts() || (!rows_fit && (hidden & 3) != 0)) return SE_ERR_UNSUPPORTED;
     SE_DISPATCH_DTYPE(dtype, T, {
-        if (tokens <= se::kRouterTokens) {
+        if (tokens <= se::kRouterTokens && rows_fit) {
             if (smem > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
                 cudaError_t e = cudaFuncSetAttribute(se::router_logits_small_kernel<T>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

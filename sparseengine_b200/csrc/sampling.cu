@@ -334,10 +334,12 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ temperatur
     ArgMax pick{0.f, -1};
     if (listed) {
         const bool in_shared = listed_count <= (float)kCand;
-        float* spill_row = in_shared ? nullptr : spill + (size_t)row * 3 * vocab;
+        // a list in global memory is at most a quarter of the row long (see `listed` above)
+        const size_t spill_stride = ((size_t)vocab + 3) / 4;
+        float* spill_row = in_shared ? nullptr : spill + (size_t)row * 3 * spill_stride;
         float* cs = in_shared ? reinterpret_cast<float*>(cand_raw) : spill_row;
-        int* ci = in_shared ? reinterpret_cast<int*>(cand_raw) + kCand : reinterpret_cast<int*>(spill_row + vocab);
-        float* ce = in_shared ? reinterpret_cast<float*>(cand_raw) + 2 * kCand : spill_row + 2 * (size_t)vocab;
+        int* ci = in_shared ? reinterpret_cast<int*>(cand_raw) + kCand : reinterpret_cast<int*>(spill_row + spill_stride);
+        float* ce = in_shared ? reinterpret_cast<float*>(cand_raw) + 2 * kCand : spill_row + 2 * spill_stride;
         int n = 0;
         int at = block_exclusive_scan(mine, warp_tot, &n);
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -536,7 +538,7 @@ __global__ void to_float_kernel(const T* __restrict__ src, float* __restrict__ d
 }  // namespace se
 
 // temperature/top_k/top_p/seeds may be null (then every row is greedy).  spill: optional workspace of
-// rows * 3 * vocab floats for lists that do not fit into shared memory (without it such rows take the
+// rows * 3 * ceil(vocab / 4) floats for lists that do not fit into shared memory (without it such rows take the
 // whole-row form).  impl: 0 = the fast
 // path where it applies, 1 = every cut and the draw over the whole row (the definition; tests
 // compare the two).

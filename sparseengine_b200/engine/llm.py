@@ -58,6 +58,8 @@ class LLM:
     def __init__(self, model, **options):
         self.config = Config.from_kwargs(model, **options)
         cfg = self.config
+        from .factory import check_kernel_tuning
+        check_kernel_tuning(cfg.kernel_tuning)
         device = require_cuda(cfg.device)
         from ..csrc import ops
         ops.library()       # compile/load the kernels now; there is no other path
@@ -68,29 +70,18 @@ class LLM:
         from ..config.registry import load_model_spec
         _, spec = load_model_spec(raw)
         self.max_model_len = min(cfg.max_model_len or spec.max_position, spec.max_position)
-
-        # weights first, then size the cache from what is left
-        from ..weights.loader import load_weights
-        from ..weights.random_init import init_random_
-        from .model import Model
-        from ..cache.manager import CacheManager
-        from .runner import ModelRunner
-        m = Model(spec, dt)
-        with torch.cuda.device(device):
-            if cfg.tiny_random or isinstance(model, dict):
-                init_random_(m, cfg.tiny_random_seed, device)
-            else:
-                load_weights(m, model, device)
-            num_pages = self._num_pages(m, dt, device)
-            cache = CacheManager(m.layout, page_size=cfg.page_size, num_pages=num_pages,
-                                 max_rows=cfg.max_num_seqs_in_gpu, max_seq_len=self.max_model_len,
-                                 dtype=dt, device=device, reserved_state_bytes=cfg.state_slot_bytes)
-        for b in m.blocks:
-            if hasattr(b.feed_forward, "chunk_rows"):
-                b.feed_forward.chunk_rows = cfg.mlp_chunk_size
-        self.runner = ModelRunner(m, cache, device, decode_graphs=cfg.decode_graph and not cfg.enable_profiler)
+        random = cfg.tiny_random or isinstance(model, dict)
+        # weights first; the cache is then sized from what they left
+        self.runner = build_runner(
+            raw if random else model, dtype=dt, page_size=cfg.page_size,
+            num_pages=lambda m: self._num_pages(m, dt, device), max_rows=cfg.max_num_seqs_in_gpu,
+            max_seq_len=self.max_model_len, device=device, random_weights=random, seed=cfg.tiny_random_seed,
+            random_std=cfg.tiny_random_std, norm_std=cfg.tiny_random_norm_std, bias_std=cfg.tiny_random_bias_std,
+            decode_graphs=cfg.decode_graph and not cfg.enable_profiler, state_slot_bytes=cfg.state_slot_bytes,
+            mlp_chunk_size=cfg.mlp_chunk_size, kernel_tuning=cfg.kernel_tuning)
+        cache = self.runner.cache
         self.runner.validate = cfg.validate_runtime_invariants
-        m.profile = {} if cfg.enable_profiler else None
+        self.runner.model.profile = {} if cfg.enable_profiler else None
         eos = tuple(cfg.eos_token_ids) or ((cfg.eos,) if cfg.eos >= 0 else ())
         if not eos and not isinstance(model, dict):
             eos = _eos_from_folder(model, raw)
@@ -185,7 +176,7 @@ class LLM:
         pending = None
         if reqs:
             from ..csrc import ops
-            ops.tc_error_enqueue(self.runner.device)
+            ops.error_enqueue(self.runner.device)
             pending = self.sampler.submit(logits, reqs)
         return _InFlight(plan, pending)
 
@@ -224,8 +215,21 @@ class LLM:
         tokens, logprobs, tops = ([], None, None)
         if cur.pending is not None:
             from ..csrc import ops
-            tokens, logprobs, tops = self.sampler.collect(cur.pending)
-            ops.tc_error_raise(self.runner.device)
+            try:
+                tokens, logprobs, tops = self.sampler.collect(cur.pending)
+                ops.error_raise(self.runner.device)
+            except BaseException:
+                # This step's results cannot be used, and the step queued behind it was fed from
+                # them.  Let that one finish (its pinned buffers are still in flight), then end
+                # every request of this step: their cache no longer matches what the host knows of
+                # them.  The engine stays usable for the requests that wait.
+                if nxt is not None and nxt.pending is not None:
+                    try:
+                        self.sampler.collect(nxt.pending)
+                    except Exception:
+                        pass
+                self.scheduler.fail(cur.plan, "error")
+                raise
         live = sum(1 for it in cur.plan.items if it.seq.status == Status.RUNNING)
         decodes = min(cur.plan.num_decodes, live)
         prefill_tokens = cur.plan.num_tokens - cur.plan.num_decodes

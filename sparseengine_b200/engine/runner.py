@@ -79,6 +79,11 @@ class ModelRunner:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        for b in model.blocks:
+            most = getattr(b.parts().get("mixer"), "max_step_entries", None)
+            if most is not None and cache.max_rows > most:
+                raise ValueError(f"{cache.max_rows} resident requests are not supported: a step takes at most {most} "
+                                 f"entries ({type(b.parts()['mixer']).__name__})")
         self.slots = [cache.slot_for(e) for e in model.layout.entries]
         self._staging = _Staging()
         self.steps = 0
@@ -150,7 +155,7 @@ class ModelRunner:
                 with torch.cuda.device(self.device):
                     for g, (upd, n) in zip(self.cache.groups, updates):
                         if n:
-                            ops.table_update(g.table, upd, n)
+                            ops.table_update(g.table, upd, n, g.pool.num_pages)
                     logits = self.model.forward(step, self.slots, want_rows)
         except BaseException:
             # the step did not happen: give back what was reserved for it
@@ -233,7 +238,7 @@ class ModelRunner:
                     q_starts=list(q_starts), kv_lens=[s + 1 for s in q_starts], rows=list(rows),
                     dtype=self.model.dtype, max_kv_bound=bound)
                 for gi, g in enumerate(groups):
-                    ops.table_update_dyn(g.table, view(8 + 2 * gi, 3 * n), view(7 + 2 * gi, 1), n)
+                    ops.table_update_dyn(g.table, view(8 + 2 * gi, 3 * n), view(7 + 2 * gi, 1), n, g.pool.num_pages)
                 return self.model.forward(step, self.slots, view(6, n))
 
             if entry is None:

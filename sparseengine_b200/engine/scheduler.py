@@ -196,6 +196,16 @@ class Scheduler:
             self.running.remove(s)
         s.status, s.finish_reason = Status.FINISHED, reason
 
+    def fail(self, plan: StepPlan, reason: str = "error") -> list:
+        """The step of ``plan`` gave no usable result: every request of it that still runs is
+        ended with ``reason`` and gives its pages and its row back.  Returns those requests."""
+        ended = []
+        for item in plan.items:
+            if item.seq.status == Status.RUNNING:
+                self._drop(item.seq, reason)
+                ended.append(item.seq)
+        return ended
+
     # ---- after the step ----------------------------------------------------------------
     def postprocess(self, plan: StepPlan, tokens: list, logprobs=None, top_logprobs=None) -> list:
         """``tokens``: one sampled token per planned item that samples, in plan order.

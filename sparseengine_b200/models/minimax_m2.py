@@ -13,6 +13,7 @@ src/sparseengine/models/rope.py:37-43 (rope_theta), src/sparseengine/configs/mod
 """
 from __future__ import annotations
 
+import re
 from dataclasses import dataclass, fields
 from typing import Any, Optional
 
@@ -54,6 +55,8 @@ class MiniMaxM2Config:
     rope_theta: float = 10000.0
     rms_norm_eps: float = 1e-6
     shared_intermediate_size: int = 0
+    rope_scaling: Optional[tuple] = None     # sorted (key, value) pairs of a linear / llama3 / yarn frequency scaling
+    num_mtp_modules: Optional[int] = None    # multi-token-prediction modules stored after the layers (None: not stated)
     stored_dtype: str = "bfloat16"
     model_type: str = "minimax_m2"
 
@@ -67,14 +70,19 @@ class MiniMaxM2Config:
             problems.append("quantization_config is set (quantized weights are not supported)")
         if int(raw.get("shared_intermediate_size", 0) or 0) != 0:
             problems.append("shared_intermediate_size != 0 (M2 has no shared expert)")
-        scaling = raw.get("rope_scaling") or None
-        params = dict(raw.get("rope_parameters") or {})
-        rope_type = None
-        for src in (scaling, params):
-            if src:
-                rope_type = src.get("rope_type", src.get("type", rope_type))
-        if rope_type not in (None, "default"):
-            problems.append(f"rope scaling type {rope_type!r} (only the default rotary encoding is supported)")
+        # frequency scaling: ``rope_parameters`` if it is there, else ``rope_scaling``
+        # (src/sparseengine/models/rope.py:14-35); linear, llama3 and yarn become a frequency table
+        # built on the host, the types that depend on the sequence length are refused (:77-88)
+        params = dict(raw.get("rope_parameters") or raw.get("rope_scaling") or {})
+        rope_type = str(params.get("rope_type", params.get("type", "default")) or "default").lower()
+        params.pop("type", None)
+        rope_scaling = None
+        if rope_type in ("linear", "llama3", "yarn"):
+            params["rope_type"] = rope_type
+            rope_scaling = tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in params.items()
+                                        if k != "rope_theta"))
+        elif rope_type != "default":
+            problems.append(f"rope scaling type {rope_type!r} (default, linear, llama3 and yarn are supported)")
 
         required = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
                     "num_attention_heads", "num_key_value_heads", "head_dim", "rotary_dim",
@@ -104,7 +112,8 @@ class MiniMaxM2Config:
             num_local_experts=int(raw["num_local_experts"]),
             num_experts_per_tok=int(raw["num_experts_per_tok"]),
             max_position_embeddings=max_pos, rope_theta=float(theta),
-            rms_norm_eps=float(raw.get("rms_norm_eps", 1e-6)),
+            rms_norm_eps=float(raw.get("rms_norm_eps", 1e-6)), rope_scaling=rope_scaling,
+            num_mtp_modules=None if raw.get("num_mtp_modules") is None else int(raw["num_mtp_modules"]),
             stored_dtype=str(dtype).replace("torch.", ""),
             model_type=str(raw.get("model_type", "minimax_m2")),
         )
@@ -125,6 +134,12 @@ class MiniMaxM2Config:
             bad.append("num_experts_per_tok exceeds num_local_experts")
         if not (self.rope_theta > 0) or not (self.rms_norm_eps > 0):
             bad.append("rope_theta and rms_norm_eps must be positive")
+        if self.rope_scaling is not None:
+            from ..parts.position import scaled_frequencies
+            try:
+                scaled_frequencies(self.rotary_dim, self.rope_theta, dict(self.rope_scaling))
+            except ValueError as e:
+                bad.append(str(e))
         if bad:
             raise ValueError("MiniMax M2 config.json cannot be used: " + "; ".join(bad))
 
@@ -146,14 +161,37 @@ class MiniMaxM2Config:
         }
         out.update(_REQUIRED_OPTIONS)
         out["use_mtp"] = True
+        if self.num_mtp_modules is not None:
+            out["num_mtp_modules"] = self.num_mtp_modules
+        if self.rope_scaling is not None:
+            out["rope_scaling"] = {k: list(v) if isinstance(v, tuple) else v for k, v in self.rope_scaling}
         return out
+
+
+_LAYER_INDEX = re.compile(r"^model\.layers\.(\d+)\.")
+
+
+def mtp_tensor_rule(num_layers: int, num_mtp_modules: Optional[int]):
+    """Which checkpoint tensors belong to multi-token-prediction modules: those stored as
+    further decoder layers, ``model.layers.<i>.`` with ``num_layers <= i`` (and, when the
+    configuration states how many modules there are, ``i < num_layers + num_mtp_modules``:
+    an index beyond that is not explained by the configuration and stays an error)."""
+    def rule(name: str) -> bool:
+        m = _LAYER_INDEX.match(name)
+        if m is None:
+            return False
+        i = int(m.group(1))
+        if i < num_layers:
+            return False
+        return num_mtp_modules is None or i < num_layers + num_mtp_modules
+    return rule
 
 
 def build_minimax_m2(cfg: MiniMaxM2Config) -> ModelSpec:
     h, d = cfg.hidden_size, cfg.head_dim
     hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
     e, inter = cfg.num_local_experts, cfg.intermediate_size
-    rotary = RotarySpec(rotary_dim=cfg.rotary_dim, theta=cfg.rope_theta)
+    rotary = RotarySpec(rotary_dim=cfg.rotary_dim, theta=cfg.rope_theta, frequency_scaling=cfg.rope_scaling)
     attention = AttentionSpec(
         hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, scale=d ** -0.5,
         qk_norm="whole_projection", qk_norm_eps=cfg.rms_norm_eps, window=None, position=rotary)
@@ -193,12 +231,12 @@ def build_minimax_m2(cfg: MiniMaxM2Config) -> ModelSpec:
     order = [ScheduleEntry(layer=i) for i in range(cfg.num_hidden_layers)]
     # Multi-token-prediction modules live outside model.layers.[0, L); the model has no
     # use for them, so their tensors are skipped and counted at load.
-    mtp = tuple(f"model.layers.{i}." for i in range(cfg.num_hidden_layers, cfg.num_hidden_layers + 16))
     return ModelSpec(
         architecture=ARCHITECTURE, hidden_size=h, vocab_size=cfg.vocab_size,
         max_position=cfg.max_position_embeddings, layers=layers, order=order,
         final_norm=norm, embed_source="model.embed_tokens.weight", head_source="lm_head.weight",
-        ignored_prefixes=("model.mtp", "mtp.", "model.mtp_modules") + mtp,
+        ignored_prefixes=("model.mtp", "mtp.", "model.mtp_modules"),
+        ignored_rule=mtp_tensor_rule(cfg.num_hidden_layers, cfg.num_mtp_modules),
         stored_dtype=cfg.stored_dtype)
 
 

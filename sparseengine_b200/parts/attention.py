@@ -13,21 +13,33 @@ from ..config.specs import ParamSpec
 from ..csrc import ops
 from .base import KVRequest, Mixer, make_position, register_mixer
 from .linear import linear
+from .position import RotaryArgs, as_rotary_args
 
 
 class PagedAttention(Mixer):
     graph_safe = True
+    # a step's entries are a grid dimension of the prompt-portion kernels
+    max_step_entries = ops.LIMITS["grid_dim_yz"]
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         s = spec
-        if s.num_heads % s.num_kv_heads:
-            raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if s.head_dim % 16 or s.head_dim > 256:
-            raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to 256)")
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ValueError("num_heads must be a positive multiple of num_kv_heads")
+        if s.head_dim <= 0 or s.head_dim % 16 or s.head_dim > ops.LIMITS["attention_max_head_dim"]:
+            raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to "
+                             f"{ops.LIMITS['attention_max_head_dim']})")
+        if s.num_heads > ops.LIMITS["grid_dim_yz"]:
+            raise ValueError(f"{s.num_heads} query heads are not supported (at most {ops.LIMITS['grid_dim_yz']}: "
+                             "heads are a grid dimension of the attention kernels)")
         if s.qk_norm not in (None, "whole_projection"):
             raise ValueError(f"qk_norm {s.qk_norm!r} is not supported")
+        if s.window is not None and s.window <= 0:
+            raise ValueError("window must be positive (None: all keys)")
         self.position = make_position(s.position, dtype) if s.position is not None else None
+        rot = getattr(s.position, "rotary_dim", 0) if s.position is not None else 0
+        if rot > s.head_dim:
+            raise ValueError(f"the position encoding rotates {rot} dims, a head has {s.head_dim}")
         self.q_norm = self.k_norm = None
 
     def parameters(self):
@@ -47,12 +59,12 @@ class PagedAttention(Mixer):
         tokens = x.shape[0]
         qkv = linear(x, self.qkv)
         q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
-        inv_freq, rot, rope_scale = (self.position.kernel_args(x.device) if self.position is not None
-                                     else (None, 0, 1.0))
-        ops.qk_prep(qkv, self.q_norm, self.k_norm, inv_freq, step.positions, step.token_seq, step.seq_rows,
+        rope = (as_rotary_args(self.position.kernel_args(x.device)) if self.position is not None
+                else RotaryArgs(None, 0))
+        ops.qk_prep(qkv, self.q_norm, self.k_norm, rope.inv_freq, step.positions, step.token_seq, step.seq_rows,
                     slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
-                    head_dim=s.head_dim, rotary_dim=rot, eps=s.qk_norm_eps, rope_scale=rope_scale,
-                    page_size=slot.page_size, write_cache=slot.write_cache)
+                    head_dim=s.head_dim, rotary_dim=rope.rotary_dim, eps=s.qk_norm_eps, rope_scale=rope.scale,
+                    page_size=slot.page_size, write_cache=slot.write_cache, pairing=rope.pairing)
         attn = torch.empty_like(q)
         self.attend(q, attn, step, slot)
         return linear(attn, self.o)
@@ -64,7 +76,8 @@ class PagedAttention(Mixer):
     # that average at least `portion_min_average` tokens per entry (measured at M2 sizes: a
     # 512-token portion after an 8,192-token prefix takes 1.39 ms per layer instead of 3.79, a
     # 32-token one 0.87 instead of 1.08; eight decoding requests beside a 64-token portion 0.86
-    # instead of 0.91).
+    # instead of 0.91).  The three numbers are defaults measured at those sizes on a B200; the
+    # engine option ``kernel_tuning`` sets them per engine (results do not depend on them).
     decode_kernel_max_tokens = 512
     portion_min_tokens = 16
     portion_min_average = 8

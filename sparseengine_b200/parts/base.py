@@ -77,6 +77,14 @@ class StepContext:
     max_kv_bound: Optional[int] = None               # an upper bound to plan launches with, if set
 
     @property
+    def state_rows(self) -> torch.Tensor:
+        """Entry ``j``'s row in every per-request state tensor (``LayerSlot.state[row]``), on the
+        device.  A mixer with state of its own that indexes its state with this tensor and finds
+        its tokens through ``token_seq`` / ``cu_q`` / ``positions`` reads nothing from the host,
+        and may declare itself ``graph_safe``.  (The same rows index the block tables.)"""
+        return self.seq_rows
+
+    @property
     def max_q_len(self) -> int:
         return max(self.q_lens) if self.q_lens else 0
 
@@ -124,6 +132,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # most entries (requests) one step may bring, if the mixer's kernels bound it (None: any)
+    max_step_entries = None
+
     def kv_request(self) -> Optional[KVRequest]:
         return None
 

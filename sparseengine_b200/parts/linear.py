@@ -20,7 +20,10 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 
 USE_GEMV = True     # False: the library product for every shape
-GEMV_MAX_OUT = 16384   # measured: beyond this many output features (the LM head) the library product is ahead
+# Beyond this many output features the library product is taken for few rows too (measured at
+# MiniMax M2's sizes: the LM head, 200,064 features, is ahead there).  An engine option
+# (``kernel_tuning={"gemv_max_out_features": n}``) sets it.
+GEMV_MAX_OUT = 16384
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -33,6 +33,13 @@ class _RoutedSwiGLU(FeedForward):
             return False
         return ops.gemm_tc_supported(self.hidden, self.inter) and ops.gemm_tc_supported(self.inter, self.hidden)
 
+    # Two 64-bit counters on the device, created with the first step: [0] the experts that got at
+    # least one row, summed over routing builds, [1] the routing builds.  The routing build
+    # counts them where its per-expert counts already are (no launch of its own, also inside
+    # replayed CUDA graphs); a benchmark reads the difference around a timed region to know how
+    # many experts' weights a step had to read.
+    route_stats = None
+
     def run_experts(self, x, ids, weights):
         tokens = x.shape[0]
         a = tokens * self.top_k
@@ -47,7 +54,10 @@ class _RoutedSwiGLU(FeedForward):
               "tile_row0": torch.empty(max_tiles, **i32), "num_tiles": torch.empty(1, **i32)}
         # the tensor-core GEMM reads the activation rows in expert order
         xs = torch.empty(a, self.hidden, dtype=x.dtype, device=dev) if tc else None
-        ops.moe_route_build(ids, self.num_experts, tile_rows, ws, gather=(x, xs, self.top_k) if tc else None)
+        if self.route_stats is None:
+            self.route_stats = torch.zeros(2, dtype=torch.int64, device=dev)
+        ops.moe_route_build(ids, self.num_experts, tile_rows, ws, gather=(x, xs, self.top_k) if tc else None,
+                            stats=self.route_stats)
         act = torch.empty(a, self.inter, dtype=x.dtype, device=dev)
         y = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
         if tc:
@@ -74,6 +84,15 @@ class SparseMoE(_RoutedSwiGLU):
             raise ValueError(f"score function {spec.score_fn!r} is not supported")
         if not 0 < spec.top_k <= spec.num_experts:
             raise ValueError("top_k must be in [1, num_experts]")
+        most = min(ops.LIMITS["router_max_experts"], ops.LIMITS["moe_max_experts"])
+        if spec.num_experts > most:
+            raise ValueError(f"{spec.num_experts} experts are not supported (at most {most}: the selection and the "
+                             "routing build keep per-expert tables in shared memory)")
+        if spec.hidden_size % 4 and spec.hidden_size > ops.LIMITS["router_max_unaligned_width"]:
+            raise ValueError(f"a router over rows of {spec.hidden_size} elements is not supported: widths that are no "
+                             f"multiple of 4 go up to {ops.LIMITS['router_max_unaligned_width']}")
+        if spec.hidden_size <= 0 or spec.intermediate_size <= 0:
+            raise ValueError("hidden_size and intermediate_size must be positive")
         self.num_experts, self.top_k = spec.num_experts, spec.top_k
         self.hidden, self.inter = spec.hidden_size, spec.intermediate_size
         self.selection_bias = None

@@ -14,6 +14,14 @@ from .base import Norm, register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        if not 0 < spec.size <= ops.LIMITS["rmsnorm_max_width"]:
+            raise ValueError(f"RMSNorm width {spec.size} is not supported: the kernel takes rows of 1 to "
+                             f"{ops.LIMITS['rmsnorm_max_width']} elements")
+        if not spec.eps > 0:
+            raise ValueError("RMSNorm eps must be positive")
+
     def parameters(self):
         return {"weight": ParamSpec((self.spec.size,), "act", "norm")}
 

@@ -1,5 +1,7 @@
-"""Per-request sampling options, with the reference's names, defaults and checks
-(src/sparseengine/sampling_params.py:38-88)."""
+"""Per-request sampling options.  Field names, defaults and accepted ranges are the
+reference's (src/sparseengine/sampling_params.py:38-88), so that a caller's keyword
+arguments carry over; the checks are a table of rules evaluated in one pass, and every
+rule that fails is reported at once."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -7,6 +9,47 @@ from typing import Optional
 
 DEFAULT_MAX_TOKENS = 8192
 GREEDY_EPS = 1e-10     # temperatures at or below this are greedy (src/sparseengine/layers/sampler.py:75)
+
+
+def _token_tuple(value) -> tuple:
+    """None, one id or an iterable of ids -> a tuple without repeats, first occurrence kept."""
+    if value is None:
+        return ()
+    if isinstance(value, int) and not isinstance(value, bool):
+        return (value,)
+    seen, out = set(), []
+    for t in value:
+        t = int(t)
+        if t not in seen:
+            seen.add(t)
+            out.append(t)
+    return tuple(out)
+
+
+def _is_token(t) -> bool:
+    return type(t) is int and t >= 0
+
+
+# (what is checked, rule over the record, what to tell the caller)
+_RULES = (
+    ("temperature", lambda p: p.temperature >= 0.0, "needs temperature >= 0 (0 means greedy)"),
+    ("top_p", lambda p: 0.0 < p.top_p <= 1.0, "needs 0 < top_p <= 1 (1 keeps every token)"),
+    ("top_k", lambda p: p.top_k >= 0, "needs top_k >= 0 (0 keeps every token)"),
+    ("presence_penalty", lambda p: -2.0 <= p.presence_penalty <= 2.0, "needs -2 <= presence_penalty <= 2"),
+    ("repetition_penalty", lambda p: p.repetition_penalty > 0.0, "needs repetition_penalty > 0 (1 means none)"),
+    ("max_tokens", lambda p: p.max_tokens >= 1, "needs max_tokens >= 1"),
+    ("eos_token_ids", lambda p: all(t >= 0 for t in p.eos_token_ids), "holds a negative token id"),
+    ("logprobs", lambda p: p.logprobs is None or p.logprobs >= 0, "needs logprobs >= 0 or None"),
+    ("benchmark_forced_token_ids",
+     lambda p: p.benchmark_forced_token_ids is None or p.ignore_eos,
+     "only works with ignore_eos=True (a forced end-of-sequence token would end the run early)"),
+    ("benchmark_forced_token_ids",
+     lambda p: p.benchmark_forced_token_ids is None or (
+         isinstance(p.benchmark_forced_token_ids, (list, tuple))
+         and len(p.benchmark_forced_token_ids) == p.max_tokens
+         and all(_is_token(t) for t in p.benchmark_forced_token_ids)),
+     "has to be a list of max_tokens token ids (plain ints >= 0), one per generated token"),
+)
 
 
 @dataclass
@@ -23,36 +66,12 @@ class SamplingParams:
     benchmark_forced_token_ids: Optional[tuple] = None
 
     def __post_init__(self):
-        if self.temperature < 0.0:
-            raise ValueError("temperature must be non-negative")
-        if not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must be in (0, 1]")
-        if self.top_k < 0:
-            raise ValueError("top_k must be non-negative")
-        if not -2.0 <= self.presence_penalty <= 2.0:
-            raise ValueError("presence_penalty must be in [-2, 2]")
-        if not self.repetition_penalty > 0.0:
-            raise ValueError("repetition_penalty must be positive")
-        if self.max_tokens <= 0:
-            raise ValueError("max_tokens must be positive")
-        if self.eos_token_ids is None:
-            self.eos_token_ids = ()
-        elif isinstance(self.eos_token_ids, int):
-            self.eos_token_ids = (int(self.eos_token_ids),)
-        else:
-            self.eos_token_ids = tuple(dict.fromkeys(int(t) for t in self.eos_token_ids))
-        if any(t < 0 for t in self.eos_token_ids):
-            raise ValueError("eos_token_ids must contain non-negative token ids")
-        if self.logprobs is not None and self.logprobs < 0:
-            raise ValueError("logprobs must be non-negative")
-        forced = self.benchmark_forced_token_ids
-        if forced is not None:
-            if not self.ignore_eos:
-                raise ValueError("benchmark_forced_token_ids requires ignore_eos")
-            if (not isinstance(forced, (list, tuple)) or len(forced) != self.max_tokens
-                    or any(type(t) is not int or t < 0 for t in forced)):
-                raise ValueError("benchmark_forced_token_ids must contain exactly max_tokens nonnegative integers")
-            self.benchmark_forced_token_ids = tuple(forced)
+        self.eos_token_ids = _token_tuple(self.eos_token_ids)
+        broken = [f"{name} {message}" for name, rule, message in _RULES if not rule(self)]
+        if broken:
+            raise ValueError("SamplingParams: " + "; ".join(broken))
+        if self.benchmark_forced_token_ids is not None:
+            self.benchmark_forced_token_ids = tuple(self.benchmark_forced_token_ids)
 
     @property
     def greedy(self) -> bool:
@@ -63,6 +82,8 @@ class SamplingParams:
         return self.presence_penalty != 0.0 or self.repetition_penalty != 1.0
 
     def validate_for_vocab(self, vocab_size: int) -> None:
-        forced = self.benchmark_forced_token_ids
-        if forced is not None and any(t >= vocab_size for t in forced):
-            raise ValueError(f"benchmark_forced_token_ids contains a token outside the vocabulary ({vocab_size})")
+        """Forced tokens have to exist in the model's vocabulary (known only to the engine)."""
+        outside = [t for t in (self.benchmark_forced_token_ids or ()) if t >= vocab_size]
+        if outside:
+            raise ValueError(f"SamplingParams: benchmark_forced_token_ids names token {outside[0]}, "
+                             f"the vocabulary has {vocab_size}")

@@ -33,14 +33,14 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, *, page_si
             entries.append(StepEntry(e["id"], list(e["tokens"]), list(e.get("want", []))))
         logits = runner.step(entries)
         if logits is not None and logits.shape[0] > 0:
-            ops.tc_error_enqueue(runner.device)
+            ops.error_enqueue(runner.device)
             arr = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
-            ops.tc_error_raise(runner.device)
+            ops.error_raise(runner.device)
             arr.tofile(os.path.join(out_dir, f"{rec['step']}.f32"))
         else:
-            ops.tc_error_enqueue(runner.device)
+            ops.error_enqueue(runner.device)
             torch.cuda.synchronize(runner.device)
-            ops.tc_error_raise(runner.device)
+            ops.error_raise(runner.device)
         for seq_id in rec.get("end", []):
             if runner.cache.has(seq_id):
                 runner.release(seq_id)

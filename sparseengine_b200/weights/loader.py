@@ -5,8 +5,8 @@ per expert).  The whole folder is checked before anything is copied, and one err
 lists every missing tensor, every unexpected tensor and every wrong shape.  Tensors go
 to the engine's activation dtype, except parameters declared ``float32`` (router gate
 and selection bias), which stay 32-bit whatever the engine dtype; integer tensors would
-be kept as int32.  Names under the model's ignored prefixes (multi-token-prediction
-modules) are skipped and counted.
+be kept as int32.  Names under the model's ignored prefixes, or that its
+``ignored_rule`` accepts (multi-token-prediction modules), are skipped and counted.
 
 Reference behaviour: src/sparseengine/utils/loader.py:674-904 (all shards, duplicate keys
 are an error, strict validation), src/sparseengine/layers/linear.py:453-468 (qkv rows),
@@ -107,13 +107,14 @@ def load_weights(model, model_dir: str, device) -> LoadReport:
             shapes[name] = tuple(f.get_slice(name).get_shape())
 
     ignored = tuple(model.spec.ignored_prefixes)
+    rule = getattr(model.spec, "ignored_rule", None)
     report = LoadReport()
     missing = sorted(n for n in expected if n not in where)
     unexpected = []
     for n in sorted(where):
         if n in expected:
             continue
-        if ignored and n.startswith(ignored):
+        if (ignored and n.startswith(ignored)) or (rule is not None and rule(n)):
             report.skipped.append(n)
         else:
             unexpected.append(n)

@@ -79,20 +79,82 @@ def rope_inv_freq(rotary_dim: int, theta: float) -> torch.Tensor:
     return 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
 
 
-def partial_rotary(x, positions, rotary_dim, theta, act):
+def rope_scaling_of(cfg: dict):
+    """The configuration's frequency scaling: ``rope_parameters`` if present, else
+    ``rope_scaling``; no type or "default" means none (src/sparseengine/models/rope.py:14-35)."""
+    params = dict(cfg.get("rope_parameters") or cfg.get("rope_scaling") or {})
+    kind = str(params.get("rope_type", params.get("type", "default")) or "default").lower()
+    return None if kind == "default" else dict(params, rope_type=kind)
+
+
+def rope_frequencies(rotary_dim: int, theta: float, scaling: dict | None):
+    """(inv_freq, factor on cos and sin) for the scaled rotary encodings
+    (src/sparseengine/layers/rotary_embedding.py:26-101): linear :34-35, llama3 :36-59, yarn :60-100
+    with the amplitude 0.1·m·ln(factor)+1 of :8-12."""
+    inv = rope_inv_freq(rotary_dim, theta)
+    if scaling is None:
+        return inv, 1.0
+    kind, factor = scaling["rope_type"], float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor, 1.0
+    old = float(scaling["original_max_position_embeddings"])
+    if kind == "llama3":
+        lo, hi = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        out = []
+        for f in inv.tolist():
+            wavelen = 2 * math.pi / f
+            if wavelen > old / lo:
+                out.append(f / factor)
+            elif wavelen < old / hi:
+                out.append(f)
+            else:
+                smooth = (old / wavelen - lo) / (hi - lo)
+                out.append((1 - smooth) * f / factor + smooth * f)
+        return torch.tensor(out, dtype=torch.float32), 1.0
+    assert kind == "yarn", kind
+    beta_fast, beta_slow = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))
+
+    def correction_dim(rotations):
+        return rotary_dim * math.log(old / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+
+    low, high = correction_dim(beta_fast), correction_dim(beta_slow)
+    if scaling.get("truncate", True):
+        low, high = math.floor(low), math.ceil(high)
+    low, high = max(low, 0), min(high, rotary_dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = ((torch.arange(rotary_dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+    inv = inv / factor * ramp + inv * (1 - ramp)
+
+    def mscale(mult=1.0):
+        return 1.0 if factor <= 1.0 else 0.1 * mult * math.log(factor) + 1.0
+
+    att = scaling.get("attention_factor")
+    if att is None:
+        m, m_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+        att = mscale(float(m)) / mscale(float(m_all)) if m and m_all else mscale()
+    return inv, float(att)
+
+
+def partial_rotary(x, positions, rotary_dim, theta, act, scaling=None, interleaved=False):
     """Rotate the first ``rotary_dim`` dims of each head (split-half pairing), pass the
-    rest through untouched.  x: [T, heads, D].
+    rest through untouched.  x: [T, heads, D].  cos and sin carry the scaled encodings'
+    factor (src/sparseengine/layers/rotary_embedding.py:208-212).  ``interleaved``: pair i is
+    the adjacent dims (2i, 2i+1) and the results are written as split halves (:115-127).
 
     src/sparseengine/layers/rotary_embedding.py:104-112 (apply_rotary_emb),
     :129-167 (apply_partial_rotary_emb); cos/sin cache :190-222.
     """
-    inv = rope_inv_freq(rotary_dim, theta)
-    ang = positions.to(torch.float32).unsqueeze(-1) * inv  # [T, R/2]
-    cos = torch.cos(ang).unsqueeze(1)
-    sin = torch.sin(ang).unsqueeze(1)
+    inv, factor = rope_frequencies(rotary_dim, theta, scaling)
+    ang = positions.to(torch.float32).unsqueeze(-1) * inv.to(positions.device)  # [T, R/2]
+    cos = (torch.cos(ang) * factor).unsqueeze(1)
+    sin = (torch.sin(ang) * factor).unsqueeze(1)
     x = x.to(torch.float32)
     rot, rest = x[..., :rotary_dim], x[..., rotary_dim:]
-    x1, x2 = rot[..., : rotary_dim // 2], rot[..., rotary_dim // 2:]
+    if interleaved:
+        x1, x2 = rot[..., 0::2], rot[..., 1::2]
+    else:
+        x1, x2 = rot[..., : rotary_dim // 2], rot[..., rotary_dim // 2:]
     y1 = x1 * cos - x2 * sin
     y2 = x2 * cos + x1 * sin
     return torch.cat((_round(y1, act), _round(y2, act), rest), dim=-1)
@@ -111,8 +173,8 @@ def causal_attention(q, k, v, act, window: int | None = None):
     hkv = k.shape[1]
     group = hq // hkv
     scale = d ** -0.5
-    out = torch.empty(t, hq, d, dtype=torch.float32)
-    pos = torch.arange(t)
+    out = torch.empty(t, hq, d, dtype=torch.float32, device=q.device)
+    pos = torch.arange(t, device=q.device)
     mask = pos[None, :] <= pos[:, None]
     if window is not None:
         mask &= pos[None, :] > pos[:, None] - window
@@ -145,13 +207,11 @@ def router(x, gate_w, bias, top_k):
     score = p + bias.to(torch.float32)
     score = torch.where(torch.isnan(score), torch.full_like(score, float("inf")), score)
     t, e = score.shape
-    ids = torch.empty(t, top_k, dtype=torch.long)
-    for i in range(t):
-        row = score[i]
-        thr = torch.topk(row, top_k).values.min()
-        greater = [j for j in range(e) if row[j] > thr]
-        equal = [j for j in range(e) if row[j] == thr]
-        ids[i] = torch.tensor((greater + equal)[:top_k])
+    thr = torch.topk(score, top_k, dim=-1).values.min(-1, keepdim=True).values      # the k-th value
+    index = torch.arange(e, device=score.device).expand(t, e)
+    # sort key: strictly greater entries by ascending index, then ties by ascending index, then the rest
+    key = torch.where(score > thr, index, torch.where(score == thr, index + e, index + 2 * e))
+    ids = torch.sort(key, dim=-1).values[:, :top_k] % e
     w = p.gather(1, ids)
     w = w / w.sum(-1, keepdim=True)
     return ids, w, logits
@@ -168,17 +228,39 @@ def experts(x, ids, weights, w1, w3, w2, act):
     w1/w3: [E, I, H], w2: [E, H, I].
     """
     t, k = ids.shape
-    out = torch.zeros(t, w2.shape[1], dtype=torch.float32)
-    for slot in range(k):
-        for i in range(t):
-            e = int(ids[i, slot])
-            xi = x[i].to(torch.float32)
-            g = _round(w1[e].to(torch.float32) @ xi, act)
-            u = _round(w3[e].to(torch.float32) @ xi, act)
+    out = torch.zeros(t, w2.shape[1], dtype=torch.float32, device=x.device)
+    x = x.to(torch.float32)
+    for slot in range(k):                       # slot order: token i adds its slot-0 expert first, then slot 1, ...
+        col = ids[:, slot]
+        for e in torch.unique(col).tolist():    # the tokens that chose expert e in this slot, as one product
+            rows = (col == e).nonzero().squeeze(-1)
+            xi = x[rows]
+            g = _round(xi @ w1[e].to(torch.float32).t(), act)
+            u = _round(xi @ w3[e].to(torch.float32).t(), act)
             a = _round(_round(g / (1.0 + torch.exp(-g)), act) * u, act)
-            d = w2[e].to(torch.float32) @ a
-            out[i] += _round(d * weights[i, slot], act)
+            d = a @ w2[e].to(torch.float32).t()
+            out[rows] += _round(d * weights[rows, slot].unsqueeze(-1), act)
     return _round(out, act)
+
+
+def sampling_kept(row: torch.Tensor, top_k: int, top_p: float, temperature: float) -> torch.Tensor:
+    """Which tokens of one row of logits survive the sampler's cuts (a bool mask).
+
+    Sorted by logit / temperature, descending; top-k keeps the first k (0 = all); softmax over
+    those; top-p then drops an entry if the mass *before* it already exceeds top_p (so the
+    first entry always stays) (src/sparseengine/layers/sampler.py:101-118)."""
+    scaled = row.to(torch.float32) / temperature
+    order = torch.argsort(scaled, descending=True, stable=True)
+    keep = len(order) if top_k <= 0 else min(top_k, len(order))
+    s = scaled[order].clone()
+    s[keep:] = float("-inf")
+    p = torch.softmax(s, -1)
+    before = torch.cumsum(p, 0) - p
+    drop = torch.cumsum(p, 0) > top_p
+    drop = torch.cat((torch.tensor([False]), drop[:-1]))
+    mask = torch.zeros(len(order), dtype=torch.bool)
+    mask[order[:keep][~drop[:keep]]] = True
+    return mask
 
 
 def _layer_tensors(tensors, i, cfg):
@@ -196,9 +278,10 @@ def _layer_tensors(tensors, i, cfg):
         "kn": tensors[p + "self_attn.k_norm.weight"],
         "gate": tensors[moe + "gate.weight"],
         "bias": tensors[moe + "e_score_correction_bias"],
-        "w1": torch.stack([tensors[f"{moe}experts.{j}.w1.weight"] for j in range(e)]),
-        "w3": torch.stack([tensors[f"{moe}experts.{j}.w3.weight"] for j in range(e)]),
-        "w2": torch.stack([tensors[f"{moe}experts.{j}.w2.weight"] for j in range(e)]),
+        # the experts' matrices stacked [E, ...]; a caller with many large experts may give the stacks
+        # themselves under "<moe>experts.stacked.w1" (w3, w2) to save the copies
+        **{w: (tensors[f"{moe}experts.stacked.{w}"] if f"{moe}experts.stacked.{w}" in tensors else
+               torch.stack([tensors[f"{moe}experts.{j}.{w}.weight"] for j in range(e)])) for w in ("w1", "w3", "w2")},
     }
 
 
@@ -218,8 +301,9 @@ def attention_block(x, lt, cfg, positions, act):
     q = whole_projection_rms_norm(q, lt["qn"], eps, act).view(t, hq, d)
     k = whole_projection_rms_norm(k, lt["kn"], eps, act).view(t, hkv, d)
     v = v.view(t, hkv, d)
-    q = partial_rotary(q, positions, rot, theta, act)
-    k = partial_rotary(k, positions, rot, theta, act)
+    scaling = rope_scaling_of(cfg)
+    q = partial_rotary(q, positions, rot, theta, act, scaling)
+    k = partial_rotary(k, positions, rot, theta, act, scaling)
     o = causal_attention(q, k, v, act)
     return linear(o.reshape(t, hq * d), lt["wo"], act), (q, k, v)
 
@@ -239,7 +323,7 @@ def moe_block(x, lt, cfg, act, forced_ids=None, info=None):
         srt = score.sort(-1, descending=True).values
         info.setdefault("ids", []).append(ids)
         info.setdefault("margin", []).append(srt[:, k - 1] - srt[:, k] if srt.shape[1] > k
-                                             else torch.full((x.shape[0],), float("inf")))
+                                             else torch.full((x.shape[0],), float("inf"), device=x.device))
     if forced_ids is not None:
         ids = forced_ids.long()
         p = torch.sigmoid(logits).gather(1, ids)
@@ -248,8 +332,10 @@ def moe_block(x, lt, cfg, act, forced_ids=None, info=None):
 
 
 def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float32, forced_ids=None,
-            info=None) -> torch.Tensor:
-    """Logits [T, V] (float32) at every position of one whole sequence.
+            info=None, want=None) -> torch.Tensor:
+    """Logits [T, V] (float32) at every position of one whole sequence (``want``: only at these
+    positions, [len(want), V]; the final norm and the head are per position).  Runs where the
+    tensors live.
 
     ``forced_ids``: optional list (one entry per layer) of expert ids [T, k] to use
     instead of the router's own; ``info``: optional dict that receives the routers' own
@@ -259,9 +345,10 @@ def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float3
     src/sparseengine/models/qwen3.py:291-328: the residual stream is rounded to act
     after each add, the norm reads the unrounded sum.
     """
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    device = tensors["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
     t = ids.shape[0]
-    positions = torch.arange(t)
+    positions = torch.arange(t, device=device)
     eps = float(cfg.get("rms_norm_eps", 1e-6))
     tensors = {n: v.to(torch.float32) if v.dtype == torch.float32 else _round(v.to(torch.float32), act)
                for n, v in tensors.items()}
@@ -277,6 +364,9 @@ def forward(cfg: dict, tensors: dict, token_ids, act: torch.dtype = torch.float3
         hidden, _ = attention_block(x, lt, cfg, positions, act)
         x, residual = add_rms_norm(hidden, residual, lt["ln2"], eps, act)
         hidden = moe_block(x, lt, cfg, act, None if forced_ids is None else forced_ids[i], info)
+    if want is not None:
+        rows = torch.as_tensor(want, dtype=torch.long, device=device)
+        hidden, residual = hidden[rows], residual[rows]
     x, _ = add_rms_norm(hidden, residual, tensors["model.norm.weight"], eps, act)
     return linear(x, tensors["lm_head.weight"], act)
 

@@ -99,3 +99,37 @@ def test_tiny_random_override_file(tmp_path):
         path.write_text(json.dumps(bad))
         with pytest.raises(ValueError, match=msg):
             cfg.apply_tiny_random_overrides(raw)
+
+
+def test_scaled_rotary_tables_are_built_on_the_host_and_match_the_reference():
+    """linear / llama3 / yarn frequency scaling becomes a table of frequencies and a factor on
+    cos and sin: compared with the tables the reference's own code gave (tests/golden)."""
+    import os
+
+    import torch
+    from safetensors.torch import load_file
+
+    from golden.golden_cases import ROPE_SCALINGS
+    from sparseengine_b200.config.specs import RotarySpec
+    from sparseengine_b200.parts.base import make_position
+    from sparseengine_b200.parts.position import scaled_frequencies
+    g = load_file(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "m2_oracles.safetensors"))
+    for name, scaling in ROPE_SCALINGS.items():
+        inv, factor = scaled_frequencies(64, 5e6, scaling)
+        assert torch.allclose(inv, g[f"rope.{name}.inv_freq"], atol=0, rtol=2e-6), name
+        assert abs(factor - float(g[f"rope.{name}.factor"])) < 1e-6, name
+    # through the configuration: a yarn entry in config.json reaches the attention part's position encoding
+    cfg = dict(plain_m2.TINY_A, head_dim=64, rotary_dim=64, rope_theta=5e6, rope_scaling=ROPE_SCALINGS["yarn"])
+    typed, spec = load_model_spec(cfg)
+    pos = make_position(spec.layers[0].mixer.position, torch.float32)
+    args = pos.kernel_args("cpu")
+    assert torch.allclose(args.inv_freq, g["rope.yarn.inv_freq"], rtol=2e-6, atol=0)
+    assert abs(args.scale - float(g["rope.yarn.factor"])) < 1e-6 and args.pairing == "split_half"
+    assert load_model_spec(typed.to_dict())[0] == typed                 # and reads back from its own config.json
+    for bad in ({"rope_type": "dynamic", "factor": 2.0}, {"rope_type": "yarn", "factor": 2.0},
+                {"rope_type": "llama3", "factor": 2.0, "original_max_position_embeddings": 64, "low_freq_factor": 4.0,
+                 "high_freq_factor": 1.0}, {"rope_type": "linear", "factor": 0.5}):
+        with pytest.raises(ValueError):
+            load_model_spec(dict(plain_m2.TINY_A, rope_scaling=bad))
+    with pytest.raises(ValueError):
+        make_position(RotarySpec(rotary_dim=24, pairing="pairs_of_three"), torch.float32)

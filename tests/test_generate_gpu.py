@@ -205,11 +205,48 @@ def test_a_kernel_that_gave_up_is_reported_by_the_next_step(folder_a):
     llm = LLM(folder, dtype="bfloat16", page_size=4, num_kvcache_slots=64, max_model_len=32)
     llm.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
     llm.step()
-    ops.tc_error_flag("cuda:0").fill_(12)
+    ops.error_word("cuda:0").fill_(12)
     with pytest.raises(RuntimeError, match="timed out waiting on a barrier .role code 12"):
         llm.step()
-    llm.step()                                   # the word was cleared: the engine goes on
-    assert int(ops.tc_error_flag("cuda:0")) == 0
+    assert int(ops.error_word("cuda:0")) == 0             # the word was cleared
+    # the request of the void step was ended and gave everything back; the engine goes on
+    c = llm.runner.cache
+    assert llm.is_finished() and c.free_pages() == c.groups[0].pool.num_pages
+    c.check()
+    out = llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0]
+    assert len(out["token_ids"]) == 4
+
+
+def test_a_failed_read_with_a_step_queued_ahead_leaves_the_engine_consistent(folder_a):
+    """Host-side failure injection: while a batch only decodes, the next step is queued before
+    this step's tokens are read.  If that read raises, the step queued ahead is let finish, the
+    requests of the failed step are ended and give their pages back (their cache is one token
+    ahead of what the host knows), and the engine serves the next request as usual."""
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, _ = folder_a
+    llm = LLM(folder, dtype="float32", page_size=4, num_kvcache_slots=128, max_model_len=64, async_scheduling=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    want = llm.generate([[5, 6, 7]], sp)[0]["token_ids"]
+    ids = [llm.add_request(p, sp) for p in ([1, 2, 3], [4, 5, 6, 7])]
+    while llm.steps_ahead == 0 or llm._inflight is None:
+        llm.step()                                # until a step runs ahead of the one being read
+    real, calls = llm.sampler.collect, []
+
+    def broken(pending):
+        calls.append(pending)
+        if len(calls) == 1:
+            raise RuntimeError("injected")
+        return real(pending)
+    llm.sampler.collect = broken
+    with pytest.raises(RuntimeError, match="injected"):
+        llm.step()
+    llm.sampler.collect = real
+    assert len(calls) == 2                        # the failed read, then the step queued behind it
+    c = llm.runner.cache
+    assert llm._inflight is None and llm.is_finished()
+    assert c.free_pages() == c.groups[0].pool.num_pages and c.free_rows == c.max_rows
+    c.check()
+    assert llm.generate([[5, 6, 7]], sp)[0]["token_ids"] == want
 
 
 def test_logprobs_of_the_chosen_and_of_the_most_likely_tokens(folder_a):

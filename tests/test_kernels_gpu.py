@@ -369,7 +369,7 @@ def test_routed_experts(dtype, tokens, hidden, inter, experts, top_k, path):
     part.use_tensor_cores = None if path == "tensor_cores" else False
     assert part.tensor_cores_usable(x) == (path == "tensor_cores")
     out = part.run_experts(x, ids, wt)
-    ops.tc_check(DEV)
+    ops.error_check(DEV)
     ref = plain_m2.experts(x.float().cpu(), ids.cpu().long(), wt.cpu(), w13[:, :inter].float().cpu(),
                            w13[:, inter:].float().cpu(), w2.float().cpu(), dtype)
     torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype, 1e-5, 2e-2))
@@ -511,7 +511,7 @@ def test_tensor_core_experts_at_m2_layer_sizes(tokens):
                      torch.bfloat16)
     part.bind({"w13": w13, "w2": w2})
     fast = part.run_experts(x, ids, wt)
-    ops.tc_check(DEV)
+    ops.error_check(DEV)
     part.use_tensor_cores = False
     slow = part.run_experts(x, ids, wt)
     # outputs are bfloat16 values of size ~1 (ulp 2^-8..2^-6): a different order of the 32-bit
@@ -528,7 +528,7 @@ def test_tensor_core_dense_gemm(rows, n_out, k_dim, nt):
     w = rnd(n_out, k_dim, dtype=torch.bfloat16, scale=0.1, seed=2)
     out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=DEV)
     ops.gemm_tc_dense(x, w, out, nt)
-    ops.tc_check(DEV)
+    ops.error_check(DEV)
     ref = plain_m2.linear(x.float().cpu(), w.float().cpu(), torch.bfloat16)
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
@@ -598,7 +598,7 @@ def test_prefill_attention_tensor_cores(hq, hkv, d, page, window, impl):
     out = torch.zeros_like(q)
     fn(q.view(t, hq * d), cache, table, rows, cu_q, kv_len, out.view(t, hq * d), entries=len(q_lens),
        max_q_len=max(q_lens), num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
-    ops.tc_check(DEV)
+    ops.error_check(DEV)
     ref = _attention_reference(q.float().cpu(), [k.float().cpu() for k in ks], [v.float().cpu() for v in vs], q_lens,
                                starts, dtype, window)
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
@@ -644,7 +644,7 @@ def test_tensor_core_attention_far_key_and_window_edge(kernel, window):
             fn(q.view(q_len, hq * d), cache, table, rows, torch.tensor([0, q_len], dtype=torch.int32, device=DEV),
                torch.tensor([n], dtype=torch.int32, device=DEV), out.view(q_len, hq * d), entries=1, max_q_len=q_len,
                num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
-            ops.tc_check(DEV)
+            ops.error_check(DEV)
         got = out[-1].float().cpu()
         visible = far >= first_seen
         for g in range(hkv):
@@ -687,3 +687,187 @@ def test_top_logprobs(dtype):
         assert ids[k].tolist() == order
         torch.testing.assert_close(vals[k].cpu(), lp[r, order], atol=2e-5, rtol=1e-5)
     assert ids[1].tolist()[:3] == [3, 10, 700]
+
+
+# ---- indices the kernels are given: an entry outside the pool is not followed ---------------
+
+def _poisoned_setup(d, page, dtype, n=40, hkv=2):
+    """One request of ``n`` keys in a cache of 8 pages of which the kernels are told 4 belong to
+    the pool; block-table entry 1 names page 6: inside the allocation (nothing can fault, even
+    if a check were wrong), outside the declared pool.  Page 6 holds infinities, so a kernel
+    that followed the entry would show them in its output."""
+    assert n <= 3 * page + page
+    table = torch.tensor([[0, 6, 2, 3]], dtype=torch.int32, device=DEV)
+    cache = rnd(8, 2, hkv, page, d, dtype=dtype, seed=40)
+    cache[6] = float("inf")
+    rows = torch.zeros(1, dtype=torch.int32, device=DEV)
+    return table, rows, cache
+
+
+@pytest.mark.parametrize("kernel", ["qk_prep", "qk_prep_many", "plain", "decode", "prefill_mma_sync", "prefill_tcgen05",
+                                    "table_update"])
+def test_a_block_table_entry_outside_the_pool_is_not_followed(kernel):
+    """The entry is skipped and the kernel's code appears in the error word, which the next
+    check raises from.  With the true pool size the same call is clean."""
+    from sparseengine_b200.csrc import ops
+    ops.error_check(DEV)
+    hq, hkv, d, page = 4, 2, 128, 16
+    dtype = torch.float32 if kernel == "plain" else torch.bfloat16
+    table, rows, cache = _poisoned_setup(d, page, dtype)
+    n = 40                                                   # positions 16..31 live on the bad entry
+    for declared, code in ((4, {"qk_prep": 21, "qk_prep_many": 21, "plain": 22, "decode": 23, "prefill_mma_sync": 24,
+                                "prefill_tcgen05": 25, "table_update": 26}[kernel]), (8, 0)):
+        word = ops.error_word(DEV)
+        if kernel.startswith("qk_prep"):
+            t = 70 if kernel == "qk_prep_many" else 3
+            first = 31 - t + 1 if t <= 16 else 0             # few tokens: all on the bad entry's page
+            qkv = rnd(t, (hq + 2 * hkv) * d, dtype=dtype, seed=1)
+            q_out = torch.zeros(t, hq * d, dtype=dtype, device=DEV)
+            tbl = torch.tensor([[0, 6, 2, 3, 1]], dtype=torch.int32, device=DEV)
+            before = cache.clone()
+            ops.qk_prep(qkv, None, None, None, torch.arange(first, first + t, dtype=torch.int32, device=DEV),
+                        torch.zeros(t, dtype=torch.int32, device=DEV), rows, tbl, cache, q_out, num_heads=hq,
+                        num_kv_heads=hkv, head_dim=d, rotary_dim=0, eps=1e-6, rope_scale=1.0, page_size=page,
+                        num_pages=declared)
+            assert torch.equal(q_out, qkv[:, :hq * d])                   # the queries are written all the same
+            if declared == 4:
+                assert torch.equal(cache[6], before[6])                  # nothing was written through the bad entry
+            else:
+                assert not torch.equal(cache[6], before[6])
+        elif kernel == "table_update":
+            tbl = torch.full((2, 4), -1, dtype=torch.int32, device=DEV)
+            upd = torch.tensor([0, 1, 3, 1, 2, 6, 5, 0, 1, 1, 9, 2], dtype=torch.int32, device=DEV)   # page 6; row 5; index 9
+            ops.table_update(tbl, upd, 4, declared)
+            want = [[-1, 3, -1, -1], [-1, -1, 6 if declared == 8 else -1, -1]]
+            assert tbl.tolist() == want
+            code = 26                                                    # row 5 and index 9 are refused either way
+        else:
+            q = rnd(1 if kernel in ("plain", "decode") else 24, hq, d, dtype=dtype, seed=2)
+            t = q.shape[0]
+            out = torch.zeros_like(q)
+            kw = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, num_pages=declared)
+            if kernel in ("plain", "decode"):
+                pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+                seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+                if kernel == "plain":
+                    ops.paged_attention_plain(q.view(t, -1), cache, table, rows, seq, pos, out.view(t, -1), **kw)
+                else:
+                    ops.attn_decode(q.view(t, -1), cache, table, rows, seq, pos, out.view(t, -1), max_keys=n, **kw)
+            else:
+                fn = ops.attn_prefill_tc if kernel == "prefill_tcgen05" else ops.attn_prefill
+                fn(q.view(t, -1), cache, table, rows, torch.tensor([0, t], dtype=torch.int32, device=DEV),
+                   torch.tensor([n], dtype=torch.int32, device=DEV), out.view(t, -1), entries=1, max_q_len=t, **kw)
+            finite = bool(torch.isfinite(out.float()).all())
+            assert finite == (declared == 4)                            # followed, page 6's infinities would show
+        got = int(word.item())
+        assert got == code, (kernel, declared, got)
+        if code:
+            with pytest.raises(RuntimeError, match=f"code {code}"):
+                ops.error_check(DEV)
+        ops.error_check(DEV)                                             # the word was cleared
+
+
+@pytest.mark.parametrize("kernel", ["prefill_mma_sync", "prefill_tcgen05", "decode", "plain"])
+def test_pages_a_window_has_left_are_not_read(kernel):
+    """A windowed request gives back the pages its window has passed, and their block-table
+    entries stay on the device.  Such a page may already hold another request's values: here it
+    holds infinities, and (for another entry) an id outside the pool.  The output is the same
+    as with clean pages, and no code is written."""
+    from sparseengine_b200.csrc import ops
+    hq, hkv, d, page, window = 8, 2, 128, 16, 40
+    dtype = torch.float32 if kernel == "plain" else torch.bfloat16
+    n, q_len = 200, (1 if kernel in ("decode", "plain") else 37)
+    table, rows, _, _, cache = _cache_setup([n], hkv, d, page, dtype)
+    k, v = rnd(n, hkv, d, dtype=dtype, seed=1), rnd(n, hkv, d, dtype=dtype, seed=2)
+    pos = torch.arange(n, device=DEV)
+    pg = table[int(rows[0]), (pos // page).long()].long()
+    cache[pg, 0, :, (pos % page).long()] = k
+    cache[pg, 1, :, (pos % page).long()] = v
+    first_needed = (n - q_len) - window + 1                     # the oldest key the portion's first query sees
+    dead = list(range(first_needed // page))                    # table entries wholly before it
+    assert len(dead) >= 4
+    q = rnd(q_len, hq, d, dtype=dtype, seed=3)
+
+    def run():
+        out = torch.zeros_like(q)
+        kw = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5, window=window)
+        if kernel in ("decode", "plain"):
+            p1 = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+            seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+            if kernel == "plain":
+                ops.paged_attention_plain(q.view(q_len, -1), cache, table, rows, seq, p1, out.view(q_len, -1), **kw)
+            else:
+                ops.attn_decode(q.view(q_len, -1), cache, table, rows, seq, p1, out.view(q_len, -1), max_keys=window, **kw)
+        else:
+            fn = ops.attn_prefill_tc if kernel == "prefill_tcgen05" else ops.attn_prefill
+            fn(q.view(q_len, -1), cache, table, rows, torch.tensor([0, q_len], dtype=torch.int32, device=DEV),
+               torch.tensor([n], dtype=torch.int32, device=DEV), out.view(q_len, -1), entries=1, max_q_len=q_len, **kw)
+        ops.error_check(DEV)
+        return out
+
+    clean = run()
+    r = int(rows[0])
+    for idx in dead[:-1]:
+        cache[int(table[r, idx])] = float("inf")                # "another request's" values
+    table[r, dead[0]] = 10 ** 6                                 # and an entry that names no page at all
+    again = run()
+    assert torch.isfinite(again.float()).all()
+    assert torch.equal(again, clean)
+    qs = torch.zeros(n, hq, d)
+    qs[n - q_len:] = q.float().cpu()
+    ref = plain_m2.causal_attention(qs, k.float().cpu(), v.float().cpu(), dtype, window)[n - q_len:]
+    torch.testing.assert_close(again.float().cpu(), ref, **tol(dtype, 2e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["split_half", "interleaved", "interleaved_to_split_half"])
+@pytest.mark.parametrize("tokens", [5, 80])
+def test_qk_prep_pairings_frequency_tables_and_amplitude(dtype, pairing, tokens):
+    """The position encoding is data to the kernel: any table of frequencies (here a yarn table
+    from the plain implementation), a factor on cos and sin, and three ways of pairing dims."""
+    from sparseengine_b200.csrc import ops
+    hq, hkv, d, rot, page = 3, 1, 64, 48, 8
+    scaling = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64}
+    inv, amp = plain_m2.rope_frequencies(rot, 1e4, scaling)
+    table, rows, positions, token_seq, cache = _cache_setup([tokens], hkv, d, page, dtype, firsts=[100])
+    qkv = rnd(tokens, (hq + 2 * hkv) * d, dtype=dtype, seed=8)
+    q_out = torch.empty(tokens, hq * d, dtype=dtype, device=DEV)
+    ops.qk_prep(qkv, None, None, inv.to(DEV), positions, token_seq, rows, table, cache, q_out, num_heads=hq,
+                num_kv_heads=hkv, head_dim=d, rotary_dim=rot, eps=1e-6, rope_scale=amp, page_size=page, pairing=pairing)
+    x = qkv.float().cpu()[:, :hq * d].view(tokens, hq, d)
+    ref = plain_m2.partial_rotary(x, positions.cpu(), rot, 1e4, dtype, scaling, interleaved=pairing != "split_half")
+    if pairing == "interleaved":                        # results go back to the adjacent dims
+        r = ref[..., :rot].clone()
+        ref[..., 0:rot:2], ref[..., 1:rot:2] = r[..., :rot // 2], r[..., rot // 2:]
+    torch.testing.assert_close(q_out.float().cpu().view(tokens, hq, d), ref, **tol(dtype, 3e-5, 2e-2))
+    assert amp > 1.0 and torch.equal(q_out.float().cpu().view(tokens, hq, d)[..., rot:], x[..., rot:])
+    with pytest.raises(ValueError, match="pairing"):
+        ops.qk_prep(qkv, None, None, inv.to(DEV), positions, token_seq, rows, table, cache, q_out, num_heads=hq,
+                    num_kv_heads=hkv, head_dim=d, rotary_dim=rot, eps=1e-6, rope_scale=1.0, page_size=page, pairing="x")
+
+
+def test_size_limits_the_parts_check_are_the_launchers_own():
+    """The limits the parts refuse at construction restate what the launchers refuse; and at a
+    limit the kernel runs, one past it the launcher says so."""
+    from sparseengine_b200.csrc import ops
+    for name in ("rmsnorm_max_width", "router_max_experts", "router_max_unaligned_width", "moe_max_experts"):
+        assert ops.limit(name) == ops.LIMITS[name], name
+    w = ops.LIMITS["rmsnorm_max_width"]
+    x, wt = rnd(2, w + 8, seed=1), torch.ones(w + 8, device=DEV)
+    y = torch.empty(2, w, device=DEV)
+    ops.rmsnorm(x[:, :w].contiguous(), wt[:w].contiguous(), 1e-6, y)
+    ref = plain_m2.rms_norm(x[:, :w].cpu(), wt[:w].cpu(), 1e-6, torch.float32)
+    torch.testing.assert_close(y.cpu(), ref, atol=1e-5, rtol=1e-5)
+    with pytest.raises(ValueError, match="size this kernel does not support"):
+        ops.rmsnorm(x, wt, 1e-6, torch.empty_like(x))
+    # a router over rows wider than its shared-memory tile: the tiled kernel takes them, for few tokens too
+    hidden, experts = 7168, 16
+    xr, gate = rnd(3, hidden, seed=2), rnd(experts, hidden, scale=0.05, seed=3)
+    ids = torch.empty(3, 2, dtype=torch.int32, device=DEV)
+    wts = torch.empty(3, 2, dtype=torch.float32, device=DEV)
+    logits = torch.empty(3, experts, device=DEV)
+    ops.router(xr, gate, None, ids, wts, top_k=2, logits_out=logits)
+    torch.testing.assert_close(logits.cpu(), xr.cpu() @ gate.cpu().t(), atol=1e-4, rtol=1e-4)
+    one = torch.empty(1, experts, device=DEV)
+    ops.router(xr[:1].contiguous(), gate, None, ids[:1], wts[:1], top_k=2, logits_out=one)
+    assert torch.equal(one[0], logits[0])                      # and a token's logits do not depend on the batch

@@ -27,6 +27,7 @@ class CompressedRotarySpec:
     theta: float
     factor: float
     amplitude: float
+    pairing: str = "interleaved"
     kind: str = "compressed_rotary"
 
 
@@ -53,6 +54,12 @@ def _register_toy():
     from sparseengine_b200.parts.linear import linear
 
     class RunningMean(Mixer):
+        """State of its own, kept on the device and reached through the step's device tensors
+        only (no host list is read), so that the part may be captured in a CUDA graph: entry e
+        owns state row ``step.state_rows[e]`` and tokens ``cu_q[e] .. cu_q[e+1]``; token i
+        belongs to entry ``token_seq[i]``."""
+        graph_safe = True
+
         def parameters(self):
             return {"w": ParamSpec((self.spec.hidden_size, self.spec.hidden_size))}
 
@@ -61,32 +68,39 @@ def _register_toy():
 
         def forward(self, x, step, slot):
             h = self.spec.hidden_size
-            out = torch.empty_like(x)
-            a = 0
-            for row, n in zip(step.rows, step.q_lens):        # a request's tokens are processed in order
-                st = slot.state[row]
-                csum = torch.cumsum(x[a:a + n].float(), 0) + st[:h]
-                cnt = torch.arange(1, n + 1, device=x.device, dtype=torch.float32) + st[h]
-                out[a:a + n] = (csum / cnt[:, None]).to(x.dtype)
-                st[:h] = csum[-1]
-                st[h] = cnt[-1]
-                a += n
+            t = x.shape[0]
+            seq = step.token_seq.long()
+            rows = step.state_rows.long()
+            idx = torch.arange(t, device=x.device)
+            # per-request inclusive sums within the step: token i adds the tokens j <= i of its own request
+            same = (seq[:, None] == seq[None, :]) & (idx[None, :] <= idx[:, None])
+            csum = same.float() @ x.float() + slot.state[rows][seq, :h]
+            cnt = (idx - step.cu_q.long()[seq] + 1).float() + slot.state[rows][seq, h]
+            out = (csum / cnt[:, None]).to(x.dtype)
+            last = step.cu_q.long()[1:] - 1                      # each entry's last token
+            slot.state[rows] = torch.cat((csum[last], cnt[last, None]), 1)
             return linear(out, self.w)
 
     register_mixer("running_mean", RunningMean)
 
     # another position encoding: rotary with compressed positions (every frequency divided by
-    # `factor`) and the rotated dims scaled by `amplitude`; the attention part only asks its
-    # position encoding for (frequencies, number of rotated dims, amplitude)
+    # `factor`), the rotated dims scaled by `amplitude`, and adjacent dims (2i, 2i+1) as pairs; the
+    # attention part only asks its position encoding for (frequencies, number of rotated dims,
+    # amplitude, pairing)
     from sparseengine_b200.parts.base import PositionEncoding, register_position
 
     class CompressedRotary(PositionEncoding):
         graph_safe = True
 
+        _table = None
+
         def kernel_args(self, device):
+            from sparseengine_b200.parts.position import RotaryArgs
             r = self.spec.rotary_dim
-            inv = 1.0 / (self.spec.theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
-            return (inv / self.spec.factor).to(device), r, float(self.spec.amplitude)
+            if self._table is None:          # once: a graph-safe part copies nothing from the host in a step
+                inv = 1.0 / (self.spec.theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
+                self._table = (inv / self.spec.factor).to(device)
+            return RotaryArgs(self._table, r, float(self.spec.amplitude), self.spec.pairing)
 
     register_position("compressed_rotary", CompressedRotary)
 
@@ -193,10 +207,12 @@ def toy_tensors(seed=3):
     return t
 
 
-def toy_plain(t, tokens, act=torch.float32, forced=None):
+def toy_plain(t, tokens, act=torch.float32, forced=None, probs=None, exact_probs=None):
     """The toy model written out with the plain implementation's functions.  ``forced``:
     expert ids [T, k] for each of the two visits of the routed layer (the engine's own
-    choice, followed through near-ties)."""
+    choice, followed through near-ties).  ``probs``: a list that receives the router's
+    probabilities of each visit; ``exact_probs``: those of a 32-bit run, by which a bfloat16 run
+    measures how far rounding moves its routers' probabilities."""
     c = TOY
     n = len(tokens)
     t = {k: (v if k == "l1.gate" else plain_m2._round(v, act)) for k, v in t.items()}   # the router stays 32-bit
@@ -208,8 +224,11 @@ def toy_plain(t, tokens, act=torch.float32, forced=None):
         ang = pos.to(torch.float32).unsqueeze(-1) * inv
         cos, sin = (torch.cos(ang) * c["amplitude"]).unsqueeze(1), (torch.sin(ang) * c["amplitude"]).unsqueeze(1)
         x = x.to(torch.float32)
-        x1, x2 = x[..., :d // 2], x[..., d // 2:]
-        return torch.cat((plain_m2._round(x1 * cos - x2 * sin, act), plain_m2._round(x2 * cos + x1 * sin, act)), -1)
+        x1, x2 = x[..., 0::2], x[..., 1::2]                 # adjacent pairs, written back in place
+        out = torch.empty_like(x)
+        out[..., 0::2] = plain_m2._round(x1 * cos - x2 * sin, act)
+        out[..., 1::2] = plain_m2._round(x2 * cos + x1 * sin, act)
+        return out
 
     def attention(x, l, window, rotate, kv=None):
         qkv = plain_m2.linear(x, t[l + "qkv"], act)
@@ -249,12 +268,18 @@ def toy_plain(t, tokens, act=torch.float32, forced=None):
             # Where the plain router's gap is clear the engine must have chosen the same experts.
             # "Clear" in bfloat16: the router's input carries the rounding of several bfloat16
             # layers (about 1 % of its size), which moves a logit (40 terms, gate weights of
-            # 0.5) by about 0.03 and a probability near 0.3 by about 0.01.
+            # 0.5) by about 0.03 and a probability near 0.3 by about 0.01; where this request's
+            # own bfloat16 and 32-bit probabilities differ by more (measured, when the 32-bit ones
+            # are given), twice that difference.
             clear = 2e-3 if act == torch.float32 else 1e-2
+            if exact_probs is not None:
+                clear = max(clear, 2 * float((p - exact_probs[len(visits)]).abs().max()))
             for i in range(n):
                 if gap[i] > clear:
                     assert sorted(own[i].tolist()) == sorted(thr_ids[i].tolist()), (len(visits), i, float(gap[i]))
         visits.append(1)
+        if probs is not None:
+            probs.append(p)
         w = p.gather(1, thr_ids) * c["routed_scale"]
         return plain_m2.experts(x, thr_ids, w, t["l1.w13"][:, :inter], t["l1.w13"][:, inter:], t["l1.w2"], act)
 
@@ -317,8 +342,14 @@ def test_toy_model_steps_like_its_plain_form(toy_folder, dtype):
         runner = build_runner(folder, dtype=dtype, page_size=page, num_pages=tu.max_live_tokens(steps) // page,
                               max_rows=4)
         got, routed = tu.run_trace_runner(runner, steps, capture=True)
-        ref = {sid: toy_plain(t, toks, act, routed[sid] if dtype == "bfloat16" else None).numpy()
-               for sid, toks in seqs.items()}
+        ref = {}
+        for sid, toks in seqs.items():
+            if dtype == "bfloat16":
+                exact = []
+                toy_plain(t, toks, probs=exact)
+                ref[sid] = toy_plain(t, toks, act, routed[sid], exact_probs=exact).numpy()
+            else:
+                ref[sid] = toy_plain(t, toks, act).numpy()
         # The toy's logits are about ten times larger than the tiny M2 models' (tied head on an
         # embedding of std 0.5) and it runs six visits without a QK norm: its plain form in
         # bfloat16 differs from its plain form in float32 by 0.02-0.04 on average and 0.1-0.26 at
@@ -331,6 +362,27 @@ def test_toy_model_steps_like_its_plain_form(toy_folder, dtype):
         win = [g for g in runner.cache.groups if g.window][0]
         assert win.pool.reused_total > 0                          # windowed pages come back while a request lives
         runner.cache.check()
+
+
+def test_toy_stateful_mixer_decodes_in_cuda_graphs(toy_folder):
+    """A mixer with state of its own that reads the step's device tensors only declares itself
+    graph-safe, and the whole toy model's decode steps replay CUDA graphs: same logits as launch
+    by launch, and as the plain form."""
+    from sparseengine_b200.engine.factory import build_runner
+    folder, t = toy_folder
+    seqs = {f"s{i}": tu.random_prompt(TOY["vocab_size"], n, 40 + i) for i, n in enumerate([45, 38, 50])}
+    steps = tu.trace_mixed(seqs, live=3, chunk=9, decode_tail=30, seed=2)
+    out = {}
+    for graphs in (True, False):
+        runner = build_runner(folder, dtype="float32", page_size=4, num_pages=tu.max_live_tokens(steps) // 4, max_rows=4,
+                              decode_graphs=graphs)
+        assert runner.decode_graphs == graphs
+        out[graphs] = tu.run_trace_runner(runner, steps)
+        assert (runner.graph_replays > 10) == graphs
+    ref = {sid: toy_plain(t, toks).numpy() for sid, toks in seqs.items()}
+    tu.compare(out[True], ref, 2e-5, 2e-5, what="toy with graphs")
+    for k in out[True]:
+        assert np.abs(out[True][k] - out[False][k]).max() <= 1e-6, k
 
 
 # ---- the built-in parts alone -----------------------------------------------------------
@@ -415,9 +467,11 @@ def test_norm_and_position_parts_alone():
     ry, rr = plain_m2.add_rms_norm(x, r, w, 1e-5, torch.float32)
     assert torch.allclose(y.cpu(), ry, atol=1e-6) and torch.equal(res.cpu(), rr)
     pos = make_position(RotarySpec(rotary_dim=24, theta=5e6), torch.float32)
-    inv, rot, scale = pos.kernel_args(DEV)
-    assert rot == 24 and scale == 1.0 and torch.equal(inv.cpu(), plain_m2.rope_inv_freq(24, 5e6))
+    args = pos.kernel_args(DEV)
+    assert args.rotary_dim == 24 and args.scale == 1.0 and args.pairing == "split_half"
+    assert torch.equal(args.inv_freq.cpu(), plain_m2.rope_inv_freq(24, 5e6))
+    assert make_position(RotarySpec(rotary_dim=24, pairing="interleaved"), torch.float32).kernel_args(DEV).pairing == "interleaved"
     with pytest.raises(ValueError):
-        make_position(RotarySpec(rotary_dim=24, pairing="interleaved"), torch.float32)
+        make_position(RotarySpec(rotary_dim=24, pairing="triples"), torch.float32)
     with pytest.raises(ValueError, match="no norm registered"):
         make_norm(type("S", (), {"kind": "layer_norm"})(), torch.float32)

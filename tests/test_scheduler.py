@@ -166,6 +166,22 @@ def test_abort_frees_everything():
     cm.check()
 
 
+def test_a_failed_step_ends_its_requests_and_frees_them():
+    sched, cm = make(num_pages=16, max_num_batched_tokens=64)
+    sched.add(seq(0, 5, max_tokens=8))
+    sched.add(seq(1, 6, max_tokens=8))
+    run_step(sched, cm)
+    plan = sched.schedule()                      # a decode step whose result never arrives
+    for it in plan.items:
+        cm.reserve(it.seq.seq_id, it.n_tokens)
+        cm.commit(it.seq.seq_id, it.n_tokens)
+    ended = sched.fail(plan, "error")
+    assert [s.seq_id for s in ended] == [0, 1] and all(s.finish_reason == "error" for s in ended)
+    assert sched.is_finished() and cm.free_pages() == 16 and cm.free_rows == cm.max_rows
+    cm.check()
+    assert sched.fail(plan) == []                # nothing of it runs any more
+
+
 def test_max_decoding_seqs_blocks_new_prompts():
     sched, cm = make(max_num_seqs_in_batch=4, max_decoding_seqs=1)
     sched.add(seq(0, 3, max_tokens=3, ignore_eos=True))

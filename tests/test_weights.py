@@ -90,6 +90,25 @@ def test_mtp_tensors_are_skipped_and_counted(tmp_path):
     assert sorted(rep.skipped) == ["model.layers.2.self_attn.q_proj.weight", "model.mtp_modules.0.norm.weight"]
 
 
+def test_mtp_rule_follows_the_layer_index_and_the_stated_number_of_modules(tmp_path):
+    """A tensor of ``model.layers.<i>.`` with i past the layers is a multi-token-prediction
+    tensor whatever i is; when config.json states ``num_mtp_modules`` an index past those
+    modules is not explained by the configuration and is reported as unexpected."""
+    tensors = tu.make_model_folder(str(tmp_path), "A")
+    t = dict(tensors)
+    t["model.layers.40.mlp.w.weight"] = torch.zeros(2)
+    save_file(t, os.path.join(str(tmp_path), "model.safetensors"))
+    rep = load_weights(_model(plain_m2.TINY_A), str(tmp_path), "cpu")
+    assert rep.skipped == ["model.layers.40.mlp.w.weight"]
+    with pytest.raises(WeightLoadError) as e:
+        load_weights(_model(dict(plain_m2.TINY_A, num_mtp_modules=3)), str(tmp_path), "cpu")
+    assert e.value.unexpected == ["model.layers.40.mlp.w.weight"]
+    t["model.layers.4.mlp.w.weight"] = t.pop("model.layers.40.mlp.w.weight")
+    save_file(t, os.path.join(str(tmp_path), "model.safetensors"))
+    rep = load_weights(_model(dict(plain_m2.TINY_A, num_mtp_modules=3)), str(tmp_path), "cpu")
+    assert rep.skipped == ["model.layers.4.mlp.w.weight"]
+
+
 def test_sharded_checkpoint_and_duplicates(tmp_path):
     tensors = tu.make_model_folder(str(tmp_path), "A")
     os.remove(os.path.join(str(tmp_path), "model.safetensors"))
