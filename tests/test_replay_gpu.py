@@ -13,9 +13,8 @@ import trace_util as tu
 pytestmark = pytest.mark.gpu
 
 ACT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-# 32-bit: only the order of sums differs.  bfloat16: logits are bfloat16 values (8 bits of
-# mantissa) behind several layers of bfloat16 activations.
-TOL = {"float32": (1e-5, 1e-5), "bfloat16": (2e-2, 2e-2)}
+# Bounds: trace_util.compare_in_dtype (32-bit: the order of sums; bfloat16: a share of the
+# logits' root mean square).
 LENGTHS = [5, 9, 13, 47, 70, 33]
 
 
@@ -110,7 +109,7 @@ def test_every_way_of_cutting_gives_the_plain_logits(folders, name, dtype, cut):
             assert runner.graph_replays > 0        # single-token steps replay CUDA graphs
     assert len(got) == sum(len(t) for t in seqs.values())
     ref = reference(name, dtype, tensors, seqs, routed)
-    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} {cut}")
+    tu.compare_in_dtype(got, ref, dtype, what=f"{name} {dtype} {cut}")
     pool = runner.cache.groups[0].pool
     assert pool.free == pool.num_pages and pool.reused_total > 0      # everything came back; pages were reused
     runner.cache.check()
@@ -149,7 +148,7 @@ def test_random_configurations_in_32_bit(seed, tmp_path):
         runner = runner_for(str(tmp_path), name, "float32", steps)
         got = tu.run_trace_runner(runner, steps)
         ref = reference(name, "float32", tensors, seqs)
-        tu.compare(got, ref, *TOL["float32"], what=f"{cfg}")
+        tu.compare_in_dtype(got, ref, "float32", what=f"{cfg}")
         runner.cache.check()
     finally:
         del tu.TINY[name]
@@ -175,7 +174,7 @@ def test_random_schedules_give_the_plain_logits(folders, name, dtype, seed):
         got = tu.run_trace_runner(runner, steps)
     assert len(got) == sum(len(e["want"]) for s in steps for e in s["entries"])
     ref = reference(name, dtype, tensors, seqs, routed)
-    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} random schedule {seed}")
+    tu.compare_in_dtype(got, ref, dtype, what=f"{name} {dtype} random schedule {seed}")
     pool = runner.cache.groups[0].pool
     assert pool.free == pool.num_pages
     runner.cache.check()
@@ -219,7 +218,7 @@ def test_long_portions_through_the_tensor_core_attention(folders, name, dtype):
     else:
         assert "se_paged_attention_plain" in took and "se_moe_grouped_gemm_plain" in took
     ref = reference(name, dtype, tensors, seqs, routed)
-    tu.compare(got, ref, *TOL[dtype], what=f"{name} {dtype} long portions")
+    tu.compare_in_dtype(got, ref, dtype, what=f"{name} {dtype} long portions")
     assert len(got) == 4 + 2 + 3 + 1 + 2 + 18
     ops.error_check("cuda:0")
 
@@ -263,8 +262,8 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     else:
         got = tu.run_trace_runner(runner_for(folder, "A", dtype, steps), steps)
     ref = reference("A", dtype, tensors, {"d": toks}, routed)
-    tu.compare({k: v for k, v in got.items() if k[1] < 3}, ref, *TOL[dtype], what="first tokens")
-    tu.compare(got, ref, *TOL[dtype], what="long decoding")
+    tu.compare_in_dtype({k: v for k, v in got.items() if k[1] < 3}, ref, dtype, what="first tokens")
+    tu.compare_in_dtype(got, ref, dtype, what="long decoding")
 
 
 def test_out_of_pages_changes_nothing(folders):
@@ -304,7 +303,7 @@ def test_trace_run_program(folders, dtype, tmp_path):
         kept = {k: v for k, v in got.items() if k[1] < upto[k[0]]}
         assert len(kept) >= 5
         got = kept
-    tu.compare(got, reference("B", dtype, tensors, seqs), *TOL[dtype], what=f"trace_run {dtype}")
+    tu.compare_in_dtype(got, reference("B", dtype, tensors, seqs), dtype, what=f"trace_run {dtype}")
 
 
 @pytest.mark.parametrize("dtype", list(ACT))

@@ -290,3 +290,27 @@ def compare(got: dict, ref: dict, atol: float, rtol: float, what: str = ""):
                                  f"plain gives {want[j]!r} (|diff| {err[j]:.3e} > {lim[j]:.3e})")
         worst = max(worst, float(err.max()))
     return worst
+
+
+# bfloat16 against the plain implementation's bfloat16: both round at the same points, but sums
+# inside a product run in another order, so values that land near the middle between two
+# bfloat16 numbers round apart (half a unit in the last place, 2^-9 of the value), and the
+# difference travels on through the layers.  The bound is stated in units of the logits' own
+# size: a share of their root mean square over the compared rows, plus one unit in the last
+# place (2^-7) of the logit itself.
+BF16_SHARE_OF_RMS = 0.05
+BF16_ULP = 2.0 ** -7
+
+
+def compare_in_dtype(got: dict, ref: dict, dtype: str, what: str = "") -> float:
+    """``compare`` with the bounds of the precision: 32-bit 1e-5 (the order of sums only);
+    bfloat16 relative to the root mean square of the reference rows that are compared.
+    Returns the worst difference in units of that root mean square."""
+    rows = np.stack([ref[sid][p] for (sid, p) in got])
+    rms = float(np.sqrt(np.mean(rows.astype(np.float64) ** 2)))
+    if dtype == "float32":
+        worst = compare(got, ref, 1e-5, 1e-5, what)
+    else:
+        worst = compare(got, ref, BF16_SHARE_OF_RMS * rms, BF16_ULP, what)
+    print(f"[compare] {what}: logits rms {rms:.4f}, worst |diff| {worst:.3e} = {worst / max(rms, 1e-30):.4f} rms")
+    return worst / max(rms, 1e-30)
