@@ -168,7 +168,7 @@ def run_ours(args) -> dict:
     def route_counters():
         """(experts that got a row, routing builds) summed over the layers, from the device."""
         torch.cuda.synchronize()
-        got = [f.route_stats.tolist() if f.route_stats is not None else [0, 0] for f in ffs]
+        got = [(f.route_stats + f.route_stats_large).tolist() if f.route_stats is not None else [0, 0] for f in ffs]
         return sum(g[0] for g in got), sum(g[1] for g in got)
 
     def fill(seq_ids, ctx):

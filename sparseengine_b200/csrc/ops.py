@@ -390,6 +390,27 @@ def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max
     return out
 
 
+PAIR_TILE_ROWS = 256      # activation rows per tile of the kernel that runs on pairs of SMs (csrc/gemm_tc_pair.cu)
+
+
+def moe_grouped_gemm_pair_supported(k_dim: int, n_out: int) -> bool:
+    f = library().se_moe_grouped_gemm_pair_supported
+    f.restype = _I
+    f.argtypes = [_I, _I]
+    return bool(f(k_dim, n_out))
+
+
+def moe_grouped_gemm_pair(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim):
+    """The grouped expert GEMM on pairs of SMs (``tcgen05.mma.cta_group::2``, tiles of 256 x 256); the
+    tile list in ``ws`` must have been built with ``PAIR_TILE_ROWS`` rows per tile."""
+    _check(_fn("se_moe_grouped_gemm_pair", "i" "pppppppppp" "iiiii" "p")(
+        mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
+        _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
+        _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(a.device)),
+        a.shape[0], experts, max_tiles, n_out, k_dim, _stream()), "moe_grouped_gemm_pair")
+    return out
+
+
 def gemm_tc_dense(x, w, out, nt: int = 128):
     rows, k_dim = x.shape
     n_out = w.shape[0]

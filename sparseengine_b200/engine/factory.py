@@ -78,6 +78,9 @@ KERNEL_TUNING_KEYS = {
     "attention_portion_min_tokens": "portion_min_tokens",               # ... and smaller ones whose longest entry has this many tokens
     "attention_portion_min_average": "portion_min_average",             # ... and this many tokens per entry on average
     "gemv_max_out_features": None,                                      # few-row projections wider than this take the library product
+    "router_tensor_core_min_tokens": "split_router_min_tokens",         # prompt steps from this size take router logits from tensor cores
+    "moe_pair_min_rows": "pair_min_rows",                               # (token, slot) rows from which experts may run on pairs of SMs
+    "moe_pair_min_rows_per_expert": "pair_min_rows_per_expert",         # ... if the experts that get rows have this many each
 }
 
 

@@ -878,3 +878,78 @@ def test_size_limits_the_parts_check_are_the_launchers_own():
     one = torch.empty(1, experts, device=DEV)
     ops.router(xr[:1].contiguous(), gate, None, ids[:1], wts[:1], top_k=2, logits_out=one)
     assert torch.equal(one[0], logits[0])                      # and a token's logits do not depend on the batch
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,experts,top_k", [
+    (8, 64, 64, 2, 1), (40, 128, 136, 2, 2), (300, 256, 192, 3, 2), (333, 200, 72, 5, 3), (700, 3072, 1536, 8, 2),
+    (2500, 3072, 1536, 64, 8), (4100, 3072, 1536, 256, 8)])
+def test_experts_on_pairs_of_sms(tokens, hidden, inter, experts, top_k):
+    """The grouped GEMMs on pairs of SMs (tcgen05.mma.cta_group::2, tiles of 256 x 256: gate and up
+    rows of the same features side by side in one accumulator) against the plain implementation's
+    experts: tiles of a few rows and of 256, experts without rows, widths that are no multiple of
+    the 128-feature block, several items per pair (the accumulators and the exchange buffers
+    alternate across items)."""
+    from sparseengine_b200.config.specs import MoESpec
+    from sparseengine_b200.csrc import ops
+    from sparseengine_b200.parts.moe import SparseMoE
+    g = torch.Generator(device=DEV).manual_seed(tokens)
+    w13 = (torch.randn(experts, 2 * inter, hidden, generator=g, device=DEV) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(experts, hidden, inter, generator=g, device=DEV) * 0.05).to(torch.bfloat16)
+    x = torch.randn(tokens, hidden, generator=g, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(experts, generator=g, device=DEV)[:top_k] for _ in range(tokens)]).int()
+    if experts >= 5:                                 # an expert without rows: its tokens go to a neighbour they do not have yet
+        for t in (ids == 1).any(-1).nonzero().view(-1).tolist():
+            spare = next(e for e in range(experts) if e != 1 and e not in ids[t].tolist())
+            ids[t][ids[t] == 1] = spare
+    wt = torch.rand(tokens, top_k, generator=g, device=DEV)
+    part = SparseMoE(MoESpec(hidden_size=hidden, num_experts=experts, top_k=top_k, intermediate_size=inter), torch.bfloat16)
+    part.bind({"w13": w13, "w2": w2})
+    part.pair_min_rows, part.pair_min_rows_per_expert = 1, 0
+    before = ops.calls.get("se_moe_grouped_gemm_pair", 0)
+    out = part.run_experts(x, ids, wt)
+    ops.error_check(DEV)
+    assert ops.calls.get("se_moe_grouped_gemm_pair", 0) == before + 2
+    ref = plain_m2.experts(x.float(), ids.long(), wt, w13[:, :inter], w13[:, inter:], w2, torch.bfloat16)
+    rms = float(ref.pow(2).mean().sqrt())
+    torch.testing.assert_close(out.float(), ref, atol=2e-2 * rms, rtol=2.0 ** -7)
+    assert (out.float() - ref).abs().mean() < 2e-3 * rms
+    part.pair_min_rows = None                        # and the one-CTA kernel gives the same values to rounding
+    one = part.run_experts(x, ids, wt)
+    torch.testing.assert_close(out.float(), one.float(), atol=2e-2 * rms, rtol=2.0 ** -7)
+
+
+@pytest.mark.parametrize("tokens,hidden,experts,top_k", [(256, 3072, 256, 8), (1000, 3072, 256, 8), (300, 1024, 40, 3)])
+def test_router_logits_from_tensor_cores_are_32_bit_accurate(tokens, hidden, experts, top_k):
+    """Prompt steps take their router logits from the tensor cores: the 32-bit gate as three
+    bfloat16 terms, K in chunks of at most 512 whose partial sums are added in 32-bit.  Against a
+    64-bit product the error stays under 6e-6 (logits of size 1), and the experts are those of
+    the 64-bit scores wherever the gap to the next score is above 1e-5."""
+    from sparseengine_b200.config.specs import MoESpec
+    from sparseengine_b200.parts.moe import SparseMoE
+    g = torch.Generator(device=DEV).manual_seed(3)
+    gate = torch.randn(experts, hidden, generator=g, device=DEV) * (1.1 / math.sqrt(hidden))
+    bias = torch.randn(experts, generator=g, device=DEV) * 0.05
+    x = torch.randn(tokens, hidden, generator=g, device=DEV).to(torch.bfloat16)
+    part = SparseMoE(MoESpec(hidden_size=hidden, num_experts=experts, top_k=top_k, intermediate_size=64), torch.bfloat16)
+    part.bind({"gate": gate, "selection_bias": bias})
+    assert part._split_gate() is not None and tokens >= part.split_router_min_tokens
+    ids, w = part.route(x)
+    ref_logits = x.double() @ gate.double().t()
+    split = part._split_gate()
+    chunks, kc, _ = split.shape
+    parts = torch.bmm(x.view(tokens, chunks, kc).transpose(0, 1), split, out_dtype=torch.float32)
+    logits = parts.view(chunks, tokens, 3, experts).sum(dim=(0, 2))
+    assert float((logits.double() - ref_logits).abs().max()) < 6e-6
+    p = torch.sigmoid(ref_logits)
+    score = p + bias.double()
+    srt = score.sort(-1, descending=True)
+    gap = srt.values[:, top_k - 1] - srt.values[:, top_k]
+    want = srt.indices[:, :top_k].sort(-1).values
+    same = (ids.long().sort(-1).values == want).all(-1)
+    assert bool(same[gap > 1e-5].all()) and int((gap > 1e-5).sum()) > tokens * 0.9
+    sel = p.gather(1, ids.long())
+    torch.testing.assert_close(w.double(), sel / sel.sum(-1, keepdim=True), atol=1e-5, rtol=1e-5)
+    # few tokens take the kernels with the fixed order of sums: the same experts
+    part.split_router_min_tokens = None
+    ids2, _ = part.route(x)
+    assert bool((ids2.long().sort(-1).values == want)[gap > 1e-5].all())
