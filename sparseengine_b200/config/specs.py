@@ -107,12 +107,19 @@ class DenseMLPSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: mixer and feed-forward between two norms, pre-norm residual block."""
+    """One layer: its parts and the name of their arrangement in a block.
+
+    The built-in arrangement ``pre_norm`` takes a mixer and a feed-forward between two norms.
+    An arrangement with further parts (a norm after each sublayer, a second feed-forward beside
+    the first, ...) finds their specs under ``extra`` by the names it gives them, builds them with
+    the same registries, and lists them in its ``parts()``; their checkpoint tensors go into
+    ``sources`` under "<part name>.<parameter>" like everyone's."""
     mixer: Any
     feed_forward: Any
     mixer_norm: Any
     feed_forward_norm: Any
     arrangement: str = "pre_norm"
+    extra: dict = field(default_factory=dict)       # part name -> spec, for arrangements with more parts
     # part-local parameter name -> tuple[Source, ...]; keys are "<part>.<param>" with
     # part in {"mixer", "feed_forward", "mixer_norm", "feed_forward_norm"}.
     sources: dict = field(default_factory=dict)
@@ -144,6 +151,8 @@ class ModelSpec:
     final_norm_source: str = "model.norm.weight"
     embed_source: str = "model.embed_tokens.weight"
     head_source: Optional[str] = "lm_head.weight"   # None = tied to the embedding
+    embed_scale: float = 1.0                        # the embedded tokens are multiplied by this (in the activation type)
+    logit_softcap: Optional[float] = None           # c: logits become c * tanh(logits / c), in 32-bit
     ignored_prefixes: tuple = ()                    # checkpoint names skipped at load
     ignored_rule: Optional[Any] = None              # name -> bool: further names skipped at load
     stored_dtype: str = "bfloat16"

@@ -39,12 +39,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     constexpr int kTileBytes = kTileKeys * D * 2;
     extern __shared__ __align__(128) uint8_t smem[];
 
-    const int entry = blockIdx.z, kvh = blockIdx.y;
+    // Blocks start in the order of their index, x fastest: the KV heads are x, and the row tiles
+    // are y taken from the end, so that the tiles with the most keys (the last rows of a causal
+    // portion) start first and the short ones fill the tail of the launch.
+    const int entry = blockIdx.z, kvh = blockIdx.x;
     const int group = hq / hkv;
     const int tok0 = cu_q[entry];
     const int q_len = cu_q[entry + 1] - tok0;
     const int total_rows = q_len * group;
-    const int row_base = blockIdx.x * kTileRows;
+    const int row_base = (int)(gridDim.y - 1 - blockIdx.y) * kTileRows;
     if (row_base >= total_rows) return;
     const int kv_end = kv_len[entry];                 // keys in the cache after this step's writes
     const int q_start = kv_end - q_len;               // position of the portion's first token
@@ -246,7 +249,9 @@ static int launch(const void* q, const void* cache, const int* table, int table_
         configured = true;
     }
     const int group = hq / hkv;
-    dim3 grid(ceil_div(max_q_len * group, kTileRows), hkv, entries);
+    const int row_tiles = ceil_div(max_q_len * group, kTileRows);
+    if (row_tiles > 65535) return SE_ERR_UNSUPPORTED;
+    dim3 grid(hkv, row_tiles, entries);
     attn_prefill_kernel<D><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
         (__nv_bfloat16*)out, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages, error);

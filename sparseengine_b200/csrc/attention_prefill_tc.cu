@@ -144,12 +144,15 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
 
-    const int entry = blockIdx.z, kvh = blockIdx.y;
+    // Blocks start in the order of their index, x fastest: the KV heads are x, and the row tiles
+    // are y taken from the end, so that the tiles with the most keys (the last rows of a causal
+    // portion) start first and the short ones fill the tail of the launch.
+    const int entry = blockIdx.z, kvh = blockIdx.x;
     const int group = hq / hkv;
     const int tok0 = cu_q[entry];
     const int q_len = cu_q[entry + 1] - tok0;
     const int total_rows = q_len * group;
-    const int row_base = blockIdx.x * (kTiles * kRows);
+    const int row_base = (int)(gridDim.y - 1 - blockIdx.y) * (kTiles * kRows);
     if (row_base >= total_rows) return;
     const int kv_end = kv_len[entry];
     const int q_start = kv_end - q_len;
@@ -441,7 +444,9 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
         configured = true;
     }
     const int group = hq / hkv;
-    dim3 grid(se::ceil_div(max_q_len * group, kTiles * kRows), hkv, entries);
+    const int row_tiles = se::ceil_div(max_q_len * group, kTiles * kRows);
+    if (row_tiles > 65535) return SE_ERR_UNSUPPORTED;
+    dim3 grid(hkv, row_tiles, entries);
     attn_prefill_tc_kernel<<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
         (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages);

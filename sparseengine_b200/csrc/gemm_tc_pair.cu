@@ -13,8 +13,9 @@
 //   MODE_GATE_UP  a CTA's 128 A rows are 64 gate rows and the 64 up rows of the same output
 //                 features (two TMA boxes), so one accumulator (256 columns) holds both and the
 //                 other 256 columns of tensor memory take the next item: the SwiGLU epilogue of
-//                 item j runs while the MMAs of item j + 1 do.  Warps that own the up lanes
-//                 hand their values to the warps that own the gate lanes through shared memory.
+//                 item j runs while the MMAs of item j + 1 do.  The warps that own the gate lanes and
+//                 those that own the up lanes exchange their values through shared memory and share
+//                 the SiLU and the stores.
 //   MODE_DOWN     128 rows of w2[e] per CTA; epilogue multiplies by the routing weight.
 //
 // Work items (tile of activation rows x block of output features) are dealt round-robin to
@@ -168,8 +169,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ float route_s[2][kTileN];
-    // [buffer][column][feature] (lanes walk features); only the gate/up epilogue exchanges values
-    __shared__ __align__(16) float xch_s[2][kXchCols][MODE == MODE_GATE_UP ? kCtaFeatures : 1];
+    // [buffer][gate | up][column][feature] (lanes walk features); only the gate/up epilogue exchanges values
+    __shared__ __align__(16) __nv_bfloat16 xch_s[2][2][kXchCols][MODE == MODE_GATE_UP ? kCtaFeatures : 1];
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * kStages]), acc_empty0 = smem_u32(&bars[2 * kStages + 2]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -301,32 +302,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * kTileN);
             if (MODE == MODE_GATE_UP) {
-                // lanes 0-63 hold gate rows, lanes 64-127 the up rows of the same features
+                // Lanes 0-63 hold gate rows, lanes 64-127 the up rows of the same features.  Both
+                // halves put their values (rounded to bfloat16, as the pipeline rounds them) into
+                // shared memory, then every thread takes one feature and half of the chunk's
+                // columns, so all four warps share the SiLU and the stores.
                 const bool is_up = et >= kCtaFeatures;
                 const int f = et & (kCtaFeatures - 1);
                 const int n = nb * kItemFeatures + (int)rank * kCtaFeatures + f;
+                const int j0 = is_up ? kXchCols / 2 : 0;                     // this thread's columns of a chunk
                 // `chunk` runs on across items: the two exchange buffers alternate without a gap
                 for (int c0 = 0; c0 < valid; c0 += kXchCols, ++chunk) {      // uniform over the 128 threads
                     uint32_t v[32];
                     tmem_ld32(taddr + c0, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    auto xch = xch_s[chunk & 1];
-                    if (is_up) {
+                    auto mine = xch_s[chunk & 1][is_up ? 1 : 0];
 #pragma unroll
-                        for (int j = 0; j < kXchCols; ++j) xch[j][f] = round_act<__nv_bfloat16>(__uint_as_float(v[j]));
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");           // the up values of this chunk are there
-                    if (!is_up && n < p.n_out) {
+                    for (int j = 0; j < kXchCols; ++j) mine[j][f] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                    asm volatile("bar.sync 1, 128;" ::: "memory");           // both halves of this chunk are there
+#ifndef SE_EXP_SKIP_EPILOGUE
+                    if (n < p.n_out) {
+#else
+                    if (n < p.n_out && p.k_dim < 0) {
+#endif
+                        const auto gs = xch_s[chunk & 1][0];
+                        const auto us = xch_s[chunk & 1][1];
 #pragma unroll
-                        for (int j = 0; j < kXchCols; ++j) {
+                        for (int jj = 0; jj < kXchCols / 2; ++jj) {
+                            const int j = j0 + jj;
                             if (c0 + j >= valid) break;
-                            const float gate = round_act<__nv_bfloat16>(__uint_as_float(v[j]));
-                            const float up = xch[j][f];
-                            const float y = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
-                            p.out[(size_t)(row0 + c0 + j) * p.n_out + n] = __float2bfloat16_rn(y);
+                            const float gate = __bfloat162float(gs[j][f]);
+                            const float up = __bfloat162float(us[j][f]);
+                            // silu in 32-bit (fast exponential and reciprocal: the result is rounded to bfloat16 next)
+                            const float silu = __fdividef(gate, 1.f + __expf(-gate));
+                            p.out[(size_t)(row0 + c0 + j) * p.n_out + n] =
+                                __float2bfloat16_rn(round_act<__nv_bfloat16>(silu) * up);
                         }
                     }
-                    // the buffer of this chunk is written again two chunks on, after the next chunk's barrier
+                    // a buffer is written again two chunks on, after the next chunk's barrier
                 }
             } else {
                 const int n = nb * kItemFeatures + (int)rank * kCtaFeatures + et;

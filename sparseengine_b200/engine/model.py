@@ -16,7 +16,7 @@ import torch
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
 from ..parts.base import KVRequest, LayerSlot, StateRequest, StepContext, make_norm
-from ..parts.block import make_block
+from ..parts.block import PreNormBlock, make_block
 from ..parts.linear import linear
 
 
@@ -144,7 +144,7 @@ class Model:
             e1.record()
             self.profile.setdefault(name, []).append((e0, e1))
             return out
-        if not hasattr(block, "mixer_norm"):
+        if not isinstance(block, PreNormBlock):
             return timed("block", block.forward, hidden, residual, step, slot)
         x, residual = timed("mixer_norm", block.mixer_norm.forward, hidden, residual)
         hidden = timed("mixer", block.mixer.forward, x, step, slot)
@@ -159,6 +159,8 @@ class Model:
         s = self.spec
         hidden = torch.empty(step.num_tokens, s.hidden_size, dtype=self.dtype, device=step.token_ids.device)
         ops.embed_gather(self.embed, step.token_ids, hidden)
+        if s.embed_scale != 1.0:
+            hidden.mul_(s.embed_scale)
         residual = None
         for entry, slot in zip(s.order, slots):
             block = self.blocks[entry.layer]
@@ -177,4 +179,8 @@ class Model:
             h, _ = self.final_norm.forward(h, r)
         else:
             h, _ = self.final_norm.forward(h)
-        return linear(h, self.head)
+        logits = linear(h, self.head)
+        if s.logit_softcap is not None:
+            c = float(s.logit_softcap)
+            logits = (torch.tanh(logits.float() / c) * c).to(logits.dtype)
+        return logits

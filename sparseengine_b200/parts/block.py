@@ -4,7 +4,11 @@
 ``residual = hidden``; afterwards each norm call adds the last sublayer's output to the
 residual (32-bit add, rounded to the activation dtype) and normalises the unrounded sum
 (src/sparseengine/models/minimax_m2.py:381-397).  Another arrangement registers under
-another name in ``ARRANGEMENTS``.
+another name in ``ARRANGEMENTS``: a class built from ``(LayerSpec, dtype)`` with ``parts()``
+(name -> part: the model lists parameters and cache needs from it; the part named ``mixer`` is
+the one that may ask for pages or state), ``forward(hidden, residual, step, slot)`` ->
+``(hidden, residual)``, and an attribute ``mixer``.  Parts beyond the four of ``pre_norm`` come
+from ``LayerSpec.extra``.
 """
 from __future__ import annotations
 
