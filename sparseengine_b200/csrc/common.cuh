@@ -112,28 +112,6 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
     for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
     *reinterpret_cast<uint4*>(p) = raw;
 }
-// acc[0..7] = sum over slots k = 0 .. top_k-1, in that order and in 32-bit, of the eight elements
-// rows[slots[k]][i .. i+7] (rows of `width` elements).  The loads of four slots are issued before
-// their values are added, so a sum over eight slots waits for memory twice, not eight times.
-template <typename T>
-__device__ __forceinline__ void sum_slots8(const T* __restrict__ rows, const int* __restrict__ slots, int top_k,
-                                           int width, int i, float* acc) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int k0 = 0; k0 < top_k; k0 += 4) {
-        float v[4][8];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (k0 + u < top_k) load8(rows + (size_t)slots[k0 + u] * width + i, v[u]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (k0 + u < top_k) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] += v[u][j];
-            }
-    }
-}
-
 template <typename T> __device__ __forceinline__ bool aligned8(const T* p) {
     return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
 }

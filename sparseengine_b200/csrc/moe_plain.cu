@@ -289,8 +289,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
     if ((hidden & 7) == 0 && aligned8(y) && aligned8(out)) {
         const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
         if (i >= hidden) return;
-        float acc[8];
-        sum_slots8(y, inv_pos + (size_t)t * top_k, top_k, hidden, i, acc);
+        float acc[8] = {};
+        for (int k = 0; k < top_k; ++k) {
+            float v[8];
+            load8(y + (size_t)inv_pos[t * top_k + k] * hidden + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
         store8(out + (size_t)t * hidden + i, acc);
         return;
     }

@@ -133,3 +133,23 @@ def test_scaled_rotary_tables_are_built_on_the_host_and_match_the_reference():
             load_model_spec(dict(plain_m2.TINY_A, rope_scaling=bad))
     with pytest.raises(ValueError):
         make_position(RotarySpec(rotary_dim=24, pairing="pairs_of_three"), torch.float32)
+
+
+def test_kernel_tuning_options_are_checked_and_reach_the_parts():
+    import torch
+
+    from sparseengine_b200.config.engine_config import Config
+    from sparseengine_b200.engine.factory import KERNEL_TUNING_KEYS, apply_kernel_tuning, check_kernel_tuning
+    from sparseengine_b200.engine.model import Model
+    cfg = Config.from_kwargs("m", kernel_tuning={"attention_decode_kernel_max_tokens": 64, "moe_pair_min_rows": 4096})
+    check_kernel_tuning(cfg.kernel_tuning)
+    for bad in ({"no_such_threshold": 1}, {"attention_portion_min_tokens": -1}, {"gemv_max_out_features": 1.5}):
+        with pytest.raises(ValueError):
+            check_kernel_tuning(bad)
+    with pytest.raises(ValueError):
+        Config.from_kwargs("m", kernel_tuning=[1, 2])
+    _, spec = load_model_spec(plain_m2.TINY_A)
+    m = Model(spec, torch.float32)
+    apply_kernel_tuning(m, cfg.kernel_tuning)
+    assert all(b.mixer.decode_kernel_max_tokens == 64 and b.feed_forward.pair_min_rows == 4096 for b in m.blocks)
+    assert set(KERNEL_TUNING_KEYS) >= {"router_tensor_core_min_tokens", "moe_pair_min_rows_per_expert"}

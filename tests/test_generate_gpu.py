@@ -49,6 +49,29 @@ def test_greedy_generation_equals_the_plain_implementation(folder_a):
     assert llm.is_finished() and llm.runner.cache.free_pages() == llm.runner.cache.groups[0].pool.num_pages
 
 
+def test_random_weights_through_the_entry_point_with_spread_norms():
+    """The smallest configuration as the entry point itself draws it: ``tiny_random`` with
+    matrices N(0, 0.02) and norm weights 1 + N(0, 0.05), seed 0, 32-bit, page size 4, three prompts
+    of 5 / 9 / 13 tokens, 8 greedy steps.  The plain implementation reads the drawn tensors by
+    their checkpoint names."""
+    from sparseengine_b200 import LLM, SamplingParams
+    from sparseengine_b200.weights.loader import _dest
+    llm = LLM(dict(plain_m2.TINY_A), tiny_random=True, tiny_random_seed=0, tiny_random_std=0.02, tiny_random_norm_std=0.05,
+              dtype="float32", page_size=4, num_kvcache_slots=256, max_model_len=128)
+    model = llm.runner.model
+    tensors = {src.name: _dest(getattr(p.owner, p.name), src.index).cpu()
+               for p in model.params() for src in p.sources}
+    norm = tensors["model.layers.0.input_layernorm.weight"]
+    assert 0.01 < float(norm.std()) < 0.12 and abs(float(norm.mean()) - 1) < 0.05
+    assert float(tensors["model.layers.1.block_sparse_moe.e_score_correction_bias"].abs().max()) == 0.0
+    prompts = [tu.random_prompt(256, n, 70 + n) for n in (5, 9, 13)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        want, margins = plain_greedy(plain_m2.TINY_A, tensors, p, 8)
+        assert min(margins) > 1e-5, "test prompt has a near-tie; pick another seed"
+        assert o["token_ids"] == want
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_batching(folder_b):
     from sparseengine_b200 import LLM, SamplingParams
     folder, _ = folder_b
