@@ -14,6 +14,7 @@
 // Any page size; head sizes 64 and 128 (others use the plain kernel); a window is honoured.
 // A block-table entry outside [0, num_pages) is not followed: the rows it stands for are
 // zero-filled and a code goes to the error word.
+#define SE_PDL_TAG "attn"
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -34,11 +35,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ token_seq, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split,
-                   int num_pages, int* __restrict__ error) {
+                   int num_pages, int* __restrict__ error, int settled) {
     constexpr int kChunks = D / 8;                   // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * D * 2;    // one K or V tile
     extern __shared__ __align__(128) uint8_t smem[];
 
+    if (!settled) grid_dependency_wait();
     const int t = blockIdx.x;
     const int group = hq / hkv;
     const int gtiles = (group + 15) / 16;
@@ -57,22 +59,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const size_t page_elems = (size_t)2 * hkv * page_size * D;
     const size_t head_off = (size_t)kvh * page_size * D;
     const size_t v_off = (size_t)hkv * page_size * D;
-
-    // Q fragments (A operand, 16 rows x D): rows g and g+8 of this lane
-    uint32_t qa[D / 16][4];
-    {
-        const __nv_bfloat16* q0 = q + ((size_t)t * hq + head0 + g) * D;
-        const __nv_bfloat16* q1 = q + ((size_t)t * hq + head0 + g + 8) * D;
-        const bool v0 = g < rows_valid, v1 = g + 8 < rows_valid;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int c = kk * 16 + 2 * t4;
-            qa[kk][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
-            qa[kk][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
-            qa[kk][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
-            qa[kk][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
-        }
-    }
 
     float o[D / 8][4];
 #pragma unroll
@@ -110,6 +96,25 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
         }
     };
+
+    // Launched as a dependent of the kernel that writes the queries and this step's keys, this
+    // kernel may have come this far (its place in the block table looked up) while that one runs.
+    if (settled) grid_dependency_wait();
+    // Q fragments (A operand, 16 rows x D): rows g and g+8 of this lane
+    uint32_t qa[D / 16][4];
+    {
+        const __nv_bfloat16* q0 = q + ((size_t)t * hq + head0 + g) * D;
+        const __nv_bfloat16* q1 = q + ((size_t)t * hq + head0 + g + 8) * D;
+        const bool v0 = g < rows_valid, v1 = g + 8 < rows_valid;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int c = kk * 16 + 2 * t4;
+            qa[kk][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+            qa[kk][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+            qa[kk][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+            qa[kk][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+        }
+    }
 
     for (int s = 0; s < kStages - 1; ++s) {
         if (s < num_tiles) load_tile(s, s);
@@ -243,6 +248,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 // out[t, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int d, int splits) {
+    grid_dependency_trigger();       // the output projection that follows may start streaming its weights
     const size_t th = blockIdx.x;
     float mt = -INFINITY;
     for (int s = 0; s < splits; ++s) mt = fmaxf(mt, part_ml[(th * splits + s) * 2]);
@@ -263,7 +269,7 @@ template <int D>
 static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
                   const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int tokens,
                   int hq, int hkv, int page_size, float scale, int window, int splits, int keys_per_split,
-                  int num_pages, int* error, cudaStream_t stream) {
+                  int num_pages, int* error, int settled, cudaStream_t stream) {
     const int group = hq / hkv;
     const int gtiles = (group + 15) / 16;
     const size_t stage_smem = (size_t)kStages * 2 * kTileKeys * D * 2;
@@ -276,11 +282,11 @@ static int launch(const void* q, const void* cache, const int* table, int table_
         configured = true;
     }
     dim3 grid(tokens, hkv * gtiles, splits);
-    attn_decode_kernel<D><<<grid, kThreads, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, token_seq, positions,
-        (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits,
-        keys_per_split, num_pages, error);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = se::launch_dependent(
+        attn_decode_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
+        table, table_stride, seq_rows, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, page_size,
+        scale * 1.4426950408889634f, window, splits, keys_per_split, num_pages, error, settled);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) {
         attn_combine_kernel<<<tokens * hq, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, D, splits);
@@ -298,11 +304,14 @@ extern "C" int se_attn_decode_supported(int head_dim, int hq, int hkv) {
 
 // part_o: float [tokens, hq, splits, head_dim]; part_ml: float [tokens, hq, splits, 2] (unused when splits == 1).
 // keys_per_split is a multiple of 64; split s of a token covers keys lo + s*keys_per_split ...
+// settled: positions, token_seq, seq_rows and the block table were complete before the kernel
+// launched just before this one began (they are inputs of the step, and that kernel is the one
+// that writes the queries and the step's keys): they are then read while it may still run.
 extern "C" int se_attn_decode(const void* q, const void* cache, const int* table, int table_stride,
                               const int* seq_rows, const int* token_seq, const int* positions, void* out,
                               float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int page_size,
                               float scale, int window, int splits, int keys_per_split, int num_pages, int* error,
-                              cudaStream_t stream) {
+                              int settled, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!se_attn_decode_supported(head_dim, hq, hkv) || splits < 1 || keys_per_split <= 0 || keys_per_split % 64)
         return SE_ERR_UNSUPPORTED;
@@ -310,8 +319,8 @@ extern "C" int se_attn_decode(const void* q, const void* cache, const int* table
     if (head_dim == 64)
         return se::dec::launch<64>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
                                    tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
-                                   stream);
+                                   settled, stream);
     return se::dec::launch<128>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
                                 tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
-                                stream);
+                                settled, stream);
 }

@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #define SE_ERR_UNSUPPORTED (-2)   // a size this kernel does not take
 #define SE_ERR_ARGUMENT (-3)      // an inconsistent argument
@@ -65,6 +67,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch.  A kernel started with `launch_dependent` may begin while the
+// kernel before it in the stream still runs, as soon as every block of that kernel has called
+// `grid_dependency_trigger` (or has ended).  What it does before `grid_dependency_wait` may
+// only read what no kernel of the step writes (weights): the wait returns when the kernel
+// before it has ended and its writes can be seen.  A kernel that is launched the ordinary
+// way starts after everything before it, so the two calls cost it nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifndef SE_PDL_TAG
+#define SE_PDL_TAG "x"
+#endif
+static inline bool se_pdl_tag_on() {
+    static const bool on = [] { const char* v = ::getenv("SE_NO_PDL"); return !(v && ::strstr(v, SE_PDL_TAG)); }();
+    return on;
+}
+#define SE_PDL_TAG_ON se_pdl_tag_on()
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = SE_PDL_TAG_ON ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // Codes a kernel writes into the library's error word (one int per device, 0 = fine; the
 // first failure stays).  1..19: a bounded wait on a barrier ran out (the number names the

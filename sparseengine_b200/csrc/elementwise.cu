@@ -25,6 +25,7 @@ __global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restric
                                T* y, T* residual_out, int hidden, float eps) {
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
+    grid_dependency_trigger();       // a projection that follows may start streaming its weights
     const size_t base = (size_t)blockIdx.x * hidden;
     const bool vec = (hidden & 7) == 0 && aligned8(x) && aligned8(y) && aligned8(w) &&
                      (residual == nullptr || (aligned8(residual) && aligned8(residual_out)));

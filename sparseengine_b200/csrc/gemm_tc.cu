@@ -26,6 +26,7 @@
 // up block of MODE_GATE_UP, one block in the other modes; two neighbouring blocks per item
 // were measured there and gained nothing) times one tile of activation rows, which the NA
 // accumulators share.
+#define SE_PDL_TAG "gemm"
 #include "common.cuh"
 
 #include <cuda.h>
@@ -134,6 +135,7 @@ struct Params {
     int total_rows;             // dense: number of activation rows
     int nt;                     // activation rows per tile: 16, 32, 64, 128 or 256
     int stages;                 // depth of the shared-memory ring
+    int lists_settled;          // the tile list and offsets were complete before the kernel before this one began
 };
 
 // ---- the persistent form ---------------------------------------------------------------------
@@ -188,7 +190,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const int second = MODE == MODE_GATE_UP ? p.up_offset : kBlockM;
     constexpr int kItemM = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
     const int nt = p.nt;
-    const int tiles = p.tile_expert != nullptr ? p.num_tiles[0] : (p.total_rows + nt - 1) / nt;
     const int num_kb = (p.k_dim + kBlockK - 1) / kBlockK;
     const int kStages = p.stages;
 
@@ -240,6 +241,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    // Launched as a dependent, this kernel may have come this far while the kernel before it
+    // still runs.  If that kernel writes the tile list, everything waits for it here; if not,
+    // only the loader waits, and only before it asks for activation rows.
+    if (!p.lists_settled) grid_dependency_wait();
+    const int tiles = p.tile_expert != nullptr ? p.num_tiles[0] : (p.total_rows + nt - 1) / nt;
 
     // Every role walks the same list of items: its own block index first, then the answers in
     // the scheduling ring.  `next_item` waits for answer j (the item after item j).
@@ -264,6 +270,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             bool ok = true;
             int asked = 0;          // requests made so far
             int used = 0;           // items with work so far
+            bool waited = !p.lists_settled;    // the kernel before this one has ended
+            // From here on the kernel after this one may set itself up and stream its weights; its
+            // own tile list is then older than the kernel before it (this one), which has seen the
+            // end of everything before itself.
+            if (waited) grid_dependency_trigger();
             int expert = 0, row0 = by * nt, row_end = p.total_rows;
             if (p.tile_expert != nullptr && by < tiles) {
                 expert = p.tile_expert[by];
@@ -304,7 +315,28 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     valid_s[used % kSchedSlots] = min(nt, row_end - row0);
                     ++used;
                     const int wy = expert * p.w_rows_per_expert + n0;
-                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    int kb_first = 0;
+                    if (!waited) {
+                        // This kernel may have started before the one that writes the activation rows
+                        // has ended.  The first trip round the ring asks for the weight tiles at once
+                        // (no kernel writes them; the tile list is older than the kernel before this
+                        // one) and for the activation tiles once that kernel has ended.
+                        kb_first = min(kStages, num_kb);
+                        for (int kb = 0; kb < kb_first; ++kb) {
+                            const uint32_t a = smem_u32(smem + (size_t)kb * stage_bytes);
+                            mbar_expect_tx(full0 + 8 * kb, stage_bytes);
+                            tma_load_2d(a, &map_w, full0 + 8 * kb, kb * kBlockK, wy);
+                            if (NA == 2) tma_load_2d(a + kTileABytes, &map_w, full0 + 8 * kb, kb * kBlockK, wy + second);
+                        }
+                        grid_dependency_wait();
+                        grid_dependency_trigger();
+                        waited = true;
+                        for (int kb = 0; kb < kb_first; ++kb)
+                            tma_load_2d(smem_u32(smem + (size_t)kb * stage_bytes) + NA * kTileABytes, &map_x,
+                                        full0 + 8 * kb, kb * kBlockK, row0);
+                        it = kb_first;
+                    }
+                    for (int kb = kb_first; kb < num_kb; ++kb, ++it) {
                         if (kb == num_kb / 2) {
                             read_answer();
                             if (abort_s) {
@@ -555,8 +587,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     if (2 * cols > 512) smem = std::max<size_t>(smem, 116 * 1024);
     const int item_m = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
     dim3 grid(ceil_div(p.n_out, item_m), tiles);
-    gemm_tc_persistent_kernel<MODE, NA><<<grid, kThreads, smem, stream>>>(mw, mx, p);
-    return (int)cudaGetLastError();
+    // as a dependent of the kernel before it: see the loader's first trip round the ring
+    cudaError_t e = se::launch_dependent(gemm_tc_persistent_kernel<MODE, NA>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 }  // namespace tc
@@ -591,11 +624,14 @@ extern "C" int se_gemm_tc_supported(int k_dim, int n_out, int nt) {
 // Grouped expert GEMM on tensor cores (bf16).
 //   mode 0: a = x rows in sorted order [assignments, k_dim]; w = w13 [experts, 2*n_out, k_dim]; out [assignments, n_out]
 //   mode 1: a = act [assignments, k_dim];                    w = w2 [experts, n_out, k_dim];    out [assignments, n_out]
-// The tile list must have been built with tile_rows = nt.
+// The tile list must have been built with tile_rows = nt.  lists_settled: the kernel launched
+// just before this one on the stream does not write the tile list, the offsets or `sorted`
+// (they were complete before it began), so this kernel may read them while that one still runs.
 extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
                                       const int* tile_expert, const int* tile_row0, const int* num_tiles,
                                       const float* route_w, void* out, int* error, int assignments, int experts,
-                                      int max_tiles, int n_out, int k_dim, int nt, cudaStream_t stream) {
+                                      int max_tiles, int n_out, int k_dim, int nt, int lists_settled,
+                                      cudaStream_t stream) {
     if (assignments <= 0 || max_tiles <= 0) return 0;
     if (!se_gemm_tc_supported(k_dim, n_out, nt) || (mode != 0 && mode != 1)) return SE_ERR_UNSUPPORTED;
     const int w_rows = mode == 0 ? 2 * n_out : n_out;
@@ -606,7 +642,7 @@ extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, co
     if (rc) return rc;
     const int na = mode == 0 ? 2 : 1;
     Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
-             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(na, nt)};
+             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(na, nt), lists_settled ? 1 : 0};
     if (mode == 0) return launch<MODE_GATE_UP, 2>(mw, mx, p, max_tiles, stream);
     // With 128-row tiles the activation tile of the down projection is as large as a weight block
     // (K is the expert width), so two weight blocks share it, which cuts what an SM takes from L2
@@ -630,6 +666,6 @@ extern "C" int se_gemm_tc_dense(const void* x, const void* w, void* out, int* er
     rc = make_map(&mx, x, rows, k_dim, nt);
     if (rc) return rc;
     Params p{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (__nv_bfloat16*)out, error,
-             n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt)};
+             n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt), 1};
     return launch<MODE_DENSE, 1>(mw, mx, p, se::ceil_div(rows, nt), stream);
 }

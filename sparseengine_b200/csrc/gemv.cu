@@ -9,6 +9,7 @@
 // harmless because A and B use the same permutation and the sum over k does not care.  No
 // shared memory on the way in; the 8 or 16 warps of a block split K and add their partial
 // sums through shared memory at the end.  The weights are read exactly once.
+#define SE_PDL_TAG "gemv"
 #include "common.cuh"
 #include "mma_util.cuh"
 #include <cstdlib>
@@ -20,10 +21,16 @@ namespace gemv {
 // split K.  kRowsPerBlock: weight rows of a block, 16 (a full fragment) or 8 (the fragment's
 // upper half stays zero): fewer rows make more blocks, which a matrix with few rows needs to
 // keep every SM loading.
+#ifndef SE_GEMV_PRELOAD
+#define SE_GEMV_PRELOAD 4
+#endif
+constexpr int kPreload = SE_GEMV_PRELOAD;      // chunks of a warp whose weights are loaded before x is waited for
+
 template <int NT, int kWarps, int kRowsPerBlock>
 __global__ void __launch_bounds__(32 * kWarps)
 gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
             int rows, int n_out, int k_dim) {
+    grid_dependency_trigger();       // the kernel after this one may set itself up meanwhile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * kRowsPerBlock;
@@ -42,11 +49,7 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-#pragma unroll 8
-    for (int c = c_begin; c < c_end; ++c) {
-        const uint4 a_lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + c * 32));     // streamed once
-        uint4 a_hi = make_uint4(0u, 0u, 0u, 0u);
-        if (kRowsPerBlock == 16) a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
+    auto step = [&](int c, const uint4& a_lo, const uint4& a_hi) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             uint4 b = make_uint4(0u, 0u, 0u, 0u);
@@ -56,6 +59,29 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
             se::mma::mma_bf16(acc[nt], a0, b.x, b.y);
             se::mma::mma_bf16(acc[nt], a1, b.z, b.w);
         }
+    };
+    // The first chunks' weights are asked for before the kernel that makes x has ended (this
+    // kernel is launched as its dependent): the weights are what takes the time, and no kernel
+    // writes them.
+    uint4 pre_lo[kPreload > 0 ? kPreload : 1], pre_hi[kPreload > 0 ? kPreload : 1];
+#pragma unroll
+    for (int i = 0; i < kPreload; ++i) {
+        pre_lo[i] = pre_hi[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (c_begin + i < c_end) {
+            pre_lo[i] = __ldcs(reinterpret_cast<const uint4*>(w_lo + (c_begin + i) * 32));     // streamed once
+            if (kRowsPerBlock == 16) pre_hi[i] = __ldcs(reinterpret_cast<const uint4*>(w_hi + (c_begin + i) * 32));
+        }
+    }
+    grid_dependency_wait();
+#pragma unroll
+    for (int i = 0; i < kPreload; ++i)
+        if (c_begin + i < c_end) step(c_begin + i, pre_lo[i], pre_hi[i]);
+#pragma unroll 4
+    for (int c = c_begin + kPreload; c < c_end; ++c) {
+        const uint4 a_lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + c * 32));
+        uint4 a_hi = make_uint4(0u, 0u, 0u, 0u);
+        if (kRowsPerBlock == 16) a_hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + c * 32));
+        step(c, a_lo, a_hi);
     }
     __shared__ float part[kWarps][kRowsPerBlock][8 * NT + 1];
 #pragma unroll
@@ -88,8 +114,8 @@ extern "C" int se_gemv_supported(int rows, int n_out, int k_dim) {
 
 template <int NT, int W, int R>
 static void launch_gemv(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, cudaStream_t stream) {
-    se::gemv::gemv_kernel<NT, W, R><<<se::ceil_div(n_out, R), 32 * W, 0, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
+    se::launch_dependent(se::gemv::gemv_kernel<NT, W, R>, dim3(se::ceil_div(n_out, R)), dim3(32 * W), 0, stream,
+                         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
 }
 
 // x [rows <= 16, k_dim], w [n_out, k_dim], out [rows, n_out]; bf16; k_dim a multiple of 32.

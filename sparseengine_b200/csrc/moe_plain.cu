@@ -146,6 +146,7 @@ moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts
                        int* __restrict__ num_tiles, const uint4* __restrict__ x, uint4* __restrict__ xs,
                        int row_vecs, unsigned long long* stats) {
     extern __shared__ int sm[];
+    grid_dependency_trigger();              // the grouped GEMM that follows may set itself up
     int* ids_s = sm;                        // [assignments]
     int* rank_s = ids_s + assignments;      // [assignments]
     int* sorted_s = rank_s + assignments;   // [assignments]
@@ -192,6 +193,7 @@ moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts
 // out[p, :] = x[sorted[p] / top_k, :] in 16-byte words (activation rows gathered into expert order)
 __global__ void gather_sorted_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted,
                                           uint4* __restrict__ out, int row_vecs, int top_k) {
+    grid_dependency_trigger();              // the grouped GEMM that follows may stream its first weight tiles
     const uint4* src = x + (size_t)(sorted[blockIdx.x] / top_k) * row_vecs;
     uint4* dst = out + (size_t)blockIdx.x * row_vecs;
     for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) dst[i] = src[i];

@@ -154,9 +154,11 @@ ROTARY_PAIRING = {"split_half": 0, "interleaved_to_split_half": 1, "interleaved"
 
 def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads,
             num_kv_heads, head_dim, rotary_dim, eps, rope_scale, page_size, write_cache=True,
-            pairing: str = "split_half", num_pages=None):
+            pairing: str = "split_half", num_pages=None, step_inputs_settled: bool = False):
     """``num_pages``: the pool the block table's entries must lie in (default: the pages ``cache``
-    holds); an entry outside it is not followed and shows in the error word."""
+    holds); an entry outside it is not followed and shows in the error word.
+    ``step_inputs_settled``: ``positions`` were complete before the kernel launched just before this
+    call (the one that writes ``qkv``) began; the rotation angles are then computed while it runs."""
     tokens = qkv.shape[0]
     dt = qkv.dtype
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -166,7 +168,7 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
     inv_rms = None
     if q_w is not None and tokens > 64:      # many tokens: norm statistics once per token, not once per head
         inv_rms = torch.empty(tokens, 2, dtype=torch.float32, device=qkv.device)
-    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iip" "iip" "ip")(
+    _check(_fn("se_qk_prep", "pppppppp" "ipp" "iiiii" "ff" "iip" "iip" "iip")(
         _ptr(qkv, None, "qkv"), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
         _ptr(inv_freq, torch.float32, "inv_freq"), _ptr(positions, torch.int32, "positions"),
         _ptr(token_seq, torch.int32, "token_seq"), _ptr(seq_rows, torch.int32, "seq_rows"),
@@ -174,7 +176,7 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
         tokens, num_heads, num_kv_heads, head_dim, rotary_dim, float(eps), float(rope_scale),
         page_size, int(write_cache), _ptr(inv_rms), ROTARY_PAIRING[pairing],
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(qkv.device)),
-        dtype_code(dt), _stream()), "qk_prep")
+        int(bool(step_inputs_settled)), dtype_code(dt), _stream()), "qk_prep")
     return q_out
 
 
@@ -238,7 +240,10 @@ def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None, st
     tile_expert[max_tiles], tile_row0[max_tiles], num_tiles[1].
     gather = (x [tokens, width], xs [A, width], top_k): also xs[p] = x[sorted[p] // top_k], the
     activation rows in expert order (in the same launch when there are few assignments).
-    stats: optional int64[2] on the device; [0] += experts that got a row, [1] += 1."""
+    stats: optional int64[2] on the device; [0] += experts that got a row, [1] += 1.
+    Returns whether the lists were complete before the last kernel of the build began (the
+    gather of rows as a launch of its own): a grouped GEMM launched next may then read them
+    while that kernel still runs (``lists_settled``)."""
     global launch_count
     assignments = ids.numel()
     x = xs = None
@@ -256,6 +261,7 @@ def moe_route_build(ids, experts: int, tile_rows: int, ws: dict, gather=None, st
                                                  "tile_row0", "num_tiles")],
         _ptr(x, None, "x"), _ptr(xs, None, "xs"), row_bytes, _ptr(stats, torch.int64, "stats"), _stream()),
         "moe_route_build")
+    return not small and gather is not None
 
 
 def moe_max_tiles(assignments: int, experts: int, tile_rows: int) -> int:
@@ -381,12 +387,16 @@ def moe_tile_rows_tc(assignments: int, experts: int) -> int:
     return nt
 
 
-def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, nt):
-    _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiii" "p")(
+def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, nt,
+                        lists_settled: bool = False):
+    """``lists_settled``: the kernel launched just before this one does not write the lists in ``ws``
+    (they were complete before it began).  The GEMM starts as a dependent of that kernel and then
+    asks for its first weight tiles while it still runs; otherwise it waits for it first."""
+    _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiiii" "p")(
         mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
         _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
         _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(a.device)),
-        a.shape[0], experts, max_tiles, n_out, k_dim, nt, _stream()), "moe_grouped_gemm_tc")
+        a.shape[0], experts, max_tiles, n_out, k_dim, nt, int(bool(lists_settled)), _stream()), "moe_grouped_gemm_tc")
     return out
 
 
@@ -467,19 +477,24 @@ def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: i
 
 
 def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,
-                scale, window=None, max_keys: int, num_pages=None):
+                scale, window=None, max_keys: int, num_pages=None, step_inputs_settled: bool = False):
+    """``step_inputs_settled``: ``table``, ``seq_rows``, ``token_seq`` and ``positions`` were complete
+    before the kernel launched just before this call began (that kernel wrote ``q`` and the step's
+    keys).  The attention kernel, launched as its dependent, then finds its place in the block table
+    while it still runs; otherwise it waits for it first."""
     tokens = q.shape[0]
     splits, per = attn_decode_plan(tokens, num_heads, num_kv_heads, max_keys, sms=sm_count(q.device))
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty(tokens * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(tokens * num_heads * splits * 2, dtype=torch.float32, device=q.device)
-    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "ip" "p")(
+    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "ip" "i" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml),
         tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per,
-        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)), _stream()),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
+        int(bool(step_inputs_settled)), _stream()),
         "attn_decode")
     return out
 

@@ -20,6 +20,7 @@
 // code goes to the error word.
 //
 // Cache layout of one cache layer: [page][K|V][kv head][slot in page][head_dim].
+#define SE_PDL_TAG "qk"
 #include "common.cuh"
 
 namespace se {
@@ -36,9 +37,14 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
                                const int* __restrict__ table, int table_stride, T* __restrict__ cache,
                                T* __restrict__ q_out, int hq, int hkv, int d, int rot, float eps,
                                float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms,
-                               int heads_per_block, int pairing, int num_pages, int* __restrict__ error) {
+                               int heads_per_block, int pairing, int num_pages, int* __restrict__ error,
+                               int settled) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
+    grid_dependency_trigger();             // the attention kernel that follows may find its keys' pages meanwhile
+    // Launched as a dependent of the projection that writes qkv: with `settled` (the positions are
+    // older than that kernel) the angles are ready when it ends.
+    if (!settled) grid_dependency_wait();
     const int t = blockIdx.x;
     const int qn = hq * d, kn = hkv * d;
     const T* row = qkv + (size_t)t * (qn + 2 * kn);
@@ -52,6 +58,7 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
             cs[half + j] = s * rope_scale;
         }
     }
+    if (settled) grid_dependency_wait();
     const int total_heads = hq + (write_cache ? hkv : 0);
     const int h_begin = blockIdx.y * heads_per_block, h_end = min(total_heads, h_begin + heads_per_block);
     float inv_cached[2] = {-1.f, -1.f};       // statistics of the q and of the k projection, once per block
@@ -137,6 +144,7 @@ qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T
                    int num_pages, int* __restrict__ error) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
+    grid_dependency_trigger();             // the attention kernel that follows may find its keys' pages meanwhile
     const int t = blockIdx.x;
     const int qn = hq * d, kn = hkv * d;
     const T* row = qkv + (size_t)t * (qn + 2 * kn);
@@ -261,7 +269,7 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
                           const int* positions, const int* token_seq, const int* seq_rows, const int* table,
                           int table_stride, void* cache, void* q_out, int tokens, int hq, int hkv, int d,
                           int rot, float eps, float rope_scale, int page_size, int write_cache, float* inv_rms,
-                          int pairing, int num_pages, int* error, int dtype, cudaStream_t stream) {
+                          int pairing, int num_pages, int* error, int settled, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || pairing < 0 || pairing > 3) return SE_ERR_ARGUMENT;
     if (inv_freq == nullptr) rot = 0;
@@ -287,10 +295,22 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
             se::qk_inv_rms_kernel<T><<<tokens, 256, 0, stream>>>((const T*)qkv, inv_rms, hq * d, hkv * d, eps));
     }
     const int heads_per_block = tokens > 64 ? 8 : 1;
-    SE_DISPATCH_DTYPE(dtype, T,
-        se::qk_prep_kernel<T><<<dim3(tokens, se::ceil_div(hq + hkv, heads_per_block)), 128, smem, stream>>>(
-            (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
-            seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
-            write_cache, two_pass ? inv_rms : nullptr, heads_per_block, pairing, num_pages, error));
+    // as a dependent of the kernel before it, unless a kernel of this call came first
+    SE_DISPATCH_DTYPE(dtype, T, {
+        const dim3 grid(tokens, se::ceil_div(hq + hkv, heads_per_block));
+        if (two_pass) {
+            se::qk_prep_kernel<T><<<grid, 128, smem, stream>>>(
+                (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
+                seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
+                write_cache, inv_rms, heads_per_block, pairing, num_pages, error, 0);
+        } else {
+            cudaError_t e = se::launch_dependent(
+                se::qk_prep_kernel<T>, grid, dim3(128), smem, stream, (const T*)qkv, (const T*)q_w, (const T*)k_w,
+                rot > 0 ? inv_freq : nullptr, positions, token_seq, seq_rows, table, table_stride, (T*)cache,
+                (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size, write_cache, (const float*)nullptr,
+                heads_per_block, pairing, num_pages, error, settled ? 1 : 0);
+            if (e != cudaSuccess) return (int)e;
+        }
+    });
     SE_LAUNCH_CHECK();
 }

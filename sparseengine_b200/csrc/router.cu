@@ -8,6 +8,7 @@
 // (src/sparseengine/kernels/triton/moe_biased_sigmoid.py:71-111); weights = unbiased p
 // of the chosen, divided by their sum (:202-238, epsilon 0 for M2:
 // src/sparseengine/kernels/triton/minimax_m2_router.py:50-63).
+#define SE_PDL_TAG "router"
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -282,6 +283,7 @@ __global__ void router_logits_small_kernel(const T* __restrict__ x, const float*
             if (i < b) gv[u] = __ldg(reinterpret_cast<const float4*>(g[0]) + i);
         }
     }
+    grid_dependency_wait();      // launched as a dependent: the gate rows are on their way before x is complete
     load_tokens(x, xs, tokens * hidden);
     __syncthreads();
     float acc[kRouterTokens][1];
@@ -569,8 +571,10 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
             }
-            se::router_logits_small_kernel<T><<<se::ceil_div(experts, 2), 32 * se::kRouterWarps, smem, stream>>>(
-                (const T*)x, gate, logits, tokens, hidden, experts);
+            cudaError_t e = se::launch_dependent(se::router_logits_small_kernel<T>, dim3(se::ceil_div(experts, 2)),
+                                                 dim3(32 * se::kRouterWarps), smem, stream, (const T*)x, gate, logits,
+                                                 tokens, hidden, experts);
+            if (e != cudaSuccess) return (int)e;
         } else if ((hidden & 3) == 0) {
             dim3 grid(se::ceil_div(tokens, se::kBigTokens), se::ceil_div(experts, se::kBigExperts));
             const int tiled_smem = se::kBigStages * (se::kBigTokens * 128 * (int)sizeof(T) + se::kBigExperts * 128 * (int)sizeof(float)) +

@@ -64,9 +64,10 @@ class PagedAttention(Mixer):
         ops.qk_prep(qkv, self.q_norm, self.k_norm, rope.inv_freq, step.positions, step.token_seq, step.seq_rows,
                     slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
                     head_dim=s.head_dim, rotary_dim=rope.rotary_dim, eps=s.qk_norm_eps, rope_scale=rope.scale,
-                    page_size=slot.page_size, write_cache=slot.write_cache, pairing=rope.pairing)
+                    page_size=slot.page_size, write_cache=slot.write_cache, pairing=rope.pairing,
+                    step_inputs_settled=True)       # the projection before it does not write the positions
         attn = torch.empty_like(q)
-        self.attend(q, attn, step, slot)
+        self.attend(q, attn, step, slot, after_qk_prep=True)
         return linear(attn, self.o)
 
     # The split-key kernel (one CTA per token, KV head and key split) reads a request's keys once
@@ -89,7 +90,9 @@ class PagedAttention(Mixer):
                 and step.num_tokens >= self.portion_min_average * step.num_seqs)
     use_tensor_cores = None      # False: always the plain kernel
 
-    def attend(self, q, out, step, slot):
+    def attend(self, q, out, step, slot, after_qk_prep=False):
+        """``after_qk_prep``: the kernel launched last is the one that wrote this step's keys and
+        ``q``; the split-key kernel then looks its place in the block table up while it still runs."""
         s = self.spec
         if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
                 and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
@@ -97,7 +100,8 @@ class PagedAttention(Mixer):
                 max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
                 ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                 num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
-                                page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys)
+                                page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys,
+                                step_inputs_settled=after_qk_prep)
             else:
                 # prompt portions: tcgen05 + tensor memory for head size 128, m16n8k16 tiles otherwise
                 fn = (ops.attn_prefill_tc if ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads)

@@ -92,8 +92,8 @@ class _RoutedSwiGLU(FeedForward):
             self.route_stats = torch.zeros(2, dtype=torch.int64, device=dev)
             self.route_stats_large = torch.zeros(2, dtype=torch.int64, device=dev)
         large = tc and self.pair_min_rows is not None and a >= self.pair_min_rows
-        ops.moe_route_build(ids, self.num_experts, tile_rows, ws, gather=(x, xs, self.top_k) if tc else None,
-                            stats=self.route_stats_large if large else self.route_stats)
+        settled = ops.moe_route_build(ids, self.num_experts, tile_rows, ws, gather=(x, xs, self.top_k) if tc else None,
+                                      stats=self.route_stats_large if large else self.route_stats)
         if large:        # what this build counted reaches the host behind this step, for later steps' choice
             if getattr(self, "_large_host", None) is None:
                 self._large_host = torch.zeros(2, dtype=torch.int64).pin_memory()
@@ -106,10 +106,11 @@ class _RoutedSwiGLU(FeedForward):
             ops.moe_grouped_gemm_pair(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,
                                       n_out=self.hidden, k_dim=self.inter)
         elif tc:
+            # the second product starts while the first still runs: the lists are older than both
             ops.moe_grouped_gemm_tc(0, xs, self.w13, ws, None, act, experts=self.num_experts, max_tiles=max_tiles,
-                                    n_out=self.inter, k_dim=self.hidden, nt=tile_rows)
+                                    n_out=self.inter, k_dim=self.hidden, nt=tile_rows, lists_settled=settled)
             ops.moe_grouped_gemm_tc(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,
-                                    n_out=self.hidden, k_dim=self.inter, nt=tile_rows)
+                                    n_out=self.hidden, k_dim=self.inter, nt=tile_rows, lists_settled=True)
         else:
             ops.moe_grouped_gemm_plain(0, x, self.w13, ws, None, act, max_tiles=max_tiles, n_out=self.inter,
                                        k_dim=self.hidden, top_k=self.top_k)
