@@ -14,7 +14,6 @@
 // Any page size; head sizes 64 and 128 (others use the plain kernel); a window is honoured.
 // A block-table entry outside [0, num_pages) is not followed: the rows it stands for are
 // zero-filled and a code goes to the error word.
-#define SE_PDL_TAG "attn"
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -30,17 +29,16 @@ using namespace se::mma;
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
-attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // written by the kernel before this one: no __restrict__ (see the wait below)
                    const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                    const int* __restrict__ token_seq, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split,
-                   int num_pages, int* __restrict__ error, int settled) {
+                   int num_pages, int* __restrict__ error) {
     constexpr int kChunks = D / 8;                   // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * D * 2;    // one K or V tile
     extern __shared__ __align__(128) uint8_t smem[];
 
-    if (!settled) grid_dependency_wait();
     const int t = blockIdx.x;
     const int group = hq / hkv;
     const int gtiles = (group + 15) / 16;
@@ -97,9 +95,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
     };
 
-    // Launched as a dependent of the kernel that writes the queries and this step's keys, this
-    // kernel may have come this far (its place in the block table looked up) while that one runs.
-    if (settled) grid_dependency_wait();
+    // Where the step's inputs are older than the kernel before this one (the one that writes the
+    // queries and this step's keys), this kernel is launched as its dependent and may have come
+    // this far (its place in the block table looked up) while that one runs.  q and the cache
+    // are not declared read-only for this kernel's lifetime, or the compiler would be free to
+    // move their loads above the wait.
+    grid_dependency_wait();
     // Q fragments (A operand, 16 rows x D): rows g and g+8 of this lane
     uint32_t qa[D / 16][4];
     {
@@ -282,10 +283,10 @@ static int launch(const void* q, const void* cache, const int* table, int table_
         configured = true;
     }
     dim3 grid(tokens, hkv * gtiles, splits);
-    cudaError_t e = se::launch_dependent(
-        attn_decode_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
-        table, table_stride, seq_rows, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, page_size,
-        scale * 1.4426950408889634f, window, splits, keys_per_split, num_pages, error, settled);
+    cudaError_t e = SE_LAUNCH_DEPENDENT_IF(
+        settled != 0, "attn", attn_decode_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q,
+        (const __nv_bfloat16*)cache, table, table_stride, seq_rows, token_seq, positions, (__nv_bfloat16*)out, part_o,
+        part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits, keys_per_split, num_pages, error);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) {
@@ -306,7 +307,8 @@ extern "C" int se_attn_decode_supported(int head_dim, int hq, int hkv) {
 // keys_per_split is a multiple of 64; split s of a token covers keys lo + s*keys_per_split ...
 // settled: positions, token_seq, seq_rows and the block table were complete before the kernel
 // launched just before this one began (they are inputs of the step, and that kernel is the one
-// that writes the queries and the step's keys): they are then read while it may still run.
+// that writes the queries and the step's keys).  The attention kernel is then launched as that
+// kernel's dependent and reads them while it may still run; else it is launched the ordinary way.
 extern "C" int se_attn_decode(const void* q, const void* cache, const int* table, int table_stride,
                               const int* seq_rows, const int* token_seq, const int* positions, void* out,
                               float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int page_size,

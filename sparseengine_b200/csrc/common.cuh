@@ -75,19 +75,21 @@ __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b -
 // before it has ended and its writes can be seen.  A kernel that is launched the ordinary
 // way starts after everything before it, so the two calls cost it nothing.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-#ifndef SE_PDL_TAG
-#define SE_PDL_TAG "x"
+__device__ __forceinline__ void grid_dependency_trigger() {
+#ifndef SE_NO_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
-static inline bool se_pdl_tag_on() {
-    static const bool on = [] { const char* v = ::getenv("SE_NO_PDL"); return !(v && ::strstr(v, SE_PDL_TAG)); }();
-    return on;
 }
-#define SE_PDL_TAG_ON se_pdl_tag_on()
+
+// SE_NO_PDL=name,name,... launches the named kernels the ordinary way (a tuning aid; names are
+// the tags at the launch sites).
+static inline bool pdl_enabled(const char* tag) {
+    const char* v = ::getenv("SE_NO_PDL");
+    return !(v != nullptr && ::strstr(v, tag) != nullptr);
+}
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args... args) {
+inline cudaError_t launch_dependent_if(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -97,9 +99,15 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = SE_PDL_TAG_ON ? 1 : 0;
+    cfg.numAttrs = dependent ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+// launch_dependent("tag", kernel, grid, block, smem, stream, args...)
+#define SE_LAUNCH_DEPENDENT(tag, ...) \
+    ([&] { static const bool on = se::pdl_enabled(tag); return se::launch_dependent_if(on, __VA_ARGS__); }())
+// the same, as a dependent only if `cond` holds (else the ordinary way: after everything before it)
+#define SE_LAUNCH_DEPENDENT_IF(cond, tag, ...) \
+    ([&] { static const bool on = se::pdl_enabled(tag); return se::launch_dependent_if(on && (cond), __VA_ARGS__); }())
 
 // Codes a kernel writes into the library's error word (one int per device, 0 = fine; the
 // first failure stays).  1..19: a bounded wait on a barrier ran out (the number names the

@@ -29,6 +29,18 @@ __global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restric
     const size_t base = (size_t)blockIdx.x * hidden;
     const bool vec = (hidden & 7) == 0 && aligned8(x) && aligned8(y) && aligned8(w) &&
                      (residual == nullptr || (aligned8(residual) && aligned8(residual_out)));
+    // Launched as a dependent of the kernel that writes x: a thread's first weights are asked for
+    // before that kernel has ended (no kernel writes them).
+    constexpr int kKeep = 2;
+    float w_keep[kKeep][8];
+    if (vec) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int i = (threadIdx.x + k * blockDim.x) * 8;
+            if (i < hidden) load8(w + i, w_keep[k]);
+        }
+    }
+    grid_dependency_wait();
     float ss = 0.f;
     if (vec) {
         for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
@@ -58,7 +70,17 @@ __global__ void rmsnorm_kernel(const T* x, const T* residual, const T* __restric
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     if (vec) {
-        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int i = (threadIdx.x + k * blockDim.x) * 8;
+            if (i < hidden) {
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = row[i + j] * inv * w_keep[k][j];
+                store8(y + base + i, o);
+            }
+        }
+        for (int i = (threadIdx.x + kKeep * blockDim.x) * 8; i < hidden; i += blockDim.x * 8) {
             float wv[8], o[8];
             load8(w + i, wv);
 #pragma unroll
@@ -130,8 +152,9 @@ extern "C" int se_rmsnorm(const void* x, const void* residual, const void* w, vo
             cudaError_t e = cudaFuncSetAttribute(se::rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        se::rmsnorm_kernel<T><<<rows, threads, smem, stream>>>((const T*)x, (const T*)residual, (const T*)w,
-                                                                (T*)y, (T*)residual_out, hidden, eps);
+        cudaError_t e = SE_LAUNCH_DEPENDENT("norm", se::rmsnorm_kernel<T>, dim3(rows), dim3(threads), smem, stream, (const T*)x,
+                                             (const T*)residual, (const T*)w, (T*)y, (T*)residual_out, hidden, eps);
+        if (e != cudaSuccess) return (int)e;
     });
     SE_LAUNCH_CHECK();
 }

@@ -26,7 +26,6 @@
 // up block of MODE_GATE_UP, one block in the other modes; two neighbouring blocks per item
 // were measured there and gained nothing) times one tile of activation rows, which the NA
 // accumulators share.
-#define SE_PDL_TAG "gemm"
 #include "common.cuh"
 
 #include <cuda.h>
@@ -588,7 +587,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     const int item_m = MODE == MODE_GATE_UP ? kBlockM : NA * kBlockM;
     dim3 grid(ceil_div(p.n_out, item_m), tiles);
     // as a dependent of the kernel before it: see the loader's first trip round the ring
-    cudaError_t e = se::launch_dependent(gemm_tc_persistent_kernel<MODE, NA>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+    cudaError_t e = SE_LAUNCH_DEPENDENT("gemm", gemm_tc_persistent_kernel<MODE, NA>, grid, dim3(kThreads), smem, stream, mw, mx, p);
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 

@@ -9,7 +9,6 @@
 // harmless because A and B use the same permutation and the sum over k does not care.  No
 // shared memory on the way in; the 8 or 16 warps of a block split K and add their partial
 // sums through shared memory at the end.  The weights are read exactly once.
-#define SE_PDL_TAG "gemv"
 #include "common.cuh"
 #include "mma_util.cuh"
 #include <cstdlib>
@@ -21,16 +20,19 @@ namespace gemv {
 // split K.  kRowsPerBlock: weight rows of a block, 16 (a full fragment) or 8 (the fragment's
 // upper half stays zero): fewer rows make more blocks, which a matrix with few rows needs to
 // keep every SM loading.
+// Chunks of a warp whose weights are loaded before x is waited for.  They are held in registers,
+// and more than 4 chunks cost more in residency than they gain (measured: 8 chunks are slower
+// than none, also for the few blocks of 16 warps that the output projection has).
 #ifndef SE_GEMV_PRELOAD
 #define SE_GEMV_PRELOAD 4
 #endif
-constexpr int kPreload = SE_GEMV_PRELOAD;      // chunks of a warp whose weights are loaded before x is waited for
 
 template <int NT, int kWarps, int kRowsPerBlock>
 __global__ void __launch_bounds__(32 * kWarps)
-gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+gemv_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
             int rows, int n_out, int k_dim) {
     grid_dependency_trigger();       // the kernel after this one may set itself up meanwhile
+    constexpr int kPreload = SE_GEMV_PRELOAD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * kRowsPerBlock;
@@ -53,7 +55,7 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             uint4 b = make_uint4(0u, 0u, 0u, 0u);
-            if (x_ok[nt]) b = __ldg(reinterpret_cast<const uint4*>(x_row[nt] + c * 32));
+            if (x_ok[nt]) b = *reinterpret_cast<const uint4*>(x_row[nt] + c * 32);
             const uint32_t a0[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
             const uint32_t a1[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
             se::mma::mma_bf16(acc[nt], a0, b.x, b.y);
@@ -62,7 +64,8 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     };
     // The first chunks' weights are asked for before the kernel that makes x has ended (this
     // kernel is launched as its dependent): the weights are what takes the time, and no kernel
-    // writes them.
+    // writes them.  x is read with ordinary loads through a pointer that is not __restrict__:
+    // loads the compiler may take for read-only over the kernel's lifetime could move above the wait.
     uint4 pre_lo[kPreload > 0 ? kPreload : 1], pre_hi[kPreload > 0 ? kPreload : 1];
 #pragma unroll
     for (int i = 0; i < kPreload; ++i) {
@@ -114,7 +117,7 @@ extern "C" int se_gemv_supported(int rows, int n_out, int k_dim) {
 
 template <int NT, int W, int R>
 static void launch_gemv(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, cudaStream_t stream) {
-    se::launch_dependent(se::gemv::gemv_kernel<NT, W, R>, dim3(se::ceil_div(n_out, R)), dim3(32 * W), 0, stream,
+    SE_LAUNCH_DEPENDENT("gemv", se::gemv::gemv_kernel<NT, W, R>, dim3(se::ceil_div(n_out, R)), dim3(32 * W), 0, stream,
                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, n_out, k_dim);
 }
 

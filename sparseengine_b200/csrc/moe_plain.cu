@@ -287,6 +287,7 @@ __global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __re
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, T* __restrict__ out,
                                    int hidden, int top_k) {
+    grid_dependency_trigger();       // the norm that follows may fetch its weights, and the projection after it its own
     const int t = blockIdx.x;
     if ((hidden & 7) == 0 && aligned8(y) && aligned8(out)) {
         const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;

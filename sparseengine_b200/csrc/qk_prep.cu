@@ -20,7 +20,6 @@
 // code goes to the error word.
 //
 // Cache layout of one cache layer: [page][K|V][kv head][slot in page][head_dim].
-#define SE_PDL_TAG "qk"
 #include "common.cuh"
 
 namespace se {
@@ -31,20 +30,18 @@ namespace se {
 // projection (the rows are a few KB and sit in L2); with many tokens one block takes all
 // heads of a token and the statistics come from a first kernel.
 template <typename T>
-__global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
+__global__ void qk_prep_kernel(const T* qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
                                const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                const int* __restrict__ token_seq, const int* __restrict__ seq_rows,
                                const int* __restrict__ table, int table_stride, T* __restrict__ cache,
                                T* __restrict__ q_out, int hq, int hkv, int d, int rot, float eps,
                                float rope_scale, int page_size, int write_cache, const float* __restrict__ inv_rms,
-                               int heads_per_block, int pairing, int num_pages, int* __restrict__ error,
-                               int settled) {
+                               int heads_per_block, int pairing, int num_pages, int* __restrict__ error) {
     extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
     __shared__ float scratch[33];
     grid_dependency_trigger();             // the attention kernel that follows may find its keys' pages meanwhile
-    // Launched as a dependent of the projection that writes qkv: with `settled` (the positions are
-    // older than that kernel) the angles are ready when it ends.
-    if (!settled) grid_dependency_wait();
+    // Where the positions are older than the projection that writes qkv, this kernel is launched
+    // as its dependent, and the angles are ready when the projection ends.
     const int t = blockIdx.x;
     const int qn = hq * d, kn = hkv * d;
     const T* row = qkv + (size_t)t * (qn + 2 * kn);
@@ -58,7 +55,7 @@ __global__ void qk_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ 
             cs[half + j] = s * rope_scale;
         }
     }
-    if (settled) grid_dependency_wait();
+    grid_dependency_wait();      // qkv is not __restrict__: its loads must stay below this line
     const int total_heads = hq + (write_cache ? hkv : 0);
     const int h_begin = blockIdx.y * heads_per_block, h_end = min(total_heads, h_begin + heads_per_block);
     float inv_cached[2] = {-1.f, -1.f};       // statistics of the q and of the k projection, once per block
@@ -302,13 +299,13 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
             se::qk_prep_kernel<T><<<grid, 128, smem, stream>>>(
                 (const T*)qkv, (const T*)q_w, (const T*)k_w, rot > 0 ? inv_freq : nullptr, positions, token_seq,
                 seq_rows, table, table_stride, (T*)cache, (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size,
-                write_cache, inv_rms, heads_per_block, pairing, num_pages, error, 0);
+                write_cache, inv_rms, heads_per_block, pairing, num_pages, error);
         } else {
-            cudaError_t e = se::launch_dependent(
-                se::qk_prep_kernel<T>, grid, dim3(128), smem, stream, (const T*)qkv, (const T*)q_w, (const T*)k_w,
+            cudaError_t e = SE_LAUNCH_DEPENDENT_IF(
+                settled != 0, "qk", se::qk_prep_kernel<T>, grid, dim3(128), smem, stream, (const T*)qkv, (const T*)q_w, (const T*)k_w,
                 rot > 0 ? inv_freq : nullptr, positions, token_seq, seq_rows, table, table_stride, (T*)cache,
                 (T*)q_out, hq, hkv, d, rot, eps, rope_scale, page_size, write_cache, (const float*)nullptr,
-                heads_per_block, pairing, num_pages, error, settled ? 1 : 0);
+                heads_per_block, pairing, num_pages, error);
             if (e != cudaSuccess) return (int)e;
         }
     });

@@ -8,7 +8,6 @@
 // (src/sparseengine/kernels/triton/moe_biased_sigmoid.py:71-111); weights = unbiased p
 // of the chosen, divided by their sum (:202-238, epsilon 0 for M2:
 // src/sparseengine/kernels/triton/minimax_m2_router.py:50-63).
-#define SE_PDL_TAG "router"
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -70,7 +69,7 @@ __device__ __forceinline__ void quarter_dot(const float* __restrict__ xs, int hi
 }
 
 template <typename T>
-__device__ __forceinline__ void load_tokens(const T* __restrict__ xt, float* xs, int n) {
+__device__ __forceinline__ void load_tokens(const T* xt, float* xs, int n) {
     if ((n & 7) == 0 && aligned8(xt)) {
         for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) load8(xt + i, xs + i);
     } else {
@@ -265,7 +264,7 @@ router_logits_tiled_kernel(const T* __restrict__ x, const float* __restrict__ ga
 constexpr int kGatePre = 8;
 
 template <typename T>
-__global__ void router_logits_small_kernel(const T* __restrict__ x, const float* __restrict__ gate,
+__global__ void router_logits_small_kernel(const T* x, const float* __restrict__ gate,
                                            float* __restrict__ logits, int tokens, int hidden, int experts) {
     extern __shared__ __align__(16) float xs[];              // [tokens <= kRouterTokens][hidden]
     __shared__ float part[kRouterWarps][kRouterTokens];
@@ -283,7 +282,7 @@ __global__ void router_logits_small_kernel(const T* __restrict__ x, const float*
             if (i < b) gv[u] = __ldg(reinterpret_cast<const float4*>(g[0]) + i);
         }
     }
-    grid_dependency_wait();      // launched as a dependent: the gate rows are on their way before x is complete
+    grid_dependency_wait();      // launched as a dependent: the gate rows are on their way before x is complete (x: no __restrict__)
     load_tokens(x, xs, tokens * hidden);
     __syncthreads();
     float acc[kRouterTokens][1];
@@ -571,7 +570,7 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
             }
-            cudaError_t e = se::launch_dependent(se::router_logits_small_kernel<T>, dim3(se::ceil_div(experts, 2)),
+            cudaError_t e = SE_LAUNCH_DEPENDENT("logits", se::router_logits_small_kernel<T>, dim3(se::ceil_div(experts, 2)),
                                                  dim3(32 * se::kRouterWarps), smem, stream, (const T*)x, gate, logits,
                                                  tokens, hidden, experts);
             if (e != cudaSuccess) return (int)e;

@@ -148,3 +148,34 @@ def test_131072_tokens_in_portions_then_decoding(long_folder):
         worst = float(np.abs(x - y).max())
         print(f"[long context] {name}: logits rms {rms:.4f}, worst |diff| {worst:.3e} = {worst / rms:.4f} rms")
         assert (np.abs(x - y) <= tu.BF16_SHARE_OF_RMS * rms + tu.BF16_ULP * np.abs(y)).all(), name
+
+
+@pytest.mark.parametrize("starts", [[CONTEXT - 7], [CONTEXT - 7, 40_000, 77]])
+def test_replayed_decode_steps_equal_launched_ones_at_far_positions(long_folder, starts):
+    """Decode steps replayed from a CUDA graph run their kernels back to back, and several of them
+    start as dependents of the kernel before them (their set-up overlaps its end); launched one
+    by one from Python they never overlap.  Both must give the same bits.  Far positions make the
+    rotation angles slow to compute, which widens the window in which a kernel that did not
+    wait for its input would read the previous step's."""
+    from sparseengine_b200.engine.factory import build_runner
+    from sparseengine_b200.engine.runner import StepEntry
+    vocab = LONG["vocab_size"]
+    outs = {}
+    for graphs in (False, True):
+        runner = build_runner(long_folder, dtype="bfloat16", page_size=PAGE,
+                              num_pages=sum(-(-(s + 40) // PAGE) for s in starts) + 4, max_rows=4, decode_graphs=graphs)
+        for i, s in enumerate(starts):          # requests that hold that many tokens without having run them
+            runner.admit(i)
+            runner.cache.reserve(i, s)
+            runner.cache.commit(i, s)
+        g = torch.Generator(device=DEV).manual_seed(11)
+        for slot in runner.slots:               # random keys and values, the same in both runs
+            slot.kv.copy_(torch.randn(slot.kv.shape, generator=g, device=DEV) * 0.5)
+        rows = []
+        for step in range(24):
+            entries = [StepEntry(i, [(31 * step + 7 * i) % vocab], [0]) for i in range(len(starts))]
+            rows.append(runner.step(entries).float().cpu())
+        outs[graphs] = torch.stack(rows)
+        assert (runner.graph_replays > 0) == graphs
+    assert torch.isfinite(outs[True]).all()
+    assert torch.equal(outs[False], outs[True])
