@@ -57,10 +57,13 @@ class PagedAttention(Mixer):
     def forward(self, x, step, slot):
         s = self.spec
         tokens = x.shape[0]
-        qkv = linear(x, self.qkv)
-        q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
+        # the position part first: whatever it launches to make its table then lies before the
+        # projection, and q/k preparation, which starts as the projection's dependent, may read the
+        # table while the projection still runs
         rope = (as_rotary_args(self.position.kernel_args(x.device)) if self.position is not None
                 else RotaryArgs(None, 0))
+        qkv = linear(x, self.qkv)
+        q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
         ops.qk_prep(qkv, self.q_norm, self.k_norm, rope.inv_freq, step.positions, step.token_seq, step.seq_rows,
                     slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
                     head_dim=s.head_dim, rotary_dim=rope.rotary_dim, eps=s.qk_norm_eps, rope_scale=rope.scale,
