@@ -198,10 +198,19 @@ def bench_dense(a, dev):
     return ms, a.n * a.k * 2, 2 * a.tokens * a.n * a.k, extra
 
 
+def bench_read_stream(a, dev):
+    """``--mb`` MB read once by bulk asynchronous copies into shared memory (csrc/read_stream.cu)."""
+    from ..csrc import ops
+    buf = torch.empty(a.mb << 20, dtype=torch.uint8, device=dev).fill_(1)
+    ms = timed(lambda: ops.read_stream(buf), a.iters)
+    ops.error_check(dev)
+    return ms, buf.numel(), 0, {}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", required=True,
-                    choices=["experts", "attention_decode", "attention_prefill", "router", "dense"])
+                    choices=["experts", "attention_decode", "attention_prefill", "router", "dense", "read_stream"])
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=3072)
@@ -219,6 +228,7 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--mb", type=int, default=4096, help="read_stream: bytes to read, in MB")
     ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma_sync"],
                     help="attention_prefill: which of the two tensor-core kernels")
     a = ap.parse_args(argv)
@@ -226,7 +236,8 @@ def main(argv=None) -> int:
         raise SystemExit("kernel_bench needs a CUDA device")
     dev = "cuda:0"
     fn = {"experts": bench_experts, "attention_decode": bench_attention_decode,
-          "attention_prefill": bench_attention_prefill, "router": bench_router, "dense": bench_dense}[a.kernel]
+          "attention_prefill": bench_attention_prefill, "router": bench_router, "dense": bench_dense,
+          "read_stream": bench_read_stream}[a.kernel]
     ms, by, fl, extra = fn(a, dev)
     pk = peaks()
     gbs, tfl = by / ms / 1e6, fl / ms / 1e9

@@ -319,11 +319,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
                     for (int j = 0; j < kXchCols; ++j) mine[j][f] = __float2bfloat16_rn(__uint_as_float(v[j]));
                     asm volatile("bar.sync 1, 128;" ::: "memory");           // both halves of this chunk are there
-#ifndef SE_EXP_SKIP_EPILOGUE
                     if (n < p.n_out) {
-#else
-                    if (n < p.n_out && p.k_dim < 0) {
-#endif
                         const auto gs = xch_s[chunk & 1][0];
                         const auto us = xch_s[chunk & 1][1];
 #pragma unroll

@@ -544,3 +544,12 @@ def gemv(x, w, out):
         _ptr(x, torch.bfloat16, "x"), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"), rows, n_out,
         k_dim, _stream()), "gemv")
     return out
+
+
+# ---- read stream (csrc/read_stream.cu) ---------------------------------------------------------
+
+def read_stream(t: torch.Tensor) -> None:
+    """Read a contiguous tensor once with bulk asynchronous copies into shared memory, the way the
+    weight-streaming GEMMs read HBM, and drop what arrives (a measuring aid: benchmarks time it)."""
+    _check(_fn("se_read_stream", "plpp")(_ptr(t, None, "tensor"), t.numel() * t.element_size(),
+                                         _ptr(error_word(t.device)), _stream()), "read_stream")

@@ -953,3 +953,17 @@ def test_router_logits_from_tensor_cores_are_32_bit_accurate(tokens, hidden, exp
     part.split_router_min_tokens = None
     ids2, _ = part.route(x)
     assert bool((ids2.long().sort(-1).values == want)[gap > 1e-5].all())
+
+
+def test_read_stream_reads_any_size_and_reports_nothing():
+    """The measuring aid that reads a tensor through bulk copies into shared memory: whole
+    stages only (what is left of a 32 KB stage is not read), any number of stages, no result and
+    no error code."""
+    from sparseengine_b200.csrc import ops
+    for nbytes in (1, 32 * 1024, 5 * 32 * 1024 + 17, 48 * 32 * 1024 * 3 + 32 * 1024, 40 << 20):
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+        ops.read_stream(buf)
+        torch.cuda.synchronize()
+        ops.error_check(DEV)
+    with pytest.raises(ValueError):
+        ops.read_stream(torch.zeros(64 * 1024 + 1, dtype=torch.uint8, device=DEV)[1:])      # not 16-byte aligned
