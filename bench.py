@@ -258,6 +258,7 @@ def run_ours(args) -> dict:
                "frac": round(flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
                "hbm_frac": round(pre_bytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
                "distinct_experts_per_layer": round(per_layer, 1)}
+    prefill["binding_roof"] = "bf16 flops" if prefill["frac"] >= prefill["hbm_frac"] else "hbm bytes"
 
     # ---- an extra point: four such prompts in one step (8,192 tokens: towards compute-bound) ----
     prompts4 = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(4)]
