@@ -10,17 +10,20 @@
 //                   (128-byte swizzle), S in tensor memory (two buffers per query tile);
 //   softmax         four warps, one thread per row: tcgen05.ld of its row of S, mask
 //                   (causal, window, end of keys), running maximum and sum in 32-bit, P
-//                   rounded to bfloat16 and written to shared memory as the next A operand;
-//   O += P·V        tcgen05.mma, M 128 x N 128 x K 64, V straight from its pages (dims
-//                   contiguous: the MN-major B operand), O in tensor memory.
+//                   rounded to bfloat16 and written back to tensor memory over the row's
+//                   scores (tcgen05.st, two values per column);
+//   O += P·V        tcgen05.mma with the A operand (P) in tensor memory, M 128 x N 128 x K 64,
+//                   V straight from its pages (dims contiguous: the MN-major B operand), O in
+//                   tensor memory.
 //
 // Tensor memory is used in full: O of the two tiles (2 x 128 columns) and their S buffers
-// (2 x 2 x 64).  The running maximum only moves when a row's maximum grows by more than 2^8
+// (2 x 2 x 64), whose first halves hold P between the softmax and P·V; shared memory holds
+// the two Q tiles and five K/V stages.  The running maximum only moves when a row's maximum grows by more than 2^8
 // (then O and the sum are rescaled), so O is read back from tensor memory rarely; the final
 // division by the sum is exact for whatever reference maximum was used.
 //
 // Warp roles (12 warps): warps 0 and 10 gather K/V tiles from their pages with cp.async into
-// four stages, alternately, and tie each tile's barrier to their copies
+// five stages, alternately, and tie each tile's barrier to their copies
 // (cp.async.mbarrier.arrive.noinc), so a tile is announced the moment it has landed and the
 // loaders never wait for data; warp 1 owns tensor memory and issues the MMAs of query tile 0,
 // warp 11 those of tile 1 (S(j) first, then P·V of tile j-1 as its P arrives), independently
@@ -38,14 +41,13 @@ constexpr int D = 128;
 constexpr int kRows = 128;
 constexpr int kKeys = 64;
 constexpr int kTiles = 2;                            // query tiles per CTA
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kLoaderWarp2 = 2 + 4 * kTiles;         // the second loader warp
 constexpr int kMmaWarp2 = kLoaderWarp2 + 1;          // the MMA issuer of query tile 1 (tile 0: warp 1)
 constexpr int kThreads = 32 * (kMmaWarp2 + 1);       // loader, MMA, 4 softmax warps per query tile, loader, MMA
 constexpr int kHalfBytes = 64 * 128;                 // [64 rows][64 dims] bf16: rows of 128 bytes
 constexpr int kQBytes = 2 * kRows * 128;             // two dim-halves of [128 rows][64 dims]
 constexpr int kKVStageBytes = 4 * kHalfBytes;        // K halves, V halves
-constexpr int kPBytes = kRows * 128;                 // [128 rows][64 keys] bf16
 constexpr uint32_t kSpin = 1u << 24;
 constexpr float kRescaleThreshold = 8.f;             // log2 units
 
@@ -94,6 +96,11 @@ __device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
 }
+// the same with the A operand in tensor memory (rows = lanes, two bfloat16 per 32-bit column)
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(id), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -127,7 +134,9 @@ __device__ __forceinline__ float ex2(float x) {
 struct Bars {
     uint64_t kv_full[kStages], kv_empty[kStages];
     uint64_t s_full[kTiles][2], s_empty[kTiles][2];      // per query tile: two S buffers
-    uint64_t p_full[kTiles], p_empty[kTiles];            // per query tile: one P buffer
+    uint64_t p_full[kTiles][2], p_empty[kTiles];         // per query tile: P of a tile is complete (one per S buffer); its P·V has finished
+    uint64_t o_done[kTiles];                             // per query tile: the last P·V has finished (a warp that never had to
+                                                         // wait for p_empty may be phases behind it, so the end has a barrier of its own)
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -139,7 +148,6 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                               // [2 tiles][2 halves][128 rows][128 B]
     uint8_t* kv_s = q_s + kTiles * kQBytes;            // [stages][K half0, K half1, V half0, V half1]
-    uint8_t* p_s = kv_s + kStages * kKVStageBytes;     // [2 tiles][128 rows][128 B]
     __shared__ __align__(8) Bars bars;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
@@ -174,8 +182,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 mbar_init(bar(&bars.s_full[x][b]), 1);
                 mbar_init(bar(&bars.s_empty[x][b]), 4);      // one arrival per softmax warp
             }
-            mbar_init(bar(&bars.p_full[x]), 4);
+            mbar_init(bar(&bars.p_full[x][0]), 4);
+            mbar_init(bar(&bars.p_full[x][1]), 4);
             mbar_init(bar(&bars.p_empty[x]), 1);
+            mbar_init(bar(&bars.o_done[x]), 1);
         }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -266,14 +276,14 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             const uint32_t id_s = idesc(kKeys, 0), id_o = idesc(D, 1);
             bool ok = true;
             auto issue_pv = [&](int i) {
-                if (!mbar_wait(bar(&bars.p_full[x]), i & 1, &abort_s)) { ok = false; return; }
+                if (!mbar_wait(bar(&bars.p_full[x][i & 1]), (i >> 1) & 1, &abort_s)) { ok = false; return; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t va = smem_u32(kv_s) + (i % kStages) * kKVStageBytes + 2 * kHalfBytes;
-                const uint32_t pa = smem_u32(p_s) + x * kPBytes;
+                const uint32_t pa = tmem_s(x, i & 1);        // P of tile i lies over the first half of its S buffer
 #pragma unroll
-                for (int kk = 0; kk < kKeys / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-                    umma(tmem_o(x), desc_kmajor(pa) + (uint64_t)(kk * 2), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
-                         (i > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kKeys / 16; ++kk)      // 16 keys per MMA: 8 columns of P, two 8-key groups of V
+                    umma_ts(tmem_o(x), pa + (uint32_t)(kk * 8), desc_mnmajor(va + kk * 2048, kHalfBytes), id_o,
+                            (i > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(bar(&bars.p_empty[x]));
                 umma_commit(bar(&bars.kv_empty[i % kStages]));
             };
@@ -294,6 +304,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 if (j >= 1) issue_pv(j - 1);
             }
             if (ok) issue_pv(num_tiles - 1);
+            if (ok) umma_commit(bar(&bars.o_done[x]));
             if (!ok) { abort_s = 1; atomicCAS(error, 0, 12); }
         }
     } else if (warp < 2 + 4 * kTiles) {
@@ -307,7 +318,6 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         const int pos = q_start + rr / group;
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        uint8_t* prow = p_s + x * kPBytes;
         float m_ref = -INFINITY, l = 0.f;                  // reference maximum (log2 units), running sum
         bool ok = true;
         for (int j = 0; j < num_tiles && ok; ++j) {
@@ -352,9 +362,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 m_ref = mx;
                 l *= factor;
             }
-            // P·V of the previous tile has finished: O is at rest and the P buffer is free
-            if (j >= 1 && !mbar_wait(bar(&bars.p_empty[x]), (j - 1) & 1, &abort_s)) { ok = false; break; }
             if (__any_sync(0xffffffffu, need)) {
+                // O must be at rest: P·V of the previous tile has finished.  (Only then: a warp whose
+                // rows keep their reference maximum runs on, up to a tile ahead of the others, which
+                // is why P's barrier exists once per S buffer.)
+                if (j >= 1 && !mbar_wait(bar(&bars.p_empty[x]), (j - 1) & 1, &abort_s)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -370,26 +382,28 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_use;
+            // P goes back to tensor memory, over the row's own scores (which are in registers now):
+            // two bfloat16 per column, the A operand of P·V.
+            uint32_t packed[32];
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
-                uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     // p = 2^(s * scale - m): one fused multiply-add and one ex2 per element
                     const float p0 = ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), scale_log2, neg_m));
                     const float p1 = ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), scale_log2, neg_m));
                     sum4[i] += p0 + p1;
-                    packed[i] = se::mma::pack_bf16(p0, p1);
+                    packed[c8 * 4 + i] = se::mma::pack_bf16(p0, p1);
                 }
-                *reinterpret_cast<uint4*>(prow + sw128(r, c8)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+            tmem_st32(tmem_s(x, b) + lane_addr, packed);
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(&bars.p_full[x]));
+            if (lane == 0) mbar_arrive(bar(&bars.p_full[x][b]));
         }
-        if (ok && mbar_wait(bar(&bars.p_empty[x]), (num_tiles - 1) & 1, &abort_s)) {
+        if (ok && mbar_wait(bar(&bars.o_done[x]), 0, &abort_s)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
@@ -436,7 +450,7 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
     using namespace se::fa;
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)kTiles * kQBytes + kStages * kKVStageBytes + kTiles * kPBytes + 1024;
+    const size_t smem = (size_t)kTiles * kQBytes + kStages * kKVStageBytes + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

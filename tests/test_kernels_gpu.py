@@ -611,6 +611,43 @@ def test_prefill_attention_tensor_cores(hq, hkv, d, page, window, impl):
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("impl", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("hq,hkv", [(6, 2), (12, 2)])
+def test_prefill_attention_when_row_maxima_keep_moving(hq, hkv, impl):
+    """Scores with a spread of about 10 (in units of e) make a row's maximum jump by more than
+    the kernels' rescaling threshold again and again, in some rows of a tile and not in others:
+    the warps of a tile then run at different paces (the ones that rescale wait for the
+    accumulator to be at rest), which is where a barrier shared between them, or a wait that may
+    be a phase behind, shows.  The last rows of a tile, which see the last keys alone, are the
+    ones that rescale there.  Against the plain attention, tightly, and bit for bit against a
+    second run."""
+    from sparseengine_b200.csrc import ops
+    d, page, n = 128, 16, 700
+    fn = ops.attn_prefill_tc if impl == "tcgen05" else ops.attn_prefill
+    dtype = torch.bfloat16
+    table, rows, _, _, cache = _cache_setup([n], hkv, d, page, dtype)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = (torch.randn(n, hq, d, generator=g, device=DEV) * 3).to(dtype)
+    k = torch.randn(n, hkv, d, generator=g, device=DEV).to(dtype)
+    v = torch.randn(n, hkv, d, generator=g, device=DEV).to(dtype)
+    p = torch.arange(n, device=DEV)
+    pg = table[int(rows[0]), (p // page).long()].long()
+    cache[pg, 0, :, (p % page).long()] = k
+    cache[pg, 1, :, (p % page).long()] = v
+    outs = []
+    for _ in range(3):
+        out = torch.zeros_like(q)
+        fn(q.view(n, hq * d), cache, table, rows, torch.tensor([0, n], dtype=torch.int32, device=DEV),
+           torch.tensor([n], dtype=torch.int32, device=DEV), out.view(n, hq * d), entries=1, max_q_len=n, num_heads=hq,
+           num_kv_heads=hkv, head_dim=d, page_size=page, scale=d ** -0.5)
+        outs.append(out)
+    ops.error_check(DEV)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ref = _attention_reference(q.float().cpu(), [k.float().cpu()], [v.float().cpu()], [n], [0], dtype, None)
+    err = (outs[0].float().cpu() - ref).abs()
+    assert float(err.max()) < 3e-2 and float(err.mean()) < 2e-3, (float(err.max()), float(err.mean()))
+
+
 @pytest.mark.parametrize("kernel", ["decode", "prefill_mma_sync", "prefill_tcgen05"])
 @pytest.mark.parametrize("window", [None, 1000])
 def test_tensor_core_attention_far_key_and_window_edge(kernel, window):
