@@ -78,6 +78,7 @@ KERNEL_TUNING_KEYS = {
     "attention_portion_min_tokens": "portion_min_tokens",               # ... and smaller ones whose longest entry has this many tokens
     "attention_portion_min_average": "portion_min_average",             # ... and this many tokens per entry on average
     "gemv_max_out_features": None,                                      # few-row projections wider than this take the library product
+    "gemv_max_rows": None,                                              # ... and so do projections of more rows than this
     "router_tensor_core_min_tokens": "split_router_min_tokens",         # prompt steps from this size take router logits from tensor cores
     "moe_pair_min_rows": "pair_min_rows",                               # (token, slot) rows from which experts may run on pairs of SMs
     "moe_pair_min_rows_per_expert": "pair_min_rows_per_expert",         # ... if the experts that get rows have this many each
@@ -99,7 +100,10 @@ def apply_kernel_tuning(model: Model, tuning: dict) -> None:
         attr = KERNEL_TUNING_KEYS[key]
         if attr is None:
             from ..parts import linear
-            linear.GEMV_MAX_OUT = int(value)
+            if key == "gemv_max_rows":
+                linear.GEMV_MAX_ROWS = int(value)
+            else:
+                linear.GEMV_MAX_OUT = int(value)
             continue
         for b in model.blocks:
             for part in b.parts().values():

@@ -152,4 +152,11 @@ def test_kernel_tuning_options_are_checked_and_reach_the_parts():
     m = Model(spec, torch.float32)
     apply_kernel_tuning(m, cfg.kernel_tuning)
     assert all(b.mixer.decode_kernel_max_tokens == 64 and b.feed_forward.pair_min_rows == 4096 for b in m.blocks)
+    from sparseengine_b200.parts import linear
+    before = linear.GEMV_MAX_ROWS, linear.GEMV_MAX_OUT
+    try:
+        apply_kernel_tuning(m, {"gemv_max_rows": 3, "gemv_max_out_features": 100})
+        assert (linear.GEMV_MAX_ROWS, linear.GEMV_MAX_OUT) == (3, 100)
+    finally:
+        linear.GEMV_MAX_ROWS, linear.GEMV_MAX_OUT = before
     assert set(KERNEL_TUNING_KEYS) >= {"router_tensor_core_min_tokens", "moe_pair_min_rows_per_expert"}

@@ -109,7 +109,7 @@ def test_preemption_recomputes_and_gives_the_same_tokens(folder_a):
 
 def test_preemption_in_bfloat16_keeps_what_rounding_cannot_touch(folder_a):
     """bfloat16: a recomputed request's logits differ from its decode steps' in the last bits
-    (and so do those of requests that share a step with the recomputation: more than 16 rows
+    (and so do those of requests that share a step with the recomputation: more than 8 rows
     take another matrix product), so a token may change where a draw falls on an edge, and
     everything after it with it.  What holds whatever the rounding: up to the first preemption
     the run is the roomy run, token for token; every request ends with its full count; no page

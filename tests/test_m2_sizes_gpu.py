@@ -18,7 +18,7 @@ M2_LAYER_SIZES = {
     "hidden_act": "silu", "qk_norm_type": "per_layer", "use_qk_norm": True, "scoring_func": "sigmoid",
     "use_routing_bias": True, "use_mtp": True, "shared_intermediate_size": 0,
 }
-# bfloat16 logits here are below 8 in size, so one unit in the last place is 2^-5; up to 16 rows the
+# bfloat16 logits here are below 8 in size, so one unit in the last place is 2^-5; up to 8 rows the
 # dense projections take this library's kernel and beyond that the library product, whose sums differ
 # in the last bit.  32-bit: only the order of sums differs.
 TOL = {"bfloat16": 2 ** -5 + 1e-6, "float32": 3e-4}
@@ -60,7 +60,7 @@ def test_a_request_decodes_the_same_beside_any_number_of_others(engine):
             alone = logits[0]
         diff = (logits[0] - alone).abs().max().item()
         assert diff <= TOL[dtype], f"{dtype}: request 0 among {batch}: |diff| {diff:.3e}"
-        if dtype == "bfloat16" and batch <= 16:
+        if dtype == "bfloat16" and batch <= 8:
             assert diff == 0.0, f"request 0 among {batch}: the step's kernels are the same, the bits must be"
 
 
