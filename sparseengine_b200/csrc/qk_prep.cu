@@ -235,6 +235,132 @@ qk_prep_vec_kernel(const T* __restrict__ qkv, const T* __restrict__ q_w, const T
     }
 }
 
+// The same for bfloat16 with fewer instructions (the kernel above spends its time issuing them,
+// not waiting for memory): values stay packed in pairs, the product with the norm weight is a
+// packed bfloat16 multiply (the exact product rounded once, which is what rounding the 32-bit
+// product gives), and a thread steps through its work items without a division.  Bit for bit
+// the results of the kernel above.
+__global__ void __launch_bounds__(256)
+qk_prep_vec_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
+                        const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ inv_freq,
+                        const int* __restrict__ positions, const int* __restrict__ token_seq,
+                        const int* __restrict__ seq_rows, const int* __restrict__ table, int table_stride,
+                        __nv_bfloat16* __restrict__ cache, __nv_bfloat16* __restrict__ q_out, int hq, int hkv, int d,
+                        int rot, float eps, float rope_scale, int page_size, int write_cache, int num_pages,
+                        int* __restrict__ error) {
+    extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
+    __shared__ float scratch[2][33];
+    grid_dependency_trigger();             // the attention kernel that follows may find its keys' pages meanwhile
+    const int t = blockIdx.x;
+    const int qn = hq * d, kn = hkv * d;
+    const __nv_bfloat16* row = qkv + (size_t)t * (qn + 2 * kn);
+    const int pos = positions[t];
+    const int ts = write_cache ? token_seq[t] : 0;
+    const int half = rot / 2;
+    auto sum_squares = [&](const __nv_bfloat16* part, int n) {
+        float ss = 0.f;
+        for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(part + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {      // in the order of the elements, as the kernel above adds them
+                const float2 f = __bfloat1622float2(h[j]);
+                ss += f.x * f.x;
+                ss += f.y * f.y;
+            }
+        }
+        return ss;
+    };
+    float ss_q = 0.f, ss_k = 0.f;
+    if (q_w != nullptr) {
+        ss_q = sum_squares(row, qn);
+        ss_k = sum_squares(row + qn, kn);
+    }
+    const int table_row = write_cache ? seq_rows[ts] : 0;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float sn, c;
+        sincosf((float)pos * inv_freq[j], &sn, &c);
+        cs[j] = c * rope_scale;
+        cs[half + j] = sn * rope_scale;
+    }
+    const int page = write_cache ? table[(size_t)table_row * table_stride + pos / page_size] : 0;
+    if (write_cache && !page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_QK_PREP)) write_cache = 0;   // q only
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_w != nullptr) {
+        inv_q = 1.0f / sqrtf(block_sum(ss_q, scratch[0]) / (float)qn + eps);
+        inv_k = 1.0f / sqrtf(block_sum(ss_k, scratch[1]) / (float)kn + eps);
+    }
+    __syncthreads();                       // cos/sin are in shared memory
+    __nv_bfloat16* kv_base = nullptr;
+    if (write_cache)
+        kv_base = cache + (size_t)page * 2 * hkv * page_size * d + (size_t)(pos % page_size) * d;
+    const int groups = d / 8, rot_groups = half / 8;
+    const int live = groups - rot_groups;                  // items per head: rotated pairs, then pass-through groups
+    const int qk_heads = hq + (write_cache ? hkv : 0);
+    // eight values of a head, normalised: cast(x * inv) * w, the product rounded once
+    auto normed8 = [&](const __nv_bfloat16* src, const __nv_bfloat16* w, float inv, __nv_bfloat162 (&out)[4]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        if (w == nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[j] = x2[j];
+            return;
+        }
+        const uint4 wraw = *reinterpret_cast<const uint4*>(w);
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(x2[j]);
+            out[j] = __hmul2(__floats2bfloat162_rn(f.x * inv, f.y * inv), w2[j]);
+        }
+    };
+    // a thread's items are threadIdx.x, + 256, ...: (head, item of the head) without dividing each time
+    const int step_h = (int)blockDim.x / live, step_i = (int)blockDim.x % live;
+    int hh = (int)threadIdx.x / live, i = (int)threadIdx.x % live;
+    for (; hh < qk_heads; hh += step_h, i += step_i) {
+        if (i >= live) { i -= live; ++hh; if (hh >= qk_heads) break; }
+        const bool is_q = hh < hq;
+        const int h = is_q ? hh : hh - hq;
+        const __nv_bfloat16* w = is_q ? q_w : k_w;
+        const float inv = is_q ? inv_q : inv_k;
+        const __nv_bfloat16* src = row + (is_q ? 0 : qn) + h * d;
+        __nv_bfloat16* dst = is_q ? q_out + (size_t)t * qn + h * d : kv_base + (size_t)h * page_size * d;
+        if (i < rot_groups) {
+            __nv_bfloat162 x1[4], x2[4];
+            normed8(src + 8 * i, w ? w + h * d + 8 * i : nullptr, inv, x1);
+            normed8(src + 8 * i + half, w ? w + h * d + 8 * i + half : nullptr, inv, x2);
+            uint4 o1, o2;
+            __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&o2);
+            const float4* c4 = reinterpret_cast<const float4*>(cs + 8 * i);
+            const float4* s4 = reinterpret_cast<const float4*>(cs + half + 8 * i);
+            const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+            const float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+            const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = __bfloat1622float2(x1[j]), b = __bfloat1622float2(x2[j]);
+                p1[j] = __floats2bfloat162_rn(a.x * c[2 * j] - b.x * sn[2 * j], a.y * c[2 * j + 1] - b.y * sn[2 * j + 1]);
+                p2[j] = __floats2bfloat162_rn(b.x * c[2 * j] + a.x * sn[2 * j], b.y * c[2 * j + 1] + a.y * sn[2 * j + 1]);
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * i) = o1;
+            *reinterpret_cast<uint4*>(dst + 8 * i + half) = o2;
+        } else {
+            __nv_bfloat162 x[4];
+            const int dim0 = 8 * (i + rot_groups);
+            normed8(src + dim0, w ? w + h * d + dim0 : nullptr, inv, x);
+            *reinterpret_cast<uint4*>(dst + dim0) = *reinterpret_cast<const uint4*>(x);
+        }
+    }
+    if (write_cache) {                     // value heads: copies
+        for (int item = threadIdx.x; item < hkv * groups; item += blockDim.x) {
+            const int h = item / groups, g = item - h * groups;
+            *reinterpret_cast<uint4*>(kv_base + (size_t)(hkv + h) * page_size * d + 8 * g) =
+                *reinterpret_cast<const uint4*>(row + qn + kn + h * d + 8 * g);
+        }
+    }
+}
+
 // inv_rms[t] = (1/sqrt(mean(q^2)+eps), 1/sqrt(mean(k^2)+eps)) of token t's whole projections:
 // for many tokens the statistics are taken once here instead of once per head.
 template <typename T>
@@ -262,6 +388,13 @@ __global__ void qk_inv_rms_kernel(const T* __restrict__ qkv, float* __restrict__
 
 }  // namespace se
 
+// SE_QK_PREP_GENERIC=1: bfloat16 steps of many tokens take the kernel that also serves 32-bit (a
+// testing aid: the two give the same bits).
+static bool se_qk_prep_generic_vec() {
+    static const bool v = [] { const char* e = ::getenv("SE_QK_PREP_GENERIC"); return e != nullptr && e[0] == '1'; }();
+    return v;
+}
+
 extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, const float* inv_freq,
                           const int* positions, const int* token_seq, const int* seq_rows, const int* table,
                           int table_stride, void* cache, void* q_out, int tokens, int hq, int hkv, int d,
@@ -276,6 +409,13 @@ extern "C" int se_qk_prep(const void* qkv, const void* q_w, const void* k_w, con
     const bool vec = tokens > 64 && pairing == 0 && (q_w == nullptr) == (k_w == nullptr) && d % 8 == 0 && (rot / 2) % 8 == 0 &&
                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0 &&
                      ((size_t)page_size * d * elem) % 16 == 0;
+    if (vec && dtype == SE_DTYPE_BF16 && !se_qk_prep_generic_vec()) {
+        se::qk_prep_vec_bf16_kernel<<<tokens, 256, smem, stream>>>(
+            (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, inv_freq, positions, token_seq,
+            seq_rows, table, table_stride, (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, hq, hkv, d, rot, eps, rope_scale,
+            page_size, write_cache, num_pages, error);
+        SE_LAUNCH_CHECK();
+    }
     if (vec) {
         SE_DISPATCH_DTYPE(dtype, T,
             se::qk_prep_vec_kernel<T><<<tokens, 256, smem, stream>>>(

@@ -1004,3 +1004,53 @@ def test_read_stream_reads_any_size_and_reports_nothing():
         ops.error_check(DEV)
     with pytest.raises(ValueError):
         ops.read_stream(torch.zeros(64 * 1024 + 1, dtype=torch.uint8, device=DEV)[1:])      # not 16-byte aligned
+
+
+_QK_PREP_SCRIPT = r"""
+import sys, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
+import plain_m2
+from sparseengine_b200.csrc import ops
+DEV = "cuda:0"
+out = {{}}
+for name, (hq, hkv, d, rot, page, norm, tokens) in {{"m2": (48, 8, 128, 64, 16, True, 300), "odd": (5, 3, 64, 32, 8, True, 130),
+                                                    "plain": (6, 2, 128, 64, 16, False, 200), "full": (4, 4, 64, 64, 4, True, 70)}}.items():
+    g = torch.Generator(device=DEV).manual_seed(len(name))
+    qkv = (torch.randn(tokens, (hq + 2 * hkv) * d, generator=g, device=DEV) * 2).bfloat16()
+    qw = (1 + 0.1 * torch.randn(hq * d, generator=g, device=DEV)).bfloat16() if norm else None
+    kw = (1 + 0.1 * torch.randn(hkv * d, generator=g, device=DEV)).bfloat16() if norm else None
+    inv = plain_m2.rope_inv_freq(rot, 1e6).to(DEV)
+    pages = -(-(tokens + 900) // page) + 1
+    table = torch.arange(pages, dtype=torch.int32, device=DEV).flip(0).view(1, -1).contiguous()
+    cache = torch.zeros(pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+    positions = torch.arange(900, 900 + tokens, dtype=torch.int32, device=DEV)
+    zeros = torch.zeros(tokens, dtype=torch.int32, device=DEV)
+    q_out = torch.empty(tokens, hq * d, dtype=torch.bfloat16, device=DEV)
+    ops.qk_prep(qkv, qw, kw, inv, positions, zeros, zeros[:1], table, cache, q_out, num_heads=hq, num_kv_heads=hkv,
+                head_dim=d, rotary_dim=rot, eps=1e-6, rope_scale=1.0, page_size=page)
+    ops.error_check(DEV)
+    out[name + ".q"] = q_out.cpu()
+    out[name + ".cache"] = cache.cpu()
+torch.save(out, sys.argv[1])
+"""
+
+
+def test_qk_prep_bfloat16_kernel_gives_the_bits_of_the_general_one(tmp_path):
+    """Steps of many bfloat16 tokens take a kernel of their own (packed pairs, fewer instructions);
+    SE_QK_PREP_GENERIC=1 sends them through the kernel that also serves 32-bit.  The library reads
+    the switch once, so each kernel runs in a process of its own; queries and cache must be equal
+    bit for bit."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "qk.py"
+    script.write_text(_QK_PREP_SCRIPT.format(root=root))
+    outs = []
+    for generic in ("0", "1"):
+        path = str(tmp_path / f"out{generic}.pt")
+        subprocess.run([sys.executable, str(script), path], check=True, env=dict(os.environ, SE_QK_PREP_GENERIC=generic))
+        outs.append(torch.load(path))
+    assert outs[0].keys() == outs[1].keys()
+    for k in outs[0]:
+        assert torch.equal(outs[0][k], outs[1][k]), k
