@@ -219,13 +219,19 @@ def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormaliz
 
 def router_select(logits, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
                   impl="auto"):
-    """Selection alone from given 32-bit logits.  ``impl``: "auto", "block" (a block per token, any
-    size and score function) or "warp" (a warp per token: sigmoid scores, up to 256 experts)."""
-    tokens, experts = logits.shape
-    _check(_fn("se_router_select", "pppp" "iiiii" "f" "ip")(
-        _ptr(logits, torch.float32, "logits"), _ptr(bias, torch.float32, "bias"), _ptr(ids, torch.int32, "ids"),
-        _ptr(weights, torch.float32, "weights"), tokens, experts, top_k, SCORE_FN[score_fn], int(renormalize),
-        float(routed_scale), {"auto": 0, "block": 1, "warp": 2}[impl], _stream()), "router_select")
+    """Selection alone from given 32-bit logits [tokens, experts], or from their parts
+    [chunks, tokens, terms, experts], whose sum over chunks and terms (taken in that order inside the
+    kernel) is the logit.  ``impl``: "auto", "block" (a block per token, any size and score function)
+    or "warp" (a warp per token: sigmoid scores, up to 256 experts)."""
+    if logits.dim() == 4:
+        chunks, tokens, terms, experts = logits.shape
+    else:
+        (tokens, experts), chunks, terms = logits.shape, 1, 1
+    _check(_fn("se_router_select", "pii" "ppp" "iiiii" "f" "ip")(
+        _ptr(logits, torch.float32, "logits"), chunks, terms, _ptr(bias, torch.float32, "bias"),
+        _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"), tokens, experts, top_k,
+        SCORE_FN[score_fn], int(renormalize), float(routed_scale), {"auto": 0, "block": 1, "warp": 2}[impl], _stream()),
+        "router_select")
     return ids, weights
 
 

@@ -323,9 +323,32 @@ __global__ void router_logits_small_kernel(const T* x, const float* __restrict__
     }
 }
 
+// A logit may arrive in parts to be added: parts[chunk][token][term][expert] (the partial
+// products of a tensor-core router product: K in chunks, the 32-bit gate in terms), summed here
+// in one fixed order, chunk by chunk and term by term, instead of by a kernel of its own.
+struct LogitParts {
+    const float* p;
+    int tokens, experts, chunks, terms;
+};
+__device__ __forceinline__ float logit_at(const LogitParts& s, int t, int e) {
+    if (s.chunks * s.terms == 1) return s.p[(size_t)t * s.experts + e];
+    // the parts' loads do not wait for one another: they are issued several at a time, the adds
+    // follow in order
+    float v = 0.f;
+    const float* base = s.p + (size_t)t * s.terms * s.experts + e;
+    const size_t chunk_stride = (size_t)s.tokens * s.terms * s.experts;
+#pragma unroll 2
+    for (int c = 0; c < s.chunks; ++c) {
+        const float* pc = base + c * chunk_stride;
+#pragma unroll 3
+        for (int k = 0; k < s.terms; ++k) v += __ldg(pc + (size_t)k * s.experts);
+    }
+    return v;
+}
+
 // One block per token: score function, selection bias, top-k in the reference's order,
 // renormalisation.
-__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+__global__ void router_select_kernel(const LogitParts src, const float* __restrict__ bias,
                                      int* __restrict__ ids, float* __restrict__ weights, int experts, int top_k,
                                      int score_fn, int renormalize, float routed_scale) {
     extern __shared__ __align__(16) float sel[];
@@ -338,7 +361,12 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     __shared__ float thr_s;
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const float* lg = logits + (size_t)t * experts;
+    const float* lg = src.p + (size_t)t * experts;
+    if (src.chunks * src.terms != 1) {       // the sums first, into the array that takes the scores below
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) sj[e] = logit_at(src, t, e);
+        __syncthreads();
+        lg = sj;
+    }
     if (score_fn == 1) {   // softmax over experts
         float mx = -INFINITY;
         for (int e = threadIdx.x; e < experts; e += blockDim.x) mx = fmaxf(mx, lg[e]);
@@ -434,7 +462,7 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
 constexpr int kSelPer = 8;             // experts per lane
 
 __global__ void __launch_bounds__(256)
-router_select_warp_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+router_select_warp_kernel(const LogitParts src, const float* __restrict__ bias, int* __restrict__ ids,
                           float* __restrict__ weights, int tokens, int experts, int top_k, int renormalize,
                           float routed_scale) {
     extern __shared__ float sel_w[];                 // [warps][top_k] probabilities of the chosen, in slot order
@@ -445,6 +473,27 @@ router_select_warp_kernel(const float* __restrict__ logits, const float* __restr
     const unsigned below = (1u << lane) - 1u;
     float pj[kSelPer], sj[kSelPer];
     unsigned key[kSelPer];                           // the score as an unsigned key in the same order; 0 = none or taken
+    // the lane's logits; parts are added chunk by chunk and term by term, the loads of a step for
+    // all of the lane's experts at once
+    float lg[kSelPer];
+    if (src.chunks * src.terms == 1) {
+#pragma unroll
+        for (int i = 0; i < kSelPer; ++i) lg[i] = 32 * i + lane < experts ? src.p[(size_t)t * experts + 32 * i + lane] : 0.f;
+    } else {
+#pragma unroll
+        for (int i = 0; i < kSelPer; ++i) lg[i] = 0.f;
+        const float* base = src.p + (size_t)t * src.terms * experts + lane;
+        const size_t chunk_stride = (size_t)src.tokens * src.terms * experts;
+        for (int c = 0; c < src.chunks; ++c) {
+#pragma unroll 3
+            for (int k = 0; k < src.terms; ++k) {
+                const float* pk = base + c * chunk_stride + (size_t)k * experts;
+#pragma unroll
+                for (int i = 0; i < kSelPer; ++i)
+                    if (32 * i + lane < experts) lg[i] += __ldg(pk + 32 * i);
+            }
+        }
+    }
 #pragma unroll
     for (int i = 0; i < kSelPer; ++i) {
         const int e = 32 * i + lane;
@@ -452,7 +501,7 @@ router_select_warp_kernel(const float* __restrict__ logits, const float* __restr
         sj[i] = 0.f;
         key[i] = 0u;
         if (e < experts) {
-            pj[i] = 1.f / (1.f + expf(-logits[(size_t)t * experts + e]));
+            pj[i] = 1.f / (1.f + expf(-lg[i]));
             const float sc = pj[i] + (bias ? bias[e] : 0.f);
             sj[i] = (sc == sc) ? sc : INFINITY;      // a NaN score counts as +inf
             const unsigned u = __float_as_uint(sj[i]);
@@ -514,8 +563,10 @@ router_select_warp_kernel(const float* __restrict__ logits, const float* __restr
 }  // namespace se
 
 // impl: 0 = by sizes, 1 = the block-per-token kernel, 2 = the warp-per-token kernel
-static int launch_select(const float* logits, const float* bias, int* ids, float* weights, int tokens, int experts,
-                         int top_k, int score_fn, int renormalize, float routed_scale, int impl, cudaStream_t stream) {
+static int launch_select(const float* logits, int chunks, int terms, const float* bias, int* ids, float* weights,
+                         int tokens, int experts, int top_k, int score_fn, int renormalize, float routed_scale, int impl,
+                         cudaStream_t stream) {
+    const se::LogitParts src{logits, tokens, experts, chunks, terms};
     const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
     const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256;
     if (impl == 2 && !warp_ok) return SE_ERR_UNSUPPORTED;
@@ -524,25 +575,27 @@ static int launch_select(const float* logits, const float* bias, int* ids, float
     // for the block kernel), so it pays when there are tokens enough to fill the SMs with warps.
     if (impl == 2 || (impl == 0 && warp_ok && tokens >= 128)) {
         se::router_select_warp_kernel<<<se::ceil_div(tokens, 8), 256, 8 * top_k * sizeof(float), stream>>>(
-            logits, bias, ids, weights, tokens, experts, top_k, renormalize, routed_scale);
+            src, bias, ids, weights, tokens, experts, top_k, renormalize, routed_scale);
         SE_LAUNCH_CHECK();
     }
     if (smem_sel > 40 * 1024) {      // static shared memory counts against the 48 KB a kernel has without asking
         cudaError_t e = cudaFuncSetAttribute(se::router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sel);
         if (e != cudaSuccess) return (int)e;
     }
-    se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(logits, bias, ids, weights, experts, top_k, score_fn,
+    se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(src, bias, ids, weights, experts, top_k, score_fn,
                                                                 renormalize, routed_scale);
     SE_LAUNCH_CHECK();
 }
 
-// Selection alone, from given logits (float [tokens, experts]).
-extern "C" int se_router_select(const float* logits, const float* bias, int* ids, float* weights, int tokens, int experts,
-                                int top_k, int score_fn, int renormalize, float routed_scale, int impl,
-                                cudaStream_t stream) {
+// Selection alone, from given logits: float [tokens, experts], or float [chunks, tokens, terms,
+// experts] whose sum over chunks and terms (in that order) is the logit.
+extern "C" int se_router_select(const float* logits, int chunks, int terms, const float* bias, int* ids, float* weights,
+                                int tokens, int experts, int top_k, int score_fn, int renormalize, float routed_scale,
+                                int impl, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (top_k <= 0 || top_k > experts || impl < 0 || impl > 2) return SE_ERR_ARGUMENT;
-    return launch_select(logits, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, impl, stream);
+    if (top_k <= 0 || top_k > experts || impl < 0 || impl > 2 || chunks < 1 || terms < 1) return SE_ERR_ARGUMENT;
+    return launch_select(logits, chunks, terms, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize,
+                         routed_scale, impl, stream);
 }
 
 // Most experts the selection takes (four floats per expert in 200 KB of shared memory), and the
@@ -595,5 +648,6 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
                                                                                         hidden, experts);
         }
     });
-    return launch_select(logits, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, 0, stream);
+    return launch_select(logits, 1, 1, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, 0,
+                         stream);
 }

@@ -204,9 +204,10 @@ class SparseMoE(_RoutedSwiGLU):
         if split is not None:
             chunks, kc, _ = split.shape
             parts = torch.bmm(x.view(tokens, chunks, kc).transpose(0, 1), split, out_dtype=torch.float32)
-            logits = parts.view(chunks, tokens, 3, self.num_experts).sum(dim=(0, 2))
-            ops.router_select(logits, self.selection_bias, ids, weights, top_k=self.top_k, score_fn=s.score_fn,
-                              renormalize=s.renormalize, routed_scale=s.routed_scale)
+            # the selection adds the parts itself (chunk by chunk, term by term)
+            ops.router_select(parts.view(chunks, tokens, 3, self.num_experts), self.selection_bias, ids, weights,
+                              top_k=self.top_k, score_fn=s.score_fn, renormalize=s.renormalize,
+                              routed_scale=s.routed_scale)
         else:
             ops.router(x, self.gate, self.selection_bias, ids, weights, top_k=self.top_k, score_fn=s.score_fn,
                        renormalize=s.renormalize, routed_scale=s.routed_scale)

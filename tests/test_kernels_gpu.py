@@ -262,6 +262,21 @@ def test_router_selection_by_a_warp_equals_selection_by_a_block(tokens, experts,
     same = (out["warp"][1] == out["block"][1]) | (out["warp"][1].isnan() & out["block"][1].isnan())
     assert bool(same.all())
     assert int(out["block"][0].min()) >= 0 and all(len(set(r)) == top_k for r in out["block"][0].tolist())
+    # logits that arrive in parts [chunks, tokens, terms, experts] are added inside the kernels, chunk by
+    # chunk and term by term: the same choice and weights as from the sums taken in that order beforehand
+    parts = torch.randn(3, tokens, 2, experts, generator=g).to(DEV)
+    summed = torch.zeros(tokens, experts, device=DEV)
+    for c in range(3):
+        for k in range(2):
+            summed = summed + parts[c, :, k]
+    for impl in ("block", "warp"):
+        got, want = [], []
+        for src, dst in ((parts, got), (summed, want)):
+            ids = torch.full((tokens, top_k), -1, dtype=torch.int32, device=DEV)
+            w = torch.full((tokens, top_k), -1.0, dtype=torch.float32, device=DEV)
+            ops.router_select(src, bias if kind != "nan" else None, ids, w, top_k=top_k, impl=impl)
+            dst.extend([ids.cpu(), w.cpu()])
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]), impl
     with pytest.raises(ValueError, match="does not support"):
         ops.router_select(torch.zeros(2, 300, device=DEV), None, torch.empty(2, 2, dtype=torch.int32, device=DEV),
                           torch.empty(2, 2, device=DEV), top_k=2, impl="warp")       # more than 256 experts
