@@ -176,7 +176,6 @@ def bench_dense(a, dev):
     out = torch.empty(a.tokens, a.n, dtype=torch.bfloat16, device=dev)
     i = [0]
 
-    from ..parts import linear as linear_mod
 
     def run_lib():
         torch.matmul(x, ws[i[0] % len(ws)].t(), out=out)

@@ -15,7 +15,7 @@ import torch
 
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
-from ..parts.base import KVRequest, LayerSlot, StateRequest, StepContext, make_norm
+from ..parts.base import KVRequest, StateRequest, StepContext, make_norm
 from ..parts.block import PreNormBlock, make_block
 from ..parts.linear import linear
 

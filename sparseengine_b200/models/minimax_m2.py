@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import re
 from dataclasses import dataclass, fields
-from typing import Any, Optional
+from typing import Optional
 
 from ..config.registry import register_architecture
 from ..config.specs import (AttentionSpec, LayerSpec, ModelSpec, MoESpec, RMSNormSpec,

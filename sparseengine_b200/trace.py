@@ -4,7 +4,6 @@ from __future__ import annotations
 import json
 import os
 
-import numpy as np
 import torch
 
 from .engine.factory import build_runner

@@ -6,7 +6,7 @@ import pytest
 import plain_m2
 from sparseengine_b200 import models  # noqa: F401
 from sparseengine_b200.config.engine_config import Config
-from sparseengine_b200.config.registry import architectures, load_model_spec, register_architecture
+from sparseengine_b200.config.registry import architectures, load_model_spec
 from sparseengine_b200.models.minimax_m2 import MiniMaxM2Config
 
 
